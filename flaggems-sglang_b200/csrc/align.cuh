@@ -1,0 +1,26 @@
+// Host-callable launchers of the routing / alignment kernels.
+#pragma once
+#include "common.cuh"
+
+namespace b200moe {
+
+int align_capacity(int n_slots, int n_experts, int block);
+int routing_max_tiles(int n_slots, int n_experts);
+
+// Block-aligned grouping (+ optional internal tables for the GEMMs: per-row
+// routing weight, per-expert block prefix, meta[0] = blocks, meta[1] = rows).
+int launch_align_block(const void* ids, int is64, const int* map, const float* weights, int P, int E,
+                       int block, int cap, int* sorted_ids, int* expert_ids, int* num_post_pad,
+                       float* row_gamma, int* blk_off, int* meta, cudaStream_t stream);
+
+// Same internal tables from hist / topk_indx / gate_scal of the routing triple.
+int launch_align_from_routing(const int* hist, const int* topk_indx, const float* gate_scal, int P,
+                              int E, int block, int cap, int* sorted_ids, float* row_gamma,
+                              int* blk_off, int* meta, cudaStream_t stream);
+
+int launch_routing_from_topk(const float* weights, const void* ids, int is64, int M, int k, int E,
+                             int* expt_indx, int* topk_indx, int* gate_indx, float* gate_scal,
+                             int* hist, int* token_offs_raw, int* token_offs_pad, int* block_pid_map,
+                             cudaStream_t stream);
+
+}  // namespace b200moe

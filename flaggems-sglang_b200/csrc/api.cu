@@ -1,0 +1,446 @@
+// C ABI: argument checks, workspace layout, tensor-map encoding and the launch sequence.
+#include <mutex>
+#include <vector>
+
+#include "align.cuh"
+#include "gemm.cuh"
+#include "prep.cuh"
+
+using namespace b200moe;
+
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+CUtensorMapDataType tmap_dtype(int dtype, int elem_bytes) {
+  if (elem_bytes == 1) return CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  return dtype == B200MOE_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+}
+
+// [rows, inner] row-major matrix, box = {box_inner, box_rows}, 128-byte swizzle.
+int make_tmap_2d(CUtensorMap* m, CUtensorMapDataType dt, int elem_bytes, const void* base, uint64_t inner,
+                 uint64_t rows, uint32_t box_inner, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return B200MOE_ERR_CUDA;
+  cuuint64_t dims[2] = {inner, rows};
+  cuuint64_t strides[1] = {inner * elem_bytes};
+  cuuint32_t box[2] = {box_inner, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200MOE_OK : B200MOE_ERR_CUDA;
+}
+
+// [experts, rows, inner] tensor, box = {box_inner, box_rows, 1}.
+int make_tmap_3d(CUtensorMap* m, CUtensorMapDataType dt, int elem_bytes, const void* base, uint64_t inner,
+                 uint64_t rows, uint64_t experts, uint32_t box_inner, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return B200MOE_ERR_CUDA;
+  cuuint64_t dims[3] = {inner, rows, experts};
+  cuuint64_t strides[2] = {inner * elem_bytes, inner * rows * elem_bytes};
+  cuuint32_t box[3] = {box_inner, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(m, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200MOE_OK : B200MOE_ERR_CUDA;
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Optional per-kernel timing for the benchmark: CUDA events recorded around the two
+// GEMM launches of every forward call between profile_begin and profile_end.
+struct Profile {
+  std::mutex mu;
+  bool on = false;
+  int max_calls = 0, calls = 0;
+  std::vector<cudaEvent_t> ev;  // kMarks events per call
+};
+Profile g_prof;
+
+// mark index: 0 = call start, 1 = before GEMM-1, 2 = after GEMM-1, 3 = before GEMM-2, 4 = after GEMM-2, 5 = call end
+constexpr int kMarks = 6;
+
+int prof_slot() {
+  if (!g_prof.on) return -1;
+  std::lock_guard<std::mutex> lk(g_prof.mu);
+  if (!g_prof.on || g_prof.calls >= g_prof.max_calls) return -1;
+  return g_prof.calls++;
+}
+void prof_mark(int slot, int mark, cudaStream_t st) {
+  if (slot >= 0) cudaEventRecord(g_prof.ev[static_cast<size_t>(slot) * kMarks + mark], st);
+}
+
+struct Layout {
+  int BT, cap, P;
+  int act_bytes;  // bytes per activation element fed to the GEMMs
+  size_t meta, blk_off, sorted_ids, expert_ids, num_post, row_gamma, xs, xs_scale, a2, a2_scale, out32,
+      total;
+};
+
+int pick_bt(const b200moe_cfg* c) {
+  if (c->block_tokens > 0) return c->block_tokens;
+  const double avg = static_cast<double>(c->M) * c->topk / (c->E > 0 ? c->E : 1);
+  if (avg <= 10) return 16;
+  if (avg <= 20) return 32;
+  if (avg <= 40) return 64;
+  if (avg < 512) return 128;
+  return 256;
+}
+
+int check_cfg(const b200moe_cfg* c) {
+  if (c == nullptr || c->struct_bytes != static_cast<int32_t>(sizeof(b200moe_cfg))) return B200MOE_ERR_BAD_ARG;
+  if (c->M < 0 || c->H <= 0 || c->I <= 0 || c->E <= 0 || c->topk <= 0) return B200MOE_ERR_BAD_ARG;
+  if (c->dtype != B200MOE_DTYPE_BF16 && c->dtype != B200MOE_DTYPE_FP16) return B200MOE_ERR_BAD_ARG;
+  if (c->activation != B200MOE_ACT_SILU && c->activation != B200MOE_ACT_GELU) return B200MOE_ERR_BAD_ARG;
+  if (c->block_tokens != 0 && (c->block_tokens < 16 || c->block_tokens > 256 || c->block_tokens % 16))
+    return B200MOE_ERR_BAD_ARG;
+  if (static_cast<long long>(c->M) * c->topk > (1LL << 24)) return B200MOE_ERR_TOO_LARGE;
+  if (c->H % 8 != 0 || c->I % 8 != 0) return B200MOE_ERR_UNSUPPORTED;  // 16-byte rows for TMA
+  if (c->wmode == B200MOE_W_16BIT) {
+    if (c->w_layout != B200MOE_LAYOUT_LAYER) return B200MOE_ERR_UNSUPPORTED;
+  } else if (c->wmode == B200MOE_W_FP8_BLOCK) {
+    if (c->H % 128 != 0 || c->I % 128 != 0) return B200MOE_ERR_UNSUPPORTED;
+  } else {
+    return B200MOE_ERR_UNSUPPORTED;
+  }
+  return B200MOE_OK;
+}
+
+int make_layout(const b200moe_cfg* c, Layout* L) {
+  L->BT = pick_bt(c);
+  L->P = c->M * c->topk;
+  int cap = align_capacity(L->P, c->E, L->BT);
+  if (cap < 0) return B200MOE_ERR_TOO_LARGE;
+  cap = static_cast<int>(align_up(static_cast<size_t>(cap > 0 ? cap : 1), L->BT));
+  L->cap = cap;
+  const bool fp8 = c->wmode == B200MOE_W_FP8_BLOCK;
+  L->act_bytes = fp8 ? 1 : 2;
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    size_t o = off;
+    off = align_up(off + bytes, 1024);
+    return o;
+  };
+  L->meta = take(64);
+  L->blk_off = take(static_cast<size_t>(c->E + 1) * 4);
+  L->sorted_ids = take(static_cast<size_t>(cap) * 4);
+  L->expert_ids = take(static_cast<size_t>(cap / L->BT + 1) * 4);
+  L->num_post = take(16);
+  L->row_gamma = take(static_cast<size_t>(cap) * 4);
+  L->xs = take(static_cast<size_t>(cap) * c->H * L->act_bytes);
+  L->xs_scale = take(fp8 ? static_cast<size_t>(cap) * (c->H / 128) * 4 : 0);
+  L->a2 = take(static_cast<size_t>(cap) * c->I * L->act_bytes);
+  L->a2_scale = take(fp8 ? static_cast<size_t>(cap) * (c->I / 128) * 4 : 0);
+  L->out32 = take(static_cast<size_t>(c->M > 0 ? c->M : 1) * c->H * 4);
+  L->total = off;
+  return B200MOE_OK;
+}
+
+int query_sms(const b200moe_cfg* c) {
+  if (c->num_sms > 0) return c->num_sms;
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+// Everything after the internal routing tables exist in the workspace.
+int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void* w1, const void* w2,
+                const b200moe_quant* quant, uint8_t* ws, void* out, int32_t* status, cudaStream_t st,
+                int slot) {
+  const int sms = query_sms(c);
+  int* meta = reinterpret_cast<int*>(ws + L.meta);
+  int* blk_off = reinterpret_cast<int*>(ws + L.blk_off);
+  int* sorted_ids = reinterpret_cast<int*>(ws + L.sorted_ids);
+  float* row_gamma = reinterpret_cast<float*>(ws + L.row_gamma);
+  void* xs = ws + L.xs;
+  void* a2 = ws + L.a2;
+  float* out32 = reinterpret_cast<float*>(ws + L.out32);
+  const bool fp8 = c->wmode == B200MOE_W_FP8_BLOCK;
+  int rc;
+
+  if (fp8) {
+    if (quant == nullptr || quant->w1_scale == nullptr || quant->w2_scale == nullptr) return B200MOE_ERR_BAD_ARG;
+    rc = launch_group_quant_fp8(x, c->dtype, xs, reinterpret_cast<float*>(ws + L.xs_scale), sorted_ids, meta,
+                                L.P, c->topk, L.cap, c->H, 1, L.cap, sms, st);
+  } else {
+    rc = launch_gather_rows(x, xs, sorted_ids, meta, L.P, c->topk, c->H * 2, L.cap, sms, st);
+  }
+  if (rc != B200MOE_OK) return rc;
+
+  GemmArgs g1 = {};
+  g1.mode = 0;
+  g1.dtype = c->dtype;
+  g1.wmode = c->wmode;
+  g1.E = c->E;
+  g1.K = c->H;
+  g1.N = c->I;
+  g1.up_row_off = c->I;
+  g1.BT = L.BT;
+  g1.topk = c->topk;
+  g1.P = L.P;
+  g1.flags = c->flags;
+  g1.activation = c->activation;
+  g1.meta = meta;
+  g1.blk_off = blk_off;
+  g1.sorted_ids = sorted_ids;
+  g1.row_gamma = row_gamma;
+  g1.out = a2;
+  g1.ld_out = c->I;
+  g1.status = status;
+  if (fp8) {
+    g1.w_scale = quant->w1_scale;
+    g1.w_scale_rows = (2 * c->I + 127) / 128;
+    g1.x_scale = reinterpret_cast<float*>(ws + L.xs_scale);
+    g1.ld_xscale = L.cap;
+    g1.out_q = reinterpret_cast<uint8_t*>(a2);
+    g1.out_scale = reinterpret_cast<float*>(ws + L.a2_scale);
+  }
+  gemm_plan(&g1);
+
+  GemmArgs g2 = g1;
+  g2.mode = 1;
+  g2.K = c->I;
+  g2.N = c->H;
+  g2.up_row_off = 0;
+  g2.out = out32;
+  g2.ld_out = c->H;
+  g2.max_split = 0;
+  if (fp8) {
+    g2.w_scale = quant->w2_scale;
+    g2.w_scale_rows = (c->H + 127) / 128;
+    g2.x_scale = reinterpret_cast<float*>(ws + L.a2_scale);
+    g2.out_q = nullptr;
+    g2.out_scale = nullptr;
+  }
+  gemm_plan(&g2);
+
+  if (c->flags & B200MOE_FLAG_SIMT) {
+    rc = launch_gemm_simt(w1, xs, g1, st, L.cap);
+    if (rc != B200MOE_OK) return rc;
+    if (cudaMemsetAsync(out32, 0, static_cast<size_t>(c->M) * c->H * 4, st) != cudaSuccess) return B200MOE_ERR_CUDA;
+    rc = launch_gemm_simt(w2, a2, g2, st, L.cap);
+    if (rc != B200MOE_OK) return rc;
+  } else {
+    const int eb = L.act_bytes;
+    const CUtensorMapDataType dt = tmap_dtype(c->dtype, eb);
+    const uint32_t kbox = 128 / eb;
+    CUtensorMap tm_w1, tm_x, tm_w2, tm_a2;
+    if ((rc = make_tmap_3d(&tm_w1, dt, eb, w1, c->H, 2ull * c->I, c->E, kbox, 128)) != B200MOE_OK) return rc;
+    if ((rc = make_tmap_2d(&tm_x, dt, eb, xs, c->H, L.cap, kbox, L.BT)) != B200MOE_OK) return rc;
+    if ((rc = make_tmap_3d(&tm_w2, dt, eb, w2, c->I, c->H, c->E, kbox, 128)) != B200MOE_OK) return rc;
+    if ((rc = make_tmap_2d(&tm_a2, dt, eb, a2, c->I, L.cap, kbox, L.BT)) != B200MOE_OK) return rc;
+    prof_mark(slot, 1, st);
+    rc = launch_gemm_tc(tm_w1, tm_x, g1, sms, st);
+    prof_mark(slot, 2, st);
+    if (rc != B200MOE_OK) return rc;
+    if (cudaMemsetAsync(out32, 0, static_cast<size_t>(c->M) * c->H * 4, st) != cudaSuccess) return B200MOE_ERR_CUDA;
+    prof_mark(slot, 3, st);
+    rc = launch_gemm_tc(tm_w2, tm_a2, g2, sms, st);
+    prof_mark(slot, 4, st);
+    if (rc != B200MOE_OK) return rc;
+  }
+  rc = launch_finalize(out32, out, c->dtype, static_cast<size_t>(c->M) * c->H, c->routed_scaling, sms, st);
+  prof_mark(slot, 5, st);
+  return rc;
+}
+
+}  // namespace
+
+extern "C" {
+
+int b200moe_version(void) { return B200MOE_VERSION; }
+
+const char* b200moe_status_string(int code) {
+  switch (code) {
+    case B200MOE_OK: return "ok";
+    case B200MOE_ERR_BAD_ARG: return "bad argument";
+    case B200MOE_ERR_UNSUPPORTED: return "unsupported shape, dtype or layout";
+    case B200MOE_ERR_WORKSPACE: return "workspace too small or misaligned";
+    case B200MOE_ERR_CUDA: return "CUDA runtime or driver call failed";
+    case B200MOE_ERR_DEVICE_TIMEOUT: return "a device-side wait ran out of time";
+    case B200MOE_ERR_TOO_LARGE: return "problem too large for this build";
+    default: return "unknown status";
+  }
+}
+
+int b200moe_pick_block_tokens(const b200moe_cfg* cfg) {
+  int rc = check_cfg(cfg);
+  if (rc != B200MOE_OK) return rc;
+  return pick_bt(cfg);
+}
+
+size_t b200moe_workspace_bytes(const b200moe_cfg* cfg) {
+  if (check_cfg(cfg) != B200MOE_OK) return 0;
+  Layout L;
+  if (make_layout(cfg, &L) != B200MOE_OK) return 0;
+  return L.total;
+}
+
+int b200moe_align_capacity(int n_slots, int n_experts, int block) {
+  if (n_slots < 0 || n_experts <= 0 || block <= 0) return B200MOE_ERR_BAD_ARG;
+  int cap = align_capacity(n_slots, n_experts, block);
+  return cap < 0 ? B200MOE_ERR_TOO_LARGE : cap;
+}
+
+int b200moe_align_block_size(const void* topk_ids, int ids_are_i64, int n_slots, int n_experts, int block,
+                             const int32_t* expert_map, int32_t* sorted_token_ids, int32_t* expert_ids,
+                             int32_t* num_tokens_post_padded, void* stream) {
+  if (n_slots < 0 || n_experts <= 0 || block <= 0) return B200MOE_ERR_BAD_ARG;
+  if (sorted_token_ids == nullptr || expert_ids == nullptr || num_tokens_post_padded == nullptr)
+    return B200MOE_ERR_BAD_ARG;
+  if (n_slots > 0 && topk_ids == nullptr) return B200MOE_ERR_BAD_ARG;
+  int cap = align_capacity(n_slots, n_experts, block);
+  if (cap < 0) return B200MOE_ERR_TOO_LARGE;
+  return launch_align_block(topk_ids, ids_are_i64, expert_map, nullptr, n_slots, n_experts, block, cap,
+                            sorted_token_ids, expert_ids, num_tokens_post_padded, nullptr, nullptr, nullptr,
+                            static_cast<cudaStream_t>(stream));
+}
+
+int b200moe_routing_max_tiles(int n_slots, int n_experts) {
+  if (n_slots < 0 || n_experts <= 0) return B200MOE_ERR_BAD_ARG;
+  return routing_max_tiles(n_slots, n_experts);
+}
+
+int b200moe_routing_from_topk(const float* topk_weights, const void* topk_ids, int ids_are_i64, int n_tokens,
+                              int topk, int n_experts, int32_t* expt_indx, int32_t* topk_indx,
+                              int32_t* gate_indx, float* gate_scal, int32_t* hist, int32_t* token_offs_raw,
+                              int32_t* token_offs_pad, int32_t* block_pid_map, void* stream) {
+  if (n_tokens < 0 || topk <= 0 || n_experts <= 0) return B200MOE_ERR_BAD_ARG;
+  if (!expt_indx || !topk_indx || !gate_indx || !gate_scal || !hist || !token_offs_raw || !token_offs_pad ||
+      !block_pid_map)
+    return B200MOE_ERR_BAD_ARG;
+  if (n_tokens > 0 && (!topk_weights || !topk_ids)) return B200MOE_ERR_BAD_ARG;
+  return launch_routing_from_topk(topk_weights, topk_ids, ids_are_i64, n_tokens, topk, n_experts, expt_indx,
+                                  topk_indx, gate_indx, gate_scal, hist, token_offs_raw, token_offs_pad,
+                                  block_pid_map, static_cast<cudaStream_t>(stream));
+}
+
+static int forward_common(const b200moe_cfg* cfg, const void* x, const void* w1, const void* w2, void* workspace,
+                          size_t workspace_bytes, void* out, int32_t* status, Layout* L) {
+  int rc = check_cfg(cfg);
+  if (rc != B200MOE_OK) return rc;
+  if (!x || !w1 || !w2 || !workspace || !out || !status) return B200MOE_ERR_BAD_ARG;
+  if ((rc = make_layout(cfg, L)) != B200MOE_OK) return rc;
+  if (workspace_bytes < L->total || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0) return B200MOE_ERR_WORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w1) & 15) ||
+      (reinterpret_cast<uintptr_t>(w2) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
+    return B200MOE_ERR_BAD_ARG;
+  return B200MOE_OK;
+}
+
+int b200moe_forward_topk(const b200moe_cfg* cfg, const void* x, const void* w1, const void* w2,
+                         const b200moe_quant* quant, const float* topk_weights, const void* topk_ids,
+                         const int32_t* expert_map, void* workspace, size_t workspace_bytes, void* out,
+                         int32_t* status, void* stream) {
+  Layout L;
+  int rc = forward_common(cfg, x, w1, w2, workspace, workspace_bytes, out, status, &L);
+  if (rc != B200MOE_OK) return rc;
+  if (cfg->M == 0) return B200MOE_OK;
+  if (!topk_weights || !topk_ids) return B200MOE_ERR_BAD_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+  const int slot = prof_slot();
+  prof_mark(slot, 0, st);
+  rc = launch_align_block(topk_ids, (cfg->flags & B200MOE_FLAG_IDS_I64) ? 1 : 0, expert_map, topk_weights, L.P,
+                          cfg->E, L.BT, L.cap, reinterpret_cast<int*>(ws + L.sorted_ids),
+                          reinterpret_cast<int*>(ws + L.expert_ids), reinterpret_cast<int*>(ws + L.num_post),
+                          reinterpret_cast<float*>(ws + L.row_gamma), reinterpret_cast<int*>(ws + L.blk_off),
+                          reinterpret_cast<int*>(ws + L.meta), st);
+  if (rc != B200MOE_OK) return rc;
+  return run_experts(cfg, L, x, w1, w2, quant, ws, out, status, st, slot);
+}
+
+int b200moe_forward_routed(const b200moe_cfg* cfg, const void* x, const void* w1, const void* w2,
+                           const b200moe_quant* quant, const int32_t* hist, const int32_t* topk_indx,
+                           const float* gate_scal, void* workspace, size_t workspace_bytes, void* out,
+                           int32_t* status, void* stream) {
+  Layout L;
+  int rc = forward_common(cfg, x, w1, w2, workspace, workspace_bytes, out, status, &L);
+  if (rc != B200MOE_OK) return rc;
+  if (cfg->M == 0) return B200MOE_OK;
+  if (!hist || !topk_indx || !gate_scal) return B200MOE_ERR_BAD_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+  const int slot = prof_slot();
+  prof_mark(slot, 0, st);
+  rc = launch_align_from_routing(hist, topk_indx, gate_scal, L.P, cfg->E, L.BT, L.cap,
+                                 reinterpret_cast<int*>(ws + L.sorted_ids),
+                                 reinterpret_cast<float*>(ws + L.row_gamma),
+                                 reinterpret_cast<int*>(ws + L.blk_off), reinterpret_cast<int*>(ws + L.meta), st);
+  if (rc != B200MOE_OK) return rc;
+  return run_experts(cfg, L, x, w1, w2, quant, ws, out, status, st, slot);
+}
+
+int b200moe_profile_begin(int max_calls) {
+  if (max_calls <= 0 || max_calls > 4096) return B200MOE_ERR_BAD_ARG;
+  std::lock_guard<std::mutex> lk(g_prof.mu);
+  for (cudaEvent_t e : g_prof.ev) cudaEventDestroy(e);
+  g_prof.ev.assign(static_cast<size_t>(max_calls) * kMarks, nullptr);
+  for (auto& e : g_prof.ev)
+    if (cudaEventCreate(&e) != cudaSuccess) return B200MOE_ERR_CUDA;
+  g_prof.max_calls = max_calls;
+  g_prof.calls = 0;
+  g_prof.on = true;
+  return B200MOE_OK;
+}
+
+int b200moe_profile_end(double* gemm1_ms, double* gemm2_ms, double* total_ms, int* calls) {
+  std::lock_guard<std::mutex> lk(g_prof.mu);
+  if (!g_prof.on) return B200MOE_ERR_BAD_ARG;
+  g_prof.on = false;
+  double g1 = 0, g2 = 0, tot = 0;
+  int rc = B200MOE_OK;
+  for (int i = 0; i < g_prof.calls; ++i) {
+    cudaEvent_t* e = &g_prof.ev[static_cast<size_t>(i) * kMarks];
+    float a = 0, b = 0, t = 0;
+    if (cudaEventSynchronize(e[5]) != cudaSuccess || cudaEventElapsedTime(&a, e[1], e[2]) != cudaSuccess ||
+        cudaEventElapsedTime(&b, e[3], e[4]) != cudaSuccess || cudaEventElapsedTime(&t, e[0], e[5]) != cudaSuccess) {
+      rc = B200MOE_ERR_CUDA;
+      break;
+    }
+    g1 += a; g2 += b; tot += t;
+  }
+  if (gemm1_ms) *gemm1_ms = g1;
+  if (gemm2_ms) *gemm2_ms = g2;
+  if (total_ms) *total_ms = tot;
+  if (calls) *calls = g_prof.calls;
+  for (cudaEvent_t e : g_prof.ev) cudaEventDestroy(e);
+  g_prof.ev.clear();
+  g_prof.calls = 0;
+  return rc;
+}
+
+int b200moe_per_token_group_quant_fp8(const void* x, int dtype, int rows, int K, void* q, float* scales,
+                                      void* stream) {
+  if (rows < 0 || K <= 0 || !x || !q || !scales) return B200MOE_ERR_BAD_ARG;
+  if (dtype != B200MOE_DTYPE_BF16 && dtype != B200MOE_DTYPE_FP16) return B200MOE_ERR_BAD_ARG;
+  if (rows == 0) return B200MOE_OK;
+  return launch_group_quant_fp8(x, dtype, q, scales, nullptr, nullptr, 0, 1, rows, K, 0, 0, 148,
+                                static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

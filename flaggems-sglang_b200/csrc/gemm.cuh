@@ -1,0 +1,52 @@
+// Grouped expert GEMMs: argument block and launchers.
+#pragma once
+#include "common.cuh"
+
+namespace b200moe {
+
+// Orientation: the expert weight tile sits on the 128-row side of the tensor-core
+// instruction and the (block of) tokens on its N side, so a decode-sized token
+// block of 16 wastes nothing and a prefill block of 256 fills the widest shape.
+struct GemmArgs {
+  int mode;        // 0: gate/up projection + activation; 1: down projection + weighted scatter-add
+  int dtype;       // B200MOE_DTYPE_* of activations / 16-bit weights
+  int wmode;       // B200MOE_W_*
+  int E;           // local experts
+  int K;           // reduction length (H for mode 0, I for mode 1)
+  int N;           // output rows per expert covered by tiles of 128 (I for mode 0, H for mode 1)
+  int up_row_off;  // mode 0: row of the first "up" weight inside an expert (= I)
+  int BT;          // tokens per block (16..256, multiple of 16)
+  int stages;      // shared-memory ring depth
+  int acc_stages;  // accumulator buffers in tensor memory (1 or 2)
+  int tmem_cols;   // allocated tensor-memory columns (power of two >= 32)
+  int num_nt;      // ceil(N / 128)
+  int kblocks;     // ceil(K / kblock elements)
+  int topk;
+  int P;           // M * topk
+  int flags;       // B200MOE_FLAG_*
+  int activation;  // B200MOE_ACT_*
+  int max_split;   // mode 1: upper bound for the reduction split
+  const int* meta;        // [0] = token blocks, [1] = padded rows
+  const int* blk_off;     // [E+1] first block of each expert
+  const int* sorted_ids;  // [cap] slot of each padded row (>= P: padding)
+  const float* row_gamma; // [cap] routing weight of each padded row
+  void* out;              // mode 0: activations [cap, N]; mode 1: fp32 combine buffer [M, N]
+  long long ld_out;       // row stride of out in elements
+  int* status;            // device status word
+  // FP8 block-scaled mode
+  const float* w_scale;   // [E, ceil(rows/128), ceil(K/128)] (rows = 2I for mode 0)
+  const float* x_scale;   // [K/128][ld_xscale] group-major activation scales
+  int ld_xscale;
+  int w_scale_rows;       // scale rows per expert
+  uint8_t* out_q;         // mode 0 FP8: quantised activations [cap, N]
+  float* out_scale;       // mode 0 FP8: [N/128][ld_xscale]
+};
+
+size_t gemm_smem_bytes(const GemmArgs& a);
+void gemm_plan(GemmArgs* a);  // fills stages / acc_stages / tmem_cols / num_nt / kblocks from the rest
+
+int launch_gemm_tc(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmArgs& a, int num_sms,
+                   cudaStream_t stream);
+int launch_gemm_simt(const void* w, const void* x, const GemmArgs& a, cudaStream_t stream, int cap);
+
+}  // namespace b200moe

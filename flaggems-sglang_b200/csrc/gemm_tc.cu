@@ -1,0 +1,381 @@
+// Grouped expert GEMMs on the sm_100a tensor cores (tcgen05.mma, accumulators in
+// tensor memory, operands staged by TMA into a shared-memory ring).
+//
+// One persistent CTA per SM, six warps:
+//   warp 0      one thread issues the TMA loads (weight tile(s) + token block per stage)
+//   warp 1      one thread issues the MMAs and the commits; the warp owns the TMEM allocation
+//   warps 2-5   epilogue: tcgen05.ld the accumulator, apply the fused tail, store
+//
+// mode 0 (gate/up): per stage a 128-row gate tile and the matching 128-row up tile; two
+//   accumulators, so that lane i of TMEM holds gate[n0+i] and up[n0+i] for every token of
+//   the block and the activation needs no data exchange.
+// mode 1 (down):    one 128-row tile; the reduction may be split over CTAs; the epilogue
+//   multiplies by the routing weight and adds into the fp32 combine buffer with
+//   red.global.add.f32 (which also merges the top-k experts of a token).
+//
+// Every wait is bounded; on a time-out the CTA raises an abort flag, all roles leave their
+// loops, the status word is set, TMEM is freed and the kernel returns.
+#include "gemm.cuh"
+
+namespace b200moe {
+
+namespace {
+
+constexpr int kThreads = 192;
+constexpr int kTileRows = 128;           // weight rows per MMA (the instruction's M)
+constexpr int kStageKBytes = 128;        // bytes of the reduction dim per stage row (one swizzle atom)
+constexpr int kTileBytes = kTileRows * kStageKBytes;  // 16 KiB
+constexpr int kMaxBT = 256;
+constexpr size_t kSmemLimit = 232448;    // 227 KiB
+
+struct Ctrl {
+  int nblocks;
+  int units_per_block;  // num_nt (* split)
+  int split;
+  int total;
+  int grid_eff;
+};
+
+__device__ __forceinline__ int pick_split(int tiles, int kblocks, int grid, int max_split) {
+  int best = 1;
+  float best_eff = -1.f;
+  int smax = min(max_split, max(1, kblocks / 4));
+  for (int s = 1; s <= smax; ++s) {
+    int total = tiles * s;
+    int waves = (total + grid - 1) / grid;
+    float eff = static_cast<float>(total) / static_cast<float>(waves * grid);
+    if (eff > best_eff + 0.04f) {
+      best_eff = eff;
+      best = s;
+    }
+  }
+  return best;
+}
+
+struct TileCoord {
+  int e;      // expert
+  int row0;   // first padded row of the token block
+  int n0;     // first weight row inside the expert
+  int kb0, kb1;  // k-block range
+};
+
+__device__ __forceinline__ TileCoord decode_tile(int id, const Ctrl& c, const int* s_blk_off, int E,
+                                                 int BT, int num_nt, int kblocks) {
+  // largest e with blk_off[e] * units <= id
+  int lo = 0, hi = E;
+  const int u = c.units_per_block;
+  while (hi - lo > 1) {
+    int mid = (lo + hi) >> 1;
+    if (s_blk_off[mid] * u <= id) lo = mid; else hi = mid;
+  }
+  TileCoord t;
+  t.e = lo;
+  const int first = s_blk_off[lo];
+  const int nb = s_blk_off[lo + 1] - first;
+  const int local = id - first * u;
+  const int b = local % nb;
+  const int rest = local / nb;
+  const int s = rest % c.split;
+  const int nt = rest / c.split;
+  t.row0 = (first + b) * BT;
+  t.n0 = nt * kTileRows;
+  t.kb0 = static_cast<int>((static_cast<long long>(s) * kblocks) / c.split);
+  t.kb1 = static_cast<int>((static_cast<long long>(s + 1) * kblocks) / c.split);
+  return t;
+}
+
+template <int MODE, typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                   const GemmArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  constexpr int A_BYTES = (MODE == 0 ? 2 : 1) * kTileBytes;
+  const int BT = a.BT;
+  const int b_bytes = BT * kStageKBytes;
+  const int stage_bytes = A_BYTES + b_bytes;
+  const int stages = a.stages;
+
+  uint8_t* ctrl_base = smem + static_cast<size_t>(stages) * stage_bytes;
+  uint64_t* bar_full = reinterpret_cast<uint64_t*>(ctrl_base);
+  uint64_t* bar_empty = bar_full + stages;
+  uint64_t* bar_tfull = bar_empty + stages;
+  uint64_t* bar_tempty = bar_tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* s_col_row = reinterpret_cast<int*>(tmem_slot + 4);          // [2][kMaxBT]
+  float* s_col_gam = reinterpret_cast<float*>(s_col_row + 2 * kMaxBT);  // [2][kMaxBT]
+  int* s_blk_off = reinterpret_cast<int*>(s_col_gam + 2 * kMaxBT);  // [E+1]
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&bar_tfull[s]), 1);
+      mbar_init(smem_u32(&bar_tempty[s]), 4);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+    prefetch_tmap(&tm_w);
+    prefetch_tmap(&tm_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), static_cast<uint32_t>(a.tmem_cols));
+    tmem_relinquish();
+  }
+  for (int e = threadIdx.x; e <= a.E; e += blockDim.x) s_blk_off[e] = a.blk_off[e];
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // ---- work decomposition, identical in every thread of every CTA
+  Ctrl c;
+  c.nblocks = a.meta[0];
+  c.split = 1;
+  if (MODE == 1 && !(a.flags & B200MOE_FLAG_NO_SPLIT_K))
+    c.split = pick_split(c.nblocks * a.num_nt, a.kblocks, gridDim.x, a.max_split);
+  c.units_per_block = a.num_nt * c.split;
+  c.total = c.nblocks * c.units_per_block;
+  {
+    int waves = (c.total + gridDim.x - 1) / static_cast<int>(gridDim.x);
+    c.grid_eff = waves > 0 ? (c.total + waves - 1) / waves : 1;
+  }
+  const int cols_per_acc = (MODE == 0 ? 2 : 1) * BT;
+  const bool active = static_cast<int>(blockIdx.x) < c.grid_eff;
+
+  if (active && warp == 0 && lane == 0) {
+    // =============================== TMA producer ===============================
+    int stage = 0;
+    uint32_t phase = 0;
+    long long issued = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < c.total; tile += c.grid_eff) {
+      const TileCoord t = decode_tile(tile, c, s_blk_off, a.E, BT, a.num_nt, a.kblocks);
+      for (int kb = t.kb0; kb < t.kb1; ++kb) {
+        if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1, abort_flag, DEV_TIMEOUT_PRODUCER)) {
+          ok = false;
+          break;
+        }
+        const uint32_t full = smem_u32(&bar_full[stage]);
+        mbar_arrive_expect_tx(full, static_cast<uint32_t>(stage_bytes));
+        const uint32_t sa = smem_u32(smem + static_cast<size_t>(stage) * stage_bytes);
+        const int k0 = kb * (kStageKBytes / static_cast<int>(sizeof(T)));
+        tma_load_3d(sa, &tm_w, full, k0, t.n0, t.e);
+        if (MODE == 0) tma_load_3d(sa + kTileBytes, &tm_w, full, k0, a.up_row_off + t.n0, t.e);
+        tma_load_2d(sa + A_BYTES, &tm_x, full, k0, t.row0);
+        ++issued;
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+    if (!ok) {
+      // let the copies still in flight land before the CTA goes away
+      const int n = static_cast<int>(issued < stages ? issued : stages);
+      for (int i = 1; i <= n; ++i) {
+        int s = stage - i;
+        uint32_t ph = phase;
+        if (s < 0) {
+          s += stages;
+          ph ^= 1;
+        }
+        mbar_wait_brief(smem_u32(&bar_full[s]), ph);
+      }
+    }
+  } else if (active && warp == 1 && lane == 0) {
+    // =============================== MMA issuer =================================
+    const uint32_t idesc = make_idesc(sizeof(T) == 2 ? (a.dtype == B200MOE_DTYPE_BF16 ? 1u : 0u) : 0u,
+                                      kTileRows, static_cast<uint32_t>(BT));
+    constexpr int kSteps = kStageKBytes / 32;                      // MMAs per stage and accumulator
+    int stage = 0, acc = 0;
+    uint32_t phase = 0, acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < c.total; tile += c.grid_eff) {
+      const TileCoord t = decode_tile(tile, c, s_blk_off, a.E, BT, a.num_nt, a.kblocks);
+      if (!mbar_wait(smem_u32(&bar_tempty[acc]), acc_phase ^ 1, abort_flag, DEV_TIMEOUT_MMA)) break;
+      tc_fence_after();
+      const uint32_t d0 = tmem_base + static_cast<uint32_t>(acc * cols_per_acc);
+      for (int kb = t.kb0; kb < t.kb1; ++kb) {
+        if (!mbar_wait(smem_u32(&bar_full[stage]), phase, abort_flag, DEV_TIMEOUT_MMA)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + static_cast<size_t>(stage) * stage_bytes);
+        const uint64_t da = smem_desc_k_sw128(sa);
+        const uint64_t db = smem_desc_k_sw128(sa + A_BYTES);
+#pragma unroll
+        for (int k = 0; k < kSteps; ++k) {
+          const uint32_t accum = (kb > t.kb0 || k > 0) ? 1u : 0u;
+          // advancing 32 bytes inside the 128-byte swizzle atom = +2 in 16-byte units
+          tc_mma_f16(d0, da + 2 * k, db + 2 * k, idesc, accum);
+          if (MODE == 0) {
+            const uint64_t du = smem_desc_k_sw128(sa + kTileBytes);
+            tc_mma_f16(d0 + static_cast<uint32_t>(BT), du + 2 * k, db + 2 * k, idesc, accum);
+          }
+        }
+        tc_commit(smem_u32(&bar_empty[stage]));
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (!ok) break;
+      tc_commit(smem_u32(&bar_tfull[acc]));
+      if (++acc == a.acc_stages) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  } else if (active && warp >= 2) {
+    // =============================== epilogue ===================================
+    const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
+    const int ep_tid = (warp - 2) * 32 + lane; // 0..127
+    const int lrow = quad * 32 + lane;         // accumulator row = weight row inside the tile
+    const bool w_on_input = (a.flags & B200MOE_FLAG_WEIGHT_ON_INPUT) != 0;
+    const bool mimic = (a.flags & B200MOE_FLAG_MIMIC_ROUNDING) != 0;
+    int acc = 0, iter = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < c.total; tile += c.grid_eff, ++iter) {
+      const TileCoord t = decode_tile(tile, c, s_blk_off, a.E, BT, a.num_nt, a.kblocks);
+      const int buf = iter & 1;
+      int* col_row = s_col_row + buf * kMaxBT;
+      float* col_gam = s_col_gam + buf * kMaxBT;
+      for (int cidx = ep_tid; cidx < BT; cidx += 128) {
+        const int slot = a.sorted_ids[t.row0 + cidx];
+        const bool valid = slot >= 0 && slot < a.P;
+        col_row[cidx] = valid ? (MODE == 1 ? slot / a.topk : slot) : -1;
+        col_gam[cidx] = valid ? a.row_gamma[t.row0 + cidx] : 0.f;
+      }
+      named_bar_sync(1, 128);
+      if (!mbar_wait(smem_u32(&bar_tfull[acc]), acc_phase, abort_flag, DEV_TIMEOUT_EPILOGUE)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
+                             static_cast<uint32_t>(acc * cols_per_acc);
+      const int n = t.n0 + lrow;
+      const bool n_ok = n < a.N;
+      if (MODE == 0) {
+        T* out = reinterpret_cast<T*>(a.out);
+        for (int c0 = 0; c0 < BT; c0 += 16) {
+          float g[16], u[16];
+          tmem_ld16x2_wait(taddr + c0, taddr + BT + c0, g, u);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float gv = g[j], uv = u[j];
+            if (w_on_input) {
+              const float gam = col_gam[c0 + j];
+              gv *= gam;
+              uv *= gam;
+            }
+            if (mimic) {
+              gv = to_f32<T>(from_f32<T>(gv));
+              uv = to_f32<T>(from_f32<T>(uv));
+            }
+            const float av = (a.activation == B200MOE_ACT_SILU ? silu_f32(gv) : gelu_f32(gv)) * uv;
+            if (n_ok) out[static_cast<size_t>(t.row0 + c0 + j) * a.ld_out + n] = from_f32<T>(av);
+          }
+        }
+      } else {
+        float* out = reinterpret_cast<float*>(a.out);
+        const bool round_pair = mimic && c.split == 1;
+        for (int c0 = 0; c0 < BT; c0 += 16) {
+          float v[16];
+          tmem_ld16_wait(taddr + c0, v);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int orow = col_row[c0 + j];
+            if (orow >= 0 && n_ok) {
+              float y = v[j];
+              if (!w_on_input) y *= col_gam[c0 + j];
+              if (round_pair) y = to_f32<T>(from_f32<T>(y));
+              atomicAdd(out + static_cast<size_t>(orow) * a.ld_out + n, y);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[acc]));
+      if (++acc == a.acc_stages) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  // ---- teardown (every thread, aborted or not)
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, static_cast<uint32_t>(a.tmem_cols));
+  }
+  if (threadIdx.x == 0 && *abort_flag != 0) atomicCAS(a.status, 0, *abort_flag);
+}
+
+}  // namespace
+
+void gemm_plan(GemmArgs* a) {
+  const int kelems = (a->wmode == B200MOE_W_FP8_BLOCK) ? 128 : 64;
+  a->num_nt = (a->N + kTileRows - 1) / kTileRows;
+  a->kblocks = (a->K + kelems - 1) / kelems;
+  const int cols = (a->mode == 0 ? 2 : 1) * a->BT;
+  a->acc_stages = (2 * cols <= 512) ? 2 : 1;
+  int need = a->acc_stages * cols;
+  int tc = 32;
+  while (tc < need) tc <<= 1;
+  a->tmem_cols = tc;
+  const size_t stage_bytes = static_cast<size_t>(a->mode == 0 ? 2 : 1) * kTileBytes +
+                             static_cast<size_t>(a->BT) * kStageKBytes;
+  const size_t ctrl = 1024 /*alignment slack*/ + 512 /*barriers*/ + 2 * kMaxBT * 8 +
+                      static_cast<size_t>(a->E + 1) * 4 + 64;
+  int st = static_cast<int>((kSmemLimit - ctrl) / stage_bytes);
+  if (st > 10) st = 10;
+  if (st < 2) st = 2;
+  a->stages = st;
+  if (a->max_split <= 0) a->max_split = 16;
+}
+
+size_t gemm_smem_bytes(const GemmArgs& a) {
+  const size_t stage_bytes = static_cast<size_t>(a.mode == 0 ? 2 : 1) * kTileBytes +
+                             static_cast<size_t>(a.BT) * kStageKBytes;
+  return 1024 + static_cast<size_t>(a.stages) * stage_bytes + 512 + 2 * kMaxBT * 8 +
+         static_cast<size_t>(a.E + 1) * 4 + 64;
+}
+
+template <int MODE, typename T>
+static int launch_one(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmArgs& a, int num_sms,
+                      cudaStream_t stream) {
+  const size_t smem = gemm_smem_bytes(a);
+  if (smem > kSmemLimit) return B200MOE_ERR_TOO_LARGE;
+  cudaError_t err = cudaFuncSetAttribute(moe_gemm_tc_kernel<MODE, T>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+  if (err != cudaSuccess) return B200MOE_ERR_CUDA;
+  moe_gemm_tc_kernel<MODE, T><<<num_sms, kThreads, smem, stream>>>(tm_w, tm_x, a);
+  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
+}
+
+int launch_gemm_tc(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmArgs& a, int num_sms,
+                   cudaStream_t stream) {
+  if (a.BT < 16 || a.BT > kMaxBT || a.BT % 16 != 0) return B200MOE_ERR_BAD_ARG;
+  if (a.wmode != B200MOE_W_16BIT) return B200MOE_ERR_UNSUPPORTED;
+  if (a.dtype == B200MOE_DTYPE_BF16) {
+    return a.mode == 0 ? launch_one<0, __nv_bfloat16>(tm_w, tm_x, a, num_sms, stream)
+                       : launch_one<1, __nv_bfloat16>(tm_w, tm_x, a, num_sms, stream);
+  }
+  return a.mode == 0 ? launch_one<0, __half>(tm_w, tm_x, a, num_sms, stream)
+                     : launch_one<1, __half>(tm_w, tm_x, a, num_sms, stream);
+}
+
+}  // namespace b200moe

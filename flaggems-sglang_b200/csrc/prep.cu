@@ -1,0 +1,151 @@
+// Row movers around the grouped GEMMs: gather token rows into expert-sorted,
+// block-padded order (optionally quantising them to FP8 per 1x128 group),
+// and turn the fp32 combine buffer into the 16-bit output.
+#include "prep.cuh"
+
+namespace b200moe {
+
+namespace {
+
+// One warp per padded row; 16-byte chunks.  Rows beyond meta[1] are left alone,
+// padding rows are zero-filled.
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const uint4* __restrict__ x, uint4* __restrict__ xs, const int* __restrict__ sorted_ids,
+                   const int* __restrict__ meta, int P, int topk, int chunks_per_row, int cap) {
+  const int warps_per_cta = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int rows = min(meta[1], cap);
+  for (int r = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); r < rows; r += gridDim.x * warps_per_cta) {
+    const int slot = sorted_ids[r];
+    uint4* dst = xs + static_cast<size_t>(r) * chunks_per_row;
+    if (slot < 0 || slot >= P) {
+      for (int c = lane; c < chunks_per_row; c += 32) dst[c] = make_uint4(0, 0, 0, 0);
+    } else {
+      const uint4* src = x + static_cast<size_t>(slot / topk) * chunks_per_row;
+      for (int c = lane; c < chunks_per_row; c += 32) dst[c] = __ldg(src + c);
+    }
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void load4(const T* p, float (&v)[4]);
+template <>
+__device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[4]) {
+  uint2 raw = *reinterpret_cast<const uint2*>(p);
+  __nv_bfloat162 a = *reinterpret_cast<__nv_bfloat162*>(&raw.x);
+  __nv_bfloat162 b = *reinterpret_cast<__nv_bfloat162*>(&raw.y);
+  v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+}
+template <>
+__device__ __forceinline__ void load4<__half>(const __half* p, float (&v)[4]) {
+  uint2 raw = *reinterpret_cast<const uint2*>(p);
+  __half2 a = *reinterpret_cast<__half2*>(&raw.x);
+  __half2 b = *reinterpret_cast<__half2*>(&raw.y);
+  v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+}
+
+// One warp per (row, 128-wide group): amax by shuffles, scale = max(amax, eps)/448,
+// q = rne_satfinite(x / scale) with an IEEE divide so that the bits match a CPU
+// restatement.  sorted_ids == nullptr: rows map to themselves.
+// scale_t != 0: scales stored [K/128][ld_scale] (group-major) instead of [rows][K/128].
+template <typename T>
+__global__ void __launch_bounds__(256)
+group_quant_fp8_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scales,
+                       const int* __restrict__ sorted_ids, const int* __restrict__ meta, int P, int topk,
+                       int n_rows_static, int K, int scale_t, int ld_scale) {
+  const int groups = K >> 7;
+  const int lane = threadIdx.x & 31;
+  const int rows = (meta != nullptr) ? min(meta[1], n_rows_static) : n_rows_static;
+  const long long total = static_cast<long long>(rows) * groups;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  for (long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; w < total;
+       w += warps) {
+    const int r = static_cast<int>(w / groups), g = static_cast<int>(w - static_cast<long long>(r) * groups);
+    int src_row = r;
+    bool pad = false;
+    if (sorted_ids != nullptr) {
+      int slot = sorted_ids[r];
+      pad = (slot < 0 || slot >= P);
+      src_row = pad ? 0 : slot / topk;
+    }
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (!pad) load4<T>(x + static_cast<size_t>(src_row) * K + g * 128 + lane * 4, v);
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+    const float s = __fdiv_rn(fmaxf(amax, 1e-10f), 448.0f);
+    uint32_t packed = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_fp8_storage_t b = __nv_cvt_float_to_fp8(__fdiv_rn(v[i], s), __NV_SATFINITE, __NV_E4M3);
+      packed |= static_cast<uint32_t>(b) << (8 * i);
+    }
+    *reinterpret_cast<uint32_t*>(q + static_cast<size_t>(r) * K + g * 128 + lane * 4) = packed;
+    if (lane == 0) {
+      if (scale_t) scales[static_cast<size_t>(g) * ld_scale + r] = s;
+      else scales[static_cast<size_t>(r) * groups + g] = s;
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+finalize_kernel(const float4* __restrict__ acc, T* __restrict__ out, size_t n4, float scale) {
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    float4 v = acc[i];
+    T o[4] = {from_f32<T>(v.x * scale), from_f32<T>(v.y * scale), from_f32<T>(v.z * scale),
+              from_f32<T>(v.w * scale)};
+    *reinterpret_cast<uint2*>(out + i * 4) = *reinterpret_cast<uint2*>(o);
+  }
+}
+
+}  // namespace
+
+int launch_gather_rows(const void* x, void* xs, const int* sorted_ids, const int* meta, int P, int topk,
+                       int row_bytes, int cap, int num_sms, cudaStream_t stream) {
+  if (row_bytes % 16 != 0) return B200MOE_ERR_UNSUPPORTED;
+  int ctas = (cap + 7) / 8;
+  if (ctas > num_sms * 8) ctas = num_sms * 8;
+  if (ctas < 1) ctas = 1;
+  gather_rows_kernel<<<ctas, 256, 0, stream>>>(reinterpret_cast<const uint4*>(x), reinterpret_cast<uint4*>(xs),
+                                              sorted_ids, meta, P, topk, row_bytes / 16, cap);
+  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
+}
+
+int launch_group_quant_fp8(const void* x, int dtype, void* q, float* scales, const int* sorted_ids,
+                           const int* meta, int P, int topk, int rows, int K, int scale_t, int ld_scale,
+                           int num_sms, cudaStream_t stream) {
+  if (K % 128 != 0) return B200MOE_ERR_UNSUPPORTED;
+  long long warps = static_cast<long long>(rows) * (K / 128);
+  long long ctas = (warps + 7) / 8;
+  if (ctas > num_sms * 16) ctas = num_sms * 16;
+  if (ctas < 1) ctas = 1;
+  if (dtype == B200MOE_DTYPE_BF16)
+    group_quant_fp8_kernel<__nv_bfloat16><<<static_cast<int>(ctas), 256, 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<uint8_t*>(q), scales, sorted_ids, meta,
+        P, topk, rows, K, scale_t, ld_scale);
+  else
+    group_quant_fp8_kernel<__half><<<static_cast<int>(ctas), 256, 0, stream>>>(
+        reinterpret_cast<const __half*>(x), reinterpret_cast<uint8_t*>(q), scales, sorted_ids, meta, P, topk,
+        rows, K, scale_t, ld_scale);
+  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
+}
+
+int launch_finalize(const float* acc, void* out, int dtype, size_t n, float scale, int num_sms,
+                    cudaStream_t stream) {
+  if (n % 4 != 0) return B200MOE_ERR_UNSUPPORTED;
+  size_t n4 = n / 4;
+  size_t ctas = (n4 + 255) / 256;
+  if (ctas > static_cast<size_t>(num_sms) * 8) ctas = static_cast<size_t>(num_sms) * 8;
+  if (ctas < 1) ctas = 1;
+  if (dtype == B200MOE_DTYPE_BF16)
+    finalize_kernel<__nv_bfloat16><<<static_cast<int>(ctas), 256, 0, stream>>>(
+        reinterpret_cast<const float4*>(acc), reinterpret_cast<__nv_bfloat16*>(out), n4, scale);
+  else
+    finalize_kernel<__half><<<static_cast<int>(ctas), 256, 0, stream>>>(
+        reinterpret_cast<const float4*>(acc), reinterpret_cast<__half*>(out), n4, scale);
+  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
+}
+
+}  // namespace b200moe

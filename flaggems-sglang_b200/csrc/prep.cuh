@@ -1,0 +1,21 @@
+// Host-callable launchers of the row movers around the grouped GEMMs.
+#pragma once
+#include "common.cuh"
+
+namespace b200moe {
+
+// xs[r] = x[sorted_ids[r] / topk] for r < meta[1]; padding rows zero-filled.
+int launch_gather_rows(const void* x, void* xs, const int* sorted_ids, const int* meta, int P, int topk,
+                       int row_bytes, int cap, int num_sms, cudaStream_t stream);
+
+// Per-token-group (1x128) FP8 quantisation, optionally gathering rows through
+// sorted_ids like launch_gather_rows.  scale_t: store scales group-major.
+int launch_group_quant_fp8(const void* x, int dtype, void* q, float* scales, const int* sorted_ids,
+                           const int* meta, int P, int topk, int rows, int K, int scale_t, int ld_scale,
+                           int num_sms, cudaStream_t stream);
+
+// out[i] = cast(acc[i] * scale)
+int launch_finalize(const float* acc, void* out, int dtype, size_t n, float scale, int num_sms,
+                    cudaStream_t stream);
+
+}  // namespace b200moe

@@ -1,0 +1,98 @@
+"""ctypes binding of libb200moe.so (the C ABI declared in include/b200moe.h)."""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+from ._build import LIB_PATH
+
+VERSION = 1
+
+OK = 0
+ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_TOO_LARGE = -1, -2, -3, -4, -5, -6
+
+DTYPE_BF16, DTYPE_FP16 = 0, 1
+W_16BIT, W_FP8_BLOCK, W_INT4_AWQ = 0, 1, 2
+LAYOUT_LAYER, LAYOUT_OP = 0, 1
+ACT_SILU, ACT_GELU = 0, 1
+FLAG_WEIGHT_ON_INPUT, FLAG_MIMIC_ROUNDING, FLAG_SIMT, FLAG_IDS_I64, FLAG_NO_SPLIT_K = 1, 2, 4, 8, 16
+
+
+class Cfg(C.Structure):
+    _fields_ = [
+        ("struct_bytes", C.c_int32), ("M", C.c_int32), ("H", C.c_int32), ("I", C.c_int32),
+        ("E", C.c_int32), ("topk", C.c_int32), ("dtype", C.c_int32), ("wmode", C.c_int32),
+        ("w_layout", C.c_int32), ("activation", C.c_int32), ("flags", C.c_int32),
+        ("block_tokens", C.c_int32), ("routed_scaling", C.c_float), ("num_sms", C.c_int32),
+    ]
+
+
+class Quant(C.Structure):
+    _fields_ = [("w1_scale", C.c_void_p), ("w2_scale", C.c_void_p), ("w1_sz", C.c_void_p), ("w2_sz", C.c_void_p)]
+
+
+# name -> (restype, argtypes); every symbol include/b200moe.h declares
+SYMBOLS = {
+    "b200moe_version": (C.c_int, []),
+    "b200moe_status_string": (C.c_char_p, [C.c_int]),
+    "b200moe_pick_block_tokens": (C.c_int, [C.POINTER(Cfg)]),
+    "b200moe_workspace_bytes": (C.c_size_t, [C.POINTER(Cfg)]),
+    "b200moe_align_capacity": (C.c_int, [C.c_int, C.c_int, C.c_int]),
+    "b200moe_align_block_size": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
+                                           C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b200moe_routing_max_tiles": (C.c_int, [C.c_int, C.c_int]),
+    "b200moe_routing_from_topk": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                            C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                            C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b200moe_forward_topk": (C.c_int, [C.POINTER(Cfg), C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(Quant),
+                                       C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
+                                       C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b200moe_forward_routed": (C.c_int, [C.POINTER(Cfg), C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(Quant),
+                                         C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
+                                         C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b200moe_profile_begin": (C.c_int, [C.c_int]),
+    "b200moe_profile_end": (C.c_int, [C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double),
+                                      C.POINTER(C.c_int)]),
+    "b200moe_per_token_group_quant_fp8": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p,
+                                                    C.c_void_p, C.c_void_p]),
+}
+
+_lib = None
+
+
+class ExtensionMissing(RuntimeError):
+    pass
+
+
+def lib() -> C.CDLL:
+    """Load the shared object; there is no fallback when it is missing."""
+    global _lib
+    if _lib is None:
+        path = Path(LIB_PATH)
+        if not path.exists():
+            raise ExtensionMissing(
+                f"{path} is not built. Run `python -c 'import __graft_entry__ as g; g.build()'` "
+                "(or `python -m flaggems_sglang_b200._build`) first; this package has no CPU or "
+                "PyTorch fallback for the fused-MoE path.")
+        handle = C.CDLL(str(path))
+        for name, (res, args) in SYMBOLS.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        if handle.b200moe_version() != VERSION:
+            raise ExtensionMissing(f"{path} has ABI version {handle.b200moe_version()}, expected {VERSION}")
+        _lib = handle
+    return _lib
+
+
+def status_string(code: int) -> str:
+    return lib().b200moe_status_string(code).decode()
+
+
+def check(code: int, what: str) -> None:
+    if code == OK:
+        return
+    msg = f"{what}: {status_string(code)} ({code})"
+    if code in (ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_TOO_LARGE):
+        raise ValueError(msg)
+    raise RuntimeError(msg)

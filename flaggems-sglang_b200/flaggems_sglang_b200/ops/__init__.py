@@ -1,0 +1,18 @@
+from .fused_moe import (
+    check_status,
+    fused_experts,
+    fused_moe_flagos,
+    triton_kernel_fused_experts,
+    triton_kernel_fused_experts_with_bias,
+)
+from ..routing import moe_align_block_size, topk_to_routing
+
+__all__ = [
+    "check_status",
+    "fused_experts",
+    "fused_moe_flagos",
+    "triton_kernel_fused_experts",
+    "triton_kernel_fused_experts_with_bias",
+    "moe_align_block_size",
+    "topk_to_routing",
+]

@@ -1,0 +1,331 @@
+"""Fused Mixture-of-Experts operator for B200 (sm_100a).
+
+Drop-in for the fused-MoE entry points of ``flaggems_sglang.ops``
+(src/flaggems_sglang/ops/fused_moe.py in the reference tree): the same names,
+positional order, defaults and exception types, implemented by a C-ABI CUDA
+library instead of Triton.  Python here only validates, allocates and launches.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import logging
+import os
+import weakref
+from types import SimpleNamespace
+from typing import Optional
+
+import torch
+
+from .. import _lib
+from ..routing import topk_to_routing
+
+logger = logging.getLogger(__name__)
+
+_UNSUPPORTED_FEATURE_MSG = "{name} is not supported"
+
+_DTYPES = {torch.bfloat16: _lib.DTYPE_BF16, torch.float16: _lib.DTYPE_FP16}
+_ACTS = {"silu": _lib.ACT_SILU, "gelu": _lib.ACT_GELU}
+
+# ---------------------------------------------------------------------------- state
+_workspaces: dict = {}     # (device index, stream handle) -> uint8 tensor
+_status: dict = {}         # device index -> int32[1]
+_relayout: "weakref.WeakKeyDictionary" = weakref.WeakKeyDictionary()
+
+
+def _workspace(dev: torch.device, nbytes: int) -> torch.Tensor:
+    key = (dev.index, torch.cuda.current_stream(dev).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(int(nbytes * 1.25) + 4096, dtype=torch.uint8, device=dev)
+        _workspaces[key] = ws
+    return ws
+
+
+def _status_word(dev: torch.device) -> torch.Tensor:
+    st = _status.get(dev.index)
+    if st is None:
+        st = torch.zeros(1, dtype=torch.int32, device=dev)
+        _status[dev.index] = st
+    return st
+
+
+def check_status(device=None) -> None:
+    """Synchronise and raise if a kernel reported a device-side time-out since
+    the last check.  Never called on the hot path."""
+    devs = list(_status) if device is None else [torch.device(device).index or 0]
+    for idx in devs:
+        st = _status.get(idx)
+        if st is None:
+            continue
+        code = int(st.item())
+        if code != 0:
+            st.zero_()
+            raise RuntimeError(f"b200moe: device-side wait timed out (code {code}) on cuda:{idx}")
+
+
+def _layer_layout(w: torch.Tensor) -> torch.Tensor:
+    """Op-level weights are [E, K, N] (reference layout, output dim contiguous);
+    the kernels stream [E, N, K].  A transposed view of a [E, N, K] tensor is used
+    as is; anything else is re-laid out once and remembered per tensor object."""
+    wt = w.transpose(-1, -2)
+    if wt.is_contiguous():
+        return wt
+    ent = _relayout.get(w)
+    if ent is None or ent[0] != w._version or ent[1] != w.data_ptr():
+        ent = (w._version, w.data_ptr(), wt.contiguous())
+        _relayout[w] = ent
+    return ent[2]
+
+
+def _make_cfg(m, h, i, e, k, dtype, wmode, activation, flags, block_tokens, routed_scaling) -> _lib.Cfg:
+    return _lib.Cfg(C.sizeof(_lib.Cfg), m, h, i, e, k, dtype, wmode, _lib.LAYOUT_LAYER, activation, flags,
+                    block_tokens, routed_scaling, 0)
+
+
+def _env_flags() -> int:
+    f = 0
+    if os.environ.get("B200MOE_SIMT", "0") == "1":
+        f |= _lib.FLAG_SIMT
+    if os.environ.get("B200MOE_NO_SPLIT_K", "0") == "1":
+        f |= _lib.FLAG_NO_SPLIT_K
+    return f
+
+
+def _block_tokens_env() -> int:
+    return int(os.environ.get("B200MOE_BLOCK_TOKENS", "0"))
+
+
+# ---------------------------------------------------------------------------- layer-layout core
+def fused_experts(
+    hidden_states: torch.Tensor,
+    w13: torch.Tensor,
+    w2: torch.Tensor,
+    topk_weights: Optional[torch.Tensor] = None,
+    topk_ids: Optional[torch.Tensor] = None,
+    *,
+    routing=None,
+    activation: str = "silu",
+    apply_router_weight_on_input: bool = False,
+    expert_map: Optional[torch.Tensor] = None,
+    routed_scaling_factor: float = 1.0,
+    mimic_reference_rounding: bool = True,
+    block_tokens: int = 0,
+    use_fp8_w8a8: bool = False,
+    w13_scale: Optional[torch.Tensor] = None,
+    w2_scale: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Fused experts on layer-layout weights ``w13 [E, 2I, H]``, ``w2 [E, H, I]``.
+
+    Routing is either ``(topk_weights [M, k], topk_ids [M, k])`` or
+    ``routing=(hist [E], topk_indx [P], gate_scal [P])`` taken from the
+    reference's routing triple.  Returns a new ``[M, H]`` tensor.
+    """
+    if activation not in _ACTS:
+        raise ValueError(f"Unsupported FusedMoe activation: {activation}")
+    if not hidden_states.is_cuda:
+        raise RuntimeError("hidden_states must be a CUDA tensor: this package has no CPU path")
+    x = hidden_states.contiguous()
+    dev = x.device
+    m, h = x.shape
+    e, two_i, hw = w13.shape
+    i = two_i // 2
+    assert hw == h, "hidden size mismatch"
+    assert w2.shape[0] == e and w2.shape[1] == h and w2.shape[2] == i, "intermediate size mismatch"
+    assert w13.is_contiguous() and w2.is_contiguous(), "weights must be contiguous"
+    dtype = _DTYPES[x.dtype]
+
+    flags = _env_flags()
+    if apply_router_weight_on_input:
+        flags |= _lib.FLAG_WEIGHT_ON_INPUT
+    if mimic_reference_rounding:
+        flags |= _lib.FLAG_MIMIC_ROUNDING
+
+    quant = None
+    wmode = _lib.W_16BIT
+    if use_fp8_w8a8:
+        wmode = _lib.W_FP8_BLOCK
+        assert w13.dtype == torch.float8_e4m3fn and w2.dtype == torch.float8_e4m3fn, "FP8 weights must be float8_e4m3fn"
+        assert w13_scale is not None and w2_scale is not None, "block scales are required"
+        s1 = w13_scale.to(torch.float32).contiguous()
+        s2 = w2_scale.to(torch.float32).contiguous()
+        quant = _lib.Quant(s1.data_ptr(), s2.data_ptr(), None, None)
+    else:
+        assert w13.dtype == x.dtype and w2.dtype == x.dtype, "weights must have the activation dtype"
+
+    lib = _lib.lib()
+    if routing is None:
+        assert topk_weights is not None and topk_ids is not None, "routing or (topk_weights, topk_ids) required"
+        k = topk_ids.shape[1]
+        ids = topk_ids.contiguous()
+        assert ids.dtype in (torch.int32, torch.int64), "topk_ids must be int32 or int64"
+        if ids.dtype == torch.int64:
+            flags |= _lib.FLAG_IDS_I64
+        tw = topk_weights.to(torch.float32).contiguous()
+    else:
+        hist, topk_indx, gate_scal, k = routing
+        hist = hist.to(torch.int32).contiguous()
+        topk_indx = topk_indx.to(torch.int32).contiguous()
+        gate_scal = gate_scal.to(torch.float32).contiguous()
+
+    cfg = _make_cfg(m, h, i, e, k, dtype, wmode, _ACTS[activation], flags,
+                    block_tokens or _block_tokens_env(), float(routed_scaling_factor))
+    out = torch.empty((m, h), dtype=x.dtype, device=dev)
+    if m == 0:
+        return out
+    nbytes = lib.b200moe_workspace_bytes(C.byref(cfg))
+    if nbytes == 0:
+        rc = lib.b200moe_pick_block_tokens(C.byref(cfg))
+        _lib.check(rc if rc < 0 else _lib.ERR_UNSUPPORTED, "fused_experts")
+    ws = _workspace(dev, nbytes)
+    base = (ws.data_ptr() + 255) & ~255
+    avail = ws.numel() - (base - ws.data_ptr())
+    status = _status_word(dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    qref = C.byref(quant) if quant is not None else None
+    with torch.cuda.device(dev):
+        if routing is None:
+            emap = None
+            if expert_map is not None:
+                emap = expert_map.to(device=dev, dtype=torch.int32).contiguous()
+            rc = lib.b200moe_forward_topk(
+                C.byref(cfg), x.data_ptr(), w13.data_ptr(), w2.data_ptr(), qref, tw.data_ptr(), ids.data_ptr(),
+                emap.data_ptr() if emap is not None else None, base, avail, out.data_ptr(),
+                status.data_ptr(), stream)
+        else:
+            rc = lib.b200moe_forward_routed(
+                C.byref(cfg), x.data_ptr(), w13.data_ptr(), w2.data_ptr(), qref, hist.data_ptr(),
+                topk_indx.data_ptr(), gate_scal.data_ptr(), base, avail, out.data_ptr(),
+                status.data_ptr(), stream)
+    _lib.check(rc, "fused_experts")
+    if os.environ.get("B200MOE_CHECK_STATUS", "0") == "1":
+        check_status(dev)
+    return out
+
+
+# ---------------------------------------------------------------------------- reference-compatible entry points
+def triton_kernel_fused_experts(
+    hidden_states: torch.Tensor,
+    w1: torch.Tensor,
+    w2: torch.Tensor,
+    routing_data,
+    gather_indx,
+    scatter_indx,
+    inplace: bool = False,
+    activation: str = "silu",
+    apply_router_weight_on_input: bool = False,
+    use_fp8_w8a8: bool = False,
+    per_channel_quant: bool = False,
+    global_num_experts: int = -1,
+    expert_map: Optional[torch.Tensor] = None,
+    w1_scale: Optional[torch.Tensor] = None,
+    w2_scale: Optional[torch.Tensor] = None,
+    a1_scale: Optional[torch.Tensor] = None,
+    a2_scale: Optional[torch.Tensor] = None,
+    block_shape: Optional[list[int]] = None,
+) -> torch.Tensor:
+    """Same signature and results as the reference's op
+    (src/flaggems_sglang/ops/fused_moe.py:133-216): ``w1 [E, H, 2I]``,
+    ``w2 [E, I, H]``, routing as the dependency's triple (read by attribute).
+
+    Beyond the reference: ``use_fp8_w8a8=True`` with ``w1_scale``/``w2_scale``
+    and ``block_shape=[128, 128]`` runs the block-quantised FP8 path (weights
+    then come in layer layout ``[E, 2I, H]`` / ``[E, H, I]``).
+    """
+    logger.debug("FLAGGEMS_SGLANG FUSED_MOE")
+    assert per_channel_quant is False, _UNSUPPORTED_FEATURE_MSG.format(name="per_channel_quant")
+    assert expert_map is None, _UNSUPPORTED_FEATURE_MSG.format(name="expert_map")
+    assert a1_scale is None, _UNSUPPORTED_FEATURE_MSG.format(name="a1_scale")
+    assert a2_scale is None, _UNSUPPORTED_FEATURE_MSG.format(name="a2_scale")
+    assert inplace is False, "Inplace is not supported"
+    assert hidden_states.ndim == 2, "hidden_states must be 2D"
+    if activation not in _ACTS:
+        raise ValueError(f"Unsupported FusedMoe activation: {activation}")
+
+    top_k = routing_data.n_expts_act
+    routing = (routing_data.expt_hist, gather_indx.src_indx, routing_data.gate_scal, top_k)
+
+    if use_fp8_w8a8:
+        assert block_shape is not None and list(block_shape) == [128, 128], "block_shape must be [128, 128]"
+        assert w1_scale is not None and w2_scale is not None, "w1_scale and w2_scale are required"
+        return fused_experts(hidden_states, w1, w2, routing=routing, activation=activation,
+                             apply_router_weight_on_input=apply_router_weight_on_input,
+                             use_fp8_w8a8=True, w13_scale=w1_scale, w2_scale=w2_scale)
+
+    assert w1_scale is None, _UNSUPPORTED_FEATURE_MSG.format(name="w1_scale")
+    assert w2_scale is None, _UNSUPPORTED_FEATURE_MSG.format(name="w2_scale")
+    assert block_shape is None, _UNSUPPORTED_FEATURE_MSG.format(name="block_shape")
+    assert hidden_states.dtype == torch.bfloat16, "hidden_states must be bfloat16"
+    assert w1.dtype == torch.bfloat16, "w1 must be bfloat16"
+    assert w2.dtype == torch.bfloat16, "w2 must be bfloat16"
+    assert hidden_states.shape[-1] == w1.shape[-2], "hidden size mismatch"
+    assert w2.shape[-1] == w1.shape[1], "intermediate size mismatch"
+
+    out = fused_experts(hidden_states, _layer_layout(w1), _layer_layout(w2), routing=routing,
+                        activation=activation, apply_router_weight_on_input=apply_router_weight_on_input)
+    return out.view(hidden_states.shape[0], hidden_states.shape[1])
+
+
+def triton_kernel_fused_experts_with_bias(
+    hidden_states: torch.Tensor,
+    w1: torch.Tensor,
+    w1_pcg,
+    b1: torch.Tensor,
+    w2: torch.Tensor,
+    w2_pcg,
+    b2: torch.Tensor,
+    routing_data,
+    gather_indx,
+    scatter_indx,
+    inplace: bool = False,
+    activation: str = "silu",
+    apply_router_weight_on_input: bool = False,
+    global_num_experts: int = -1,
+    gemm1_alpha: Optional[float] = None,
+    gemm1_clamp_limit: Optional[float] = None,
+) -> torch.Tensor:
+    """Signature of the reference's bias variant
+    (src/flaggems_sglang/ops/fused_moe.py:219-309).  Not built yet: the variant
+    is untested upstream and sits outside the measured path."""
+    logger.debug("FLAGGEMS_SGLANG FUSED_MOE_WITH_BIAS")
+    assert inplace is False, "Inplace is not supported"
+    assert hidden_states.dtype == torch.bfloat16, "hidden_states must be bfloat16"
+    if activation != "silu":
+        raise ValueError(f"Unsupported FusedMoe activation: {activation}")
+    raise NotImplementedError("per-expert bias / interleaved swiglu variant is not implemented")
+
+
+def fused_moe_flagos(obj, layer: torch.nn.Module, dispatch_output):
+    """SGLang plugin hook (src/flaggems_sglang/ops/fused_moe.py:312-406).
+
+    ``layer.w13_weight [E, 2I, H]`` and ``layer.w2_weight [E, H, I]`` are used
+    where they lie (the reference transposes and copies both on every call), the
+    top-k output goes straight to the device-side alignment, and the routed
+    scaling factor is folded into the output conversion.
+    """
+    cfg = obj.runner.config
+    hidden_states = dispatch_output.hidden_states
+    topk_output = dispatch_output.topk_output
+    if getattr(cfg, "no_combine", False):
+        raise NotImplementedError("no_combine is not implemented")
+    if getattr(layer, "w13_weight_bias", None) is not None or getattr(layer, "w2_weight_bias", None) is not None:
+        raise NotImplementedError("per-expert bias is not implemented")
+    scale = getattr(cfg, "routed_scaling_factor", None)
+    scale = 1.0 if scale is None else float(scale)
+    common = dict(activation=cfg.activation,
+                  apply_router_weight_on_input=bool(getattr(cfg, "apply_router_weight_on_input", False)),
+                  routed_scaling_factor=scale)
+    if hasattr(topk_output, "topk_weights"):
+        out = fused_experts(hidden_states, layer.w13_weight, layer.w2_weight,
+                            topk_output.topk_weights, topk_output.topk_ids, **common)
+    else:
+        routing_data, gather_indx, _ = topk_output
+        routing = (routing_data.expt_hist, gather_indx.src_indx, routing_data.gate_scal, routing_data.n_expts_act)
+        out = fused_experts(hidden_states, layer.w13_weight, layer.w2_weight, routing=routing, **common)
+    try:
+        from sglang.srt.layers.moe.token_dispatcher.standard import StandardCombineInput
+        return StandardCombineInput(hidden_states=out)
+    except Exception:
+        return SimpleNamespace(hidden_states=out)
+
+
+_standard_topk_to_triton_kernels = topk_to_routing

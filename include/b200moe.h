@@ -1,0 +1,178 @@
+/*
+ * b200moe.h -- C ABI of the B200 (sm_100a) fused Mixture-of-Experts library.
+ *
+ * Every entry point takes plain device pointers, integers and a CUDA stream
+ * (passed as void* so that this header needs no CUDA include), launches
+ * asynchronously on that stream, allocates nothing and never synchronises.
+ * Return value: 0 on success, a negative B200MOE_ERR_* code otherwise.
+ * Device-side problems (a bounded wait that ran out) are reported through the
+ * caller-provided status word, which the caller reads after synchronising.
+ *
+ * Each declaration names the reference interface it stands in for, by the
+ * file's path inside the flagos-ai/FlagGems-sglang tree.
+ */
+#ifndef B200MOE_H_
+#define B200MOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200MOE_VERSION 1
+
+/* status codes */
+#define B200MOE_OK 0
+#define B200MOE_ERR_BAD_ARG (-1)
+#define B200MOE_ERR_UNSUPPORTED (-2)
+#define B200MOE_ERR_WORKSPACE (-3)
+#define B200MOE_ERR_CUDA (-4)
+#define B200MOE_ERR_DEVICE_TIMEOUT (-5)
+#define B200MOE_ERR_TOO_LARGE (-6)
+
+/* activation / output element type */
+#define B200MOE_DTYPE_BF16 0
+#define B200MOE_DTYPE_FP16 1
+
+/* weight storage */
+#define B200MOE_W_16BIT 0     /* same 16-bit type as the activations               */
+#define B200MOE_W_FP8_BLOCK 1 /* e4m3fn, fp32 scale per 128x128 block              */
+#define B200MOE_W_INT4_AWQ 2  /* uint4 g128, packed by b200moe_awq_repack           */
+
+/* weight layout (16-bit weights only) */
+#define B200MOE_LAYOUT_LAYER 0 /* w1 [E,2I,H], w2 [E,H,I]: reduction dim contiguous */
+#define B200MOE_LAYOUT_OP 1    /* w1 [E,H,2I], w2 [E,I,H]: output dim contiguous    */
+
+#define B200MOE_ACT_SILU 0
+#define B200MOE_ACT_GELU 1
+
+/* cfg.flags */
+#define B200MOE_FLAG_WEIGHT_ON_INPUT 1  /* router weight scales GEMM-1's output, not GEMM-2's */
+#define B200MOE_FLAG_MIMIC_ROUNDING 2   /* round y1 (and y2 when K is not split) to the 16-bit type */
+#define B200MOE_FLAG_SIMT 4             /* plain CUDA-core GEMMs (validation aid, slow)        */
+#define B200MOE_FLAG_IDS_I64 8          /* topk_ids are int64 instead of int32                 */
+#define B200MOE_FLAG_NO_SPLIT_K 16      /* keep GEMM-2's reduction in one piece                */
+
+typedef struct b200moe_cfg {
+  int32_t struct_bytes;   /* sizeof(b200moe_cfg), checked                      */
+  int32_t M;              /* tokens                                             */
+  int32_t H;              /* hidden size                                        */
+  int32_t I;              /* intermediate size (w1 has 2*I output rows)         */
+  int32_t E;              /* experts held locally                               */
+  int32_t topk;           /* experts per token                                  */
+  int32_t dtype;          /* B200MOE_DTYPE_*                                    */
+  int32_t wmode;          /* B200MOE_W_*                                        */
+  int32_t w_layout;       /* B200MOE_LAYOUT_*                                   */
+  int32_t activation;     /* B200MOE_ACT_*                                      */
+  int32_t flags;          /* B200MOE_FLAG_*                                     */
+  int32_t block_tokens;   /* token block of the GEMMs: 0 = choose, else 16..256 */
+  float routed_scaling;   /* output multiplier (1.0f for none)                  */
+  int32_t num_sms;        /* 0 = query the current device                       */
+} b200moe_cfg;
+
+/* scales / zero points for the quantised weight modes (NULL members unused) */
+typedef struct b200moe_quant {
+  const float *w1_scale;  /* FP8: [E, ceil(2I/128), ceil(H/128)]                 */
+  const float *w2_scale;  /* FP8: [E, ceil(H/128), ceil(I/128)]                  */
+  const void *w1_sz;      /* AWQ: repacked scale/zero table from b200moe_awq_repack */
+  const void *w2_sz;
+} b200moe_quant;
+
+int b200moe_version(void);
+const char *b200moe_status_string(int code);
+
+/* Token block the library would pick for this problem (16, 32, 64, 128 or 256). */
+int b200moe_pick_block_tokens(const b200moe_cfg *cfg);
+
+/* Bytes of scratch b200moe_forward_* needs for this problem (256-byte aligned base). */
+size_t b200moe_workspace_bytes(const b200moe_cfg *cfg);
+
+/*
+ * Block-aligned grouping of the flat slot ids i = token*topk + j by expert.
+ * Stands in for the alignment step the reference delegates to its dependency's
+ * routing tables (src/flaggems_sglang/ops/fused_moe.py:103-130); the output
+ * contract is the serving ecosystem's moe_align_block_size:
+ *   sorted_token_ids[cap]   expert 0's slots ascending, sentinel n_slots up to a
+ *                           multiple of `block`, expert 1's slots, ...; tail = n_slots
+ *   expert_ids[ceil(cap/block)]  expert of each block; tail = -1
+ *   num_tokens_post_padded[1]
+ * cap = b200moe_align_capacity(n_slots, n_experts, block).  expert_map (may be
+ * NULL) maps ids to local experts, negative = not local (slot dropped).
+ */
+int b200moe_align_capacity(int n_slots, int n_experts, int block);
+int b200moe_align_block_size(const void *topk_ids, int ids_are_i64, int n_slots,
+                             int n_experts, int block, const int32_t *expert_map,
+                             int32_t *sorted_token_ids, int32_t *expert_ids,
+                             int32_t *num_tokens_post_padded, void *stream);
+
+/*
+ * top-k -> routing tables.  Replaces _standard_topk_to_triton_kernels
+ * (src/flaggems_sglang/ops/fused_moe.py:103-130) and the expert-data tables it
+ * obtains from its dependency.  All outputs int32 unless noted:
+ *   expt_indx[P], topk_indx[P], gate_indx[P], gate_scal[P] (fp32), hist[E],
+ *   token_offs_raw[E+1], token_offs_pad[4][E+1], block_pid_map[4][max_tiles]
+ * for block sizes 16, 32, 64, 128; max_tiles = b200moe_routing_max_tiles(P, E).
+ */
+int b200moe_routing_max_tiles(int n_slots, int n_experts);
+int b200moe_routing_from_topk(const float *topk_weights, const void *topk_ids,
+                              int ids_are_i64, int n_tokens, int topk, int n_experts,
+                              int32_t *expt_indx, int32_t *topk_indx, int32_t *gate_indx,
+                              float *gate_scal, int32_t *hist, int32_t *token_offs_raw,
+                              int32_t *token_offs_pad, int32_t *block_pid_map,
+                              void *stream);
+
+/*
+ * Fused experts from top-k routing.  Replaces triton_kernel_fused_experts
+ * (src/flaggems_sglang/ops/fused_moe.py:133-216) preceded by the routing
+ * conversion of fused_moe_flagos (same file, 339-350).
+ *   x [M,H], out [M,H] of cfg.dtype; topk_weights [M,topk] fp32; topk_ids
+ *   [M,topk] int32 (int64 with B200MOE_FLAG_IDS_I64); expert_map may be NULL.
+ *   status: device int32, set non-zero if a device-side wait gave up.
+ */
+int b200moe_forward_topk(const b200moe_cfg *cfg, const void *x, const void *w1,
+                         const void *w2, const b200moe_quant *quant,
+                         const float *topk_weights, const void *topk_ids,
+                         const int32_t *expert_map, void *workspace,
+                         size_t workspace_bytes, void *out, int32_t *status,
+                         void *stream);
+
+/*
+ * Fused experts from the reference's routing triple.  Replaces
+ * triton_kernel_fused_experts (src/flaggems_sglang/ops/fused_moe.py:133-216)
+ * as the reference's tests call it (tests/test_fused_moe.py:94): hist[E] =
+ * routing_data.expt_hist, topk_indx[P] = gather_indx.src_indx, gate_scal[P]
+ * (fp32) = routing_data.gate_scal.
+ */
+int b200moe_forward_routed(const b200moe_cfg *cfg, const void *x, const void *w1,
+                           const void *w2, const b200moe_quant *quant,
+                           const int32_t *hist, const int32_t *topk_indx,
+                           const float *gate_scal, void *workspace,
+                           size_t workspace_bytes, void *out, int32_t *status,
+                           void *stream);
+
+/*
+ * Dynamic per-token-group FP8 quantisation (1 x 128 groups): the step in front
+ * of the FP8 path (shapes listed at benchmark/core_shapes.yaml:311-317).
+ * x [rows, K] of `dtype`; q [rows, K] e4m3fn; scales [rows, K/128] fp32.
+ */
+int b200moe_per_token_group_quant_fp8(const void *x, int dtype, int rows, int K,
+                                      void *q, float *scales, void *stream);
+
+/*
+ * Per-kernel timing for benchmarks (no counterpart in the reference, whose
+ * benchmark times the host side of an asynchronous launch,
+ * benchmark/test_fused_moe.py:39-59).  Between begin and end every forward call
+ * records CUDA events around its two grouped GEMMs on the caller's stream;
+ * end synchronises on them and returns the summed milliseconds and the number
+ * of calls seen.  begin creates the events (host objects), so neither belongs
+ * inside a timed or captured region.
+ */
+int b200moe_profile_begin(int max_calls);
+int b200moe_profile_end(double *gemm1_ms, double *gemm2_ms, double *total_ms, int *calls);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200MOE_H_ */

@@ -1,0 +1,87 @@
+"""CPU: the shared object loads, exports every symbol the header declares, and
+its host-only entry points agree with the oracle.  No kernel is launched."""
+import ctypes as C
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from oracle import routing as R
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _declared_symbols():
+    text = (ROOT / "include" / "b200moe.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(b200moe_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_exported(built_lib):
+    names = _declared_symbols()
+    assert len(names) >= 10
+    for n in names:
+        assert hasattr(built_lib, n), f"{n} declared in include/b200moe.h but not exported"
+
+
+def test_binding_covers_header(built_lib):
+    from flaggems_sglang_b200 import _lib
+    assert sorted(_lib.SYMBOLS) == _declared_symbols()
+    assert built_lib.b200moe_version() == _lib.VERSION
+    assert C.sizeof(_lib.Cfg) == 14 * 4
+
+
+@pytest.mark.parametrize("p,e,b", [(0, 8, 16), (2, 8, 16), (128, 8, 64), (8192, 8, 256), (2048, 128, 16),
+                                   (32768, 256, 128), (5, 3, 128)])
+def test_capacity_matches_oracle(built_lib, p, e, b):
+    assert built_lib.b200moe_align_capacity(p, e, b) == R.align_capacity(p, e, b)
+    assert built_lib.b200moe_routing_max_tiles(p, e) == R.max_tiles(p, e)
+
+
+def test_argument_errors(built_lib):
+    from flaggems_sglang_b200 import _lib
+    assert built_lib.b200moe_align_capacity(-1, 8, 16) == _lib.ERR_BAD_ARG
+    bad = _lib.Cfg(4, 1, 128, 128, 8, 2, 0, 0, 0, 0, 0, 0, 1.0, 0)
+    assert built_lib.b200moe_workspace_bytes(C.byref(bad)) == 0
+    assert built_lib.b200moe_pick_block_tokens(C.byref(bad)) == _lib.ERR_BAD_ARG
+    ok = _lib.Cfg(C.sizeof(_lib.Cfg), 64, 1024, 512, 8, 2, 0, 0, 0, 0, 0, 0, 1.0, 148)
+    assert built_lib.b200moe_pick_block_tokens(C.byref(ok)) in (16, 32, 64, 128, 256)
+    assert built_lib.b200moe_workspace_bytes(C.byref(ok)) > 64 * 1024 * 4
+    odd = _lib.Cfg(C.sizeof(_lib.Cfg), 64, 1023, 512, 8, 2, 0, 0, 0, 0, 0, 0, 1.0, 148)
+    assert built_lib.b200moe_pick_block_tokens(C.byref(odd)) == _lib.ERR_UNSUPPORTED
+    assert built_lib.b200moe_status_string(_lib.ERR_WORKSPACE).decode().startswith("workspace")
+
+
+def test_product_fails_loudly_without_gpu():
+    import torch
+    import flaggems_sglang_b200 as F
+    if torch.cuda.is_available():
+        pytest.skip("CUDA present")
+    x = torch.zeros(2, 128, dtype=torch.bfloat16)
+    w13 = torch.zeros(2, 256, 128, dtype=torch.bfloat16)
+    w2 = torch.zeros(2, 128, 128, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError):
+        F.fused_experts(x, w13, w2, torch.ones(2, 1), torch.zeros(2, 1, dtype=torch.int32))
+    with pytest.raises(RuntimeError):
+        F.moe_align_block_size(torch.zeros(2, 1, dtype=torch.int32), 16, 2)
+
+
+def test_reference_error_conventions():
+    import torch
+    import flaggems_sglang
+    from flaggems_sglang_b200 import RoutingData, GatherIndx, ScatterIndx
+    z = torch.zeros(1, dtype=torch.int32)
+    rd = RoutingData(torch.ones(2), z, 2, 1, None)
+    gi, si = GatherIndx(z, z), ScatterIndx(z, z)
+    x = torch.zeros(2, 128, dtype=torch.bfloat16)
+    w1 = torch.zeros(2, 128, 256, dtype=torch.bfloat16)
+    w2 = torch.zeros(2, 128, 128, dtype=torch.bfloat16)
+    with pytest.raises(AssertionError):
+        flaggems_sglang.triton_kernel_fused_experts(x, w1, w2, rd, gi, si, inplace=True)
+    with pytest.raises(AssertionError):
+        flaggems_sglang.triton_kernel_fused_experts(x.float(), w1, w2, rd, gi, si)
+    with pytest.raises(AssertionError):
+        flaggems_sglang.triton_kernel_fused_experts(x, w1, w2, rd, gi, si, per_channel_quant=True)
+    with pytest.raises(ValueError):
+        flaggems_sglang.triton_kernel_fused_experts(x, w1, w2, rd, gi, si, activation="relu")
