@@ -154,6 +154,38 @@ int make_layout(const b200moe_cfg* c, Layout* L) {
   return B200MOE_OK;
 }
 
+// Would the reference round each (token, expert) row of the down projection to the 16-bit
+// type before the top-k sum?  It does exactly when its grouped matmul does not split the
+// reduction: the dependency picks split_k = 1 for its persistent kernel (>= 2 tiles per SM)
+// and otherwise min(n_sms / grid, ceil(k / 64) / 4) (triton_kernels
+// matmul_ogs_details/opt_flags.py, make_default_opt_flags_nvidia, and
+// opt_flags_details/opt_flags_nvidia.py, compute_split_k); with split_k > 1 the partial
+// products stay in fp32 until the combined reduction (matmul_ogs.py, scratch dtype).
+int next_pow2(int v) {
+  int p = 1;
+  while (p < v) p <<= 1;
+  return p;
+}
+int cdiv(int a, int b) { return (a + b - 1) / b; }
+bool reference_rounds_pairs(int P, int E, int n, int k, int sms) {
+  const int tpe = P / E > 1 ? P / E : 1;
+  int block_m = next_pow2(tpe);
+  block_m = block_m < 16 ? 16 : (block_m > 128 ? 128 : block_m);
+  int block_n = 256;
+  if (n <= 128) {
+    block_n = next_pow2(n);
+    block_n = block_n < 16 ? 16 : (block_n > 128 ? 128 : block_n);
+  }
+  const int grid_n = cdiv(n, block_n);
+  const int grid_m_routed = (P <= E) ? P : cdiv(P - E + 1 > 0 ? P - E + 1 : 0, block_m) + E - 1;
+  if (static_cast<double>(grid_m_routed) * grid_n / sms >= 2.0) return true;  // persistent kernel
+  const int grid = cdiv(P, block_m) * grid_n;
+  int split = grid > 0 ? sms / grid : 1;
+  const int by_k = cdiv(k, 64) / 4;
+  if (split > by_k) split = by_k;
+  return split <= 1;
+}
+
 int query_sms(const b200moe_cfg* c) {
   if (c->num_sms > 0) return c->num_sms;
   static int cached[64] = {0};
@@ -229,6 +261,10 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
   g2.out = out32;
   g2.ld_out = c->H;
   g2.max_split = 0;
+  if (c->flags & B200MOE_FLAG_MIMIC_ROUNDING) {
+    if (reference_rounds_pairs(L.P, c->E, c->H, c->I, sms)) g2.flags |= B200MOE_FLAG_NO_SPLIT_K;
+    else g2.flags &= ~B200MOE_FLAG_MIMIC_ROUNDING;
+  }
   if (fp8) {
     g2.w_scale = quant->w2_scale;
     g2.w_scale_rows = (c->H + 127) / 128;
@@ -310,11 +346,11 @@ int b200moe_align_block_size(const void* topk_ids, int ids_are_i64, int n_slots,
                              const int32_t* expert_map, int32_t* sorted_token_ids, int32_t* expert_ids,
                              int32_t* num_tokens_post_padded, void* stream) {
   if (n_slots < 0 || n_experts <= 0 || block <= 0) return B200MOE_ERR_BAD_ARG;
-  if (sorted_token_ids == nullptr || expert_ids == nullptr || num_tokens_post_padded == nullptr)
-    return B200MOE_ERR_BAD_ARG;
+  if (num_tokens_post_padded == nullptr) return B200MOE_ERR_BAD_ARG;
   if (n_slots > 0 && topk_ids == nullptr) return B200MOE_ERR_BAD_ARG;
   int cap = align_capacity(n_slots, n_experts, block);
   if (cap < 0) return B200MOE_ERR_TOO_LARGE;
+  if (cap > 0 && (sorted_token_ids == nullptr || expert_ids == nullptr)) return B200MOE_ERR_BAD_ARG;
   return launch_align_block(topk_ids, ids_are_i64, expert_map, nullptr, n_slots, n_experts, block, cap,
                             sorted_token_ids, expert_ids, num_tokens_post_padded, nullptr, nullptr, nullptr,
                             static_cast<cudaStream_t>(stream));

@@ -79,6 +79,9 @@ def moe_align_block_size(topk_ids: torch.Tensor, block_size: int, num_experts: i
     cap = lib.b200moe_align_capacity(n_slots, num_experts, block_size)
     _lib.check(min(cap, 0), "moe_align_block_size")
     dev = ids.device
+    if cap == 0:
+        z = torch.zeros(0, dtype=torch.int32, device=dev)
+        return z, z.clone(), torch.zeros(1, dtype=torch.int32, device=dev)
     sorted_ids = torch.empty(cap, dtype=torch.int32, device=dev)
     expert_ids = torch.empty((cap + block_size - 1) // block_size, dtype=torch.int32, device=dev)
     num_post = torch.empty(1, dtype=torch.int32, device=dev)

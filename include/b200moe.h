@@ -50,7 +50,7 @@ extern "C" {
 
 /* cfg.flags */
 #define B200MOE_FLAG_WEIGHT_ON_INPUT 1  /* router weight scales GEMM-1's output, not GEMM-2's */
-#define B200MOE_FLAG_MIMIC_ROUNDING 2   /* round y1 (and y2 when K is not split) to the 16-bit type */
+#define B200MOE_FLAG_MIMIC_ROUNDING 2   /* round intermediates to the 16-bit type where the reference does */
 #define B200MOE_FLAG_SIMT 4             /* plain CUDA-core GEMMs (validation aid, slow)        */
 #define B200MOE_FLAG_IDS_I64 8          /* topk_ids are int64 instead of int32                 */
 #define B200MOE_FLAG_NO_SPLIT_K 16      /* keep GEMM-2's reduction in one piece                */

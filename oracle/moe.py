@@ -28,6 +28,38 @@ from . import quant as Q
 from .routing import topk_to_routing
 
 
+def _next_pow2(v: int) -> int:
+    p = 1
+    while p < v:
+        p <<= 1
+    return p
+
+
+def reference_rounds_pairs(n_slots: int, n_experts: int, n: int, k: int, n_sms: int = 148) -> bool:
+    """Does the reference round each (token, expert) row of GEMM-2 to the 16-bit
+    type before the top-k sum (rounding point 3)?
+
+    Only when its dependency does not split the reduction.  Restated from
+    triton_kernels/matmul_ogs_details/opt_flags.py (make_default_opt_flags_nvidia:
+    block_m, persistence, split_k) and opt_flags_details/opt_flags_nvidia.py
+    (compute_block_n, compute_grid_size, compute_split_k); n = output columns (H),
+    k = reduction length (I), n_sms = 148 on a B200.  Checked against outputs of
+    the reference recorded on a B200 (tests/golden/fused_moe_ref_golden.npz)."""
+    cdiv = lambda a, b: -(-a // b)
+    block_m = max(16, min(_next_pow2(max(1, n_slots // n_experts)), 128))
+    block_n = 256 if n > 128 else max(16, min(128, _next_pow2(n)))
+    grid_n = cdiv(n, block_n)
+    if n_slots <= n_experts:
+        grid_m_routed = n_slots
+    else:
+        grid_m_routed = cdiv(max(n_slots - n_experts + 1, 0), block_m) + n_experts - 1
+    if grid_m_routed * grid_n / n_sms >= 2.0:       # persistent kernel: never splits
+        return True
+    grid = cdiv(n_slots, block_m) * grid_n
+    split = max(1, min(n_sms // grid, cdiv(k, 64) // 4))
+    return split == 1
+
+
 def silu_mul(y1: torch.Tensor) -> torch.Tensor:
     i = y1.shape[-1] // 2
     g, u = y1[..., :i].float(), y1[..., i:].float()
@@ -38,6 +70,10 @@ def gelu_mul(y1: torch.Tensor) -> torch.Tensor:
     i = y1.shape[-1] // 2
     g, u = y1[..., :i].float(), y1[..., i:].float()
     return torch.nn.functional.gelu(g) * u
+
+
+def _n_local(w1) -> int:
+    return w1.shape[0] if hasattr(w1, "shape") else w1.n_experts
 
 
 def _round(t: torch.Tensor, dtype, on: bool) -> torch.Tensor:
@@ -72,7 +108,8 @@ def fused_experts(
     k = topk_ids.shape[1]
     out_dtype = out_dtype or x.dtype
     if round_y2 is None:
-        round_y2 = mimic_rounding
+        i_dim = (w2.shape[2] if hasattr(w2, "shape") else None)
+        round_y2 = mimic_rounding and (i_dim is None or reference_rounds_pairs(m * k, _n_local(w1), h, i_dim))
     n_local = w1.shape[0] if hasattr(w1, "shape") else w1.n_experts
     get1 = (lambda e: w1[e].float()) if hasattr(w1, "shape") else w1
     get2 = (lambda e: w2[e].float()) if hasattr(w2, "shape") else w2

@@ -43,6 +43,38 @@ def test_oracle_config1_tiny_bf16():
     torch.testing.assert_close(out.float(), dense, rtol=2e-2, atol=2e-3)
 
 
+def test_oracle_matches_reference_outputs():
+    """Pins the floating-point oracle: outputs of the reference's Triton op recorded
+    on a B200 for its own test shapes and input recipe (tests/test_fused_moe.py:50-58)."""
+    from conftest import GOLDEN
+    from flaggems_sglang_b200.testing import route
+    from parity import assert_parity, bit_equal_fraction
+    gold = np.load(GOLDEN / "fused_moe_ref_golden.npz")
+    for key in sorted(gold.files):
+        name, which = key.split("/")
+        M, K, N, E, topk = (int(p.lstrip("MKNEtopk")) for p in name.split("_"))
+        if M * K * N > 17 * 1280 * 3072:
+            continue                      # keep the CPU suite short
+        torch.manual_seed(M + K + N + E + topk)
+        x = torch.randn(M, K, dtype=torch.bfloat16)
+        w1 = torch.randn(E, K, N * 2, dtype=torch.bfloat16) * 0.1
+        w2 = torch.randn(E, N, K, dtype=torch.bfloat16) * 0.1
+        tw, ids = route(torch.randn(M, E, dtype=torch.float32), topk)
+        ref = OM.fused_experts(x, w1.transpose(1, 2), w2.transpose(1, 2), tw, ids,
+                               apply_router_weight_on_input=(which == "gate_in"))
+        g = torch.from_numpy(gold[key]).view(torch.bfloat16)
+        assert_parity(ref, g, what=key)
+        assert bit_equal_fraction(ref, g) >= 0.9, key
+
+
+def test_reference_split_rule_on_recorded_shapes():
+    # (M, K, N, E, topk, rounds GEMM-2 rows): which recorded outputs carry rounding point 3
+    for M, K, N, E, k, rounds in [(1, 128, 256, 8, 2, True), (7, 128, 256, 8, 2, True), (33, 256, 512, 16, 4, False),
+                                  (1, 1280, 3072, 64, 8, False), (4, 1280, 3072, 64, 8, False),
+                                  (17, 1280, 3072, 64, 8, True), (64, 1280, 3072, 64, 8, True)]:
+        assert OM.reference_rounds_pairs(M * k, E, K, N) is rounds
+
+
 def test_expert_lo_partition_sums_to_whole():
     from flaggems_sglang_b200.testing import make_tokens, make_weights
     w13, w2 = make_weights(64, 32, 8, dtype=torch.float32, seed=1, scale=0.1)
