@@ -90,6 +90,7 @@ void prof_mark(int slot, int mark, cudaStream_t st) {
 
 struct Layout {
   int BT, cap, P;
+  int orient;     // GEMM tile orientation that goes with BT
   int act_bytes;  // bytes per activation element fed to the GEMMs
   size_t meta, blk_off, sorted_ids, expert_ids, num_post, row_gamma, xs, xs_scale, a2, a2_scale, out32,
       total;
@@ -101,8 +102,7 @@ int pick_bt(const b200moe_cfg* c) {
   if (avg <= 10) return 16;
   if (avg <= 20) return 32;
   if (avg <= 40) return 64;
-  if (avg < 512) return 128;
-  return 256;
+  return 128;
 }
 
 int check_cfg(const b200moe_cfg* c) {
@@ -126,6 +126,8 @@ int check_cfg(const b200moe_cfg* c) {
 
 int make_layout(const b200moe_cfg* c, Layout* L) {
   L->BT = pick_bt(c);
+  // a block of 128 tokens sits on the M side of the MMA; smaller (and 256-token) blocks on the N side
+  L->orient = (L->BT == 128 && c->wmode == B200MOE_W_16BIT) ? 1 : 0;
   L->P = c->M * c->topk;
   int cap = align_capacity(L->P, c->E, L->BT);
   if (cap < 0) return B200MOE_ERR_TOO_LARGE;
@@ -232,6 +234,7 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
   g1.N = c->I;
   g1.up_row_off = c->I;
   g1.BT = L.BT;
+  g1.orient = L.orient;
   g1.topk = c->topk;
   g1.P = L.P;
   g1.flags = c->flags;
@@ -287,7 +290,8 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
     CUtensorMap tm_w1, tm_x, tm_w2, tm_a2;
     if ((rc = make_tmap_3d(&tm_w1, dt, eb, w1, c->H, 2ull * c->I, c->E, kbox, 128)) != B200MOE_OK) return rc;
     if ((rc = make_tmap_2d(&tm_x, dt, eb, xs, c->H, L.cap, kbox, L.BT)) != B200MOE_OK) return rc;
-    if ((rc = make_tmap_3d(&tm_w2, dt, eb, w2, c->I, c->H, c->E, kbox, 128)) != B200MOE_OK) return rc;
+    if ((rc = make_tmap_3d(&tm_w2, dt, eb, w2, c->I, c->H, c->E, kbox, L.orient == 1 ? 256 : 128)) != B200MOE_OK)
+      return rc;
     if ((rc = make_tmap_2d(&tm_a2, dt, eb, a2, c->I, L.cap, kbox, L.BT)) != B200MOE_OK) return rc;
     prof_mark(slot, 1, st);
     rc = launch_gemm_tc(tm_w1, tm_x, g1, sms, st);

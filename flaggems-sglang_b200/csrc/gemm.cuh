@@ -15,6 +15,7 @@ struct GemmArgs {
   int K;           // reduction length (H for mode 0, I for mode 1)
   int N;           // output rows per expert covered by tiles of 128 (I for mode 0, H for mode 1)
   int up_row_off;  // mode 0: row of the first "up" weight inside an expert (= I)
+  int orient;      // 0: weight rows on the MMA's M side (decode); 1: tokens on the M side (BT = 128)
   int BT;          // tokens per block (16..256, multiple of 16)
   int stages;      // shared-memory ring depth
   int acc_stages;  // accumulator buffers in tensor memory (1 or 2)

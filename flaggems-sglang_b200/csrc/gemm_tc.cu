@@ -60,7 +60,7 @@ struct TileCoord {
 };
 
 __device__ __forceinline__ TileCoord decode_tile(int id, const Ctrl& c, const int* s_blk_off, int E,
-                                                 int BT, int num_nt, int kblocks) {
+                                                 int BT, int num_nt, int kblocks, int tile_n) {
   // largest e with blk_off[e] * units <= id
   int lo = 0, hi = E;
   const int u = c.units_per_block;
@@ -78,23 +78,68 @@ __device__ __forceinline__ TileCoord decode_tile(int id, const Ctrl& c, const in
   const int s = rest % c.split;
   const int nt = rest / c.split;
   t.row0 = (first + b) * BT;
-  t.n0 = nt * kTileRows;
+  t.n0 = nt * tile_n;
   t.kb0 = static_cast<int>((static_cast<long long>(s) * kblocks) / c.split);
   t.kb1 = static_cast<int>((static_cast<long long>(s + 1) * kblocks) / c.split);
   return t;
 }
 
-template <int MODE, typename T>
+// Geometry of one pipeline stage and one accumulator for (MODE, ORIENT).
+//   ORIENT 0 ("weights on M"): decode-sized token blocks (BT = 16..256 tokens on the N side).
+//   ORIENT 1 ("tokens on M"):  BT = 128 tokens on the M side, 256 weight rows on the N side;
+//                              every epilogue thread owns one token row and stores contiguous
+//                              output columns with 16-byte accesses.
+template <int MODE, int ORIENT>
+struct Geo {
+  static constexpr int kWBytes = (ORIENT == 1) ? 2 * kTileBytes : (MODE == 0 ? 2 : 1) * kTileBytes;
+  static constexpr int kTileN = (ORIENT == 1 && MODE == 1) ? 256 : 128;  // output columns per tile
+};
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.v4.f32.add [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <typename T>
+__device__ __forceinline__ float act_mul(float g, float u, bool w_on_input, float gam, bool mimic,
+                                         int activation) {
+  if (w_on_input) {
+    g *= gam;
+    u *= gam;
+  }
+  if (mimic) {
+    g = to_f32<T>(from_f32<T>(g));
+    u = to_f32<T>(from_f32<T>(u));
+  }
+  const float s = (activation == B200MOE_ACT_SILU) ? __fdividef(g, 1.0f + __expf(-g)) : gelu_f32(g);
+  return s * u;
+}
+
+template <int MODE, typename T, int ORIENT>
 __global__ void __launch_bounds__(kThreads, 1)
 moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                    const GemmArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  constexpr int A_BYTES = (MODE == 0 ? 2 : 1) * kTileBytes;
+  using G = Geo<MODE, ORIENT>;
+  constexpr int W_BYTES = G::kWBytes;
   const int BT = a.BT;
-  const int b_bytes = BT * kStageKBytes;
-  const int stage_bytes = A_BYTES + b_bytes;
+  const int x_bytes = BT * kStageKBytes;
+  const int stage_bytes = W_BYTES + x_bytes;
   const int stages = a.stages;
 
   uint8_t* ctrl_base = smem + static_cast<size_t>(stages) * stage_bytes;
@@ -104,9 +149,9 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   uint64_t* bar_tempty = bar_tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* s_col_row = reinterpret_cast<int*>(tmem_slot + 4);          // [2][kMaxBT]
+  int* s_col_row = reinterpret_cast<int*>(tmem_slot + 4);               // [2][kMaxBT]
   float* s_col_gam = reinterpret_cast<float*>(s_col_row + 2 * kMaxBT);  // [2][kMaxBT]
-  int* s_blk_off = reinterpret_cast<int*>(s_col_gam + 2 * kMaxBT);  // [E+1]
+  int* s_blk_off = reinterpret_cast<int*>(s_col_gam + 2 * kMaxBT);      // [E+1]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -145,10 +190,12 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   c.units_per_block = a.num_nt * c.split;
   c.total = c.nblocks * c.units_per_block;
   {
+    // spread the tiles evenly: with w waves, ceil(total / w) CTAs do w tiles each
     int waves = (c.total + gridDim.x - 1) / static_cast<int>(gridDim.x);
     c.grid_eff = waves > 0 ? (c.total + waves - 1) / waves : 1;
+    if (a.flags & B200MOE_FLAG_NO_GRID_BALANCE) c.grid_eff = gridDim.x;
   }
-  const int cols_per_acc = (MODE == 0 ? 2 : 1) * BT;
+  const int cols_per_acc = (ORIENT == 1) ? 256 : (MODE == 0 ? 2 : 1) * BT;
   const bool active = static_cast<int>(blockIdx.x) < c.grid_eff;
 
   if (active && warp == 0 && lane == 0) {
@@ -158,7 +205,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     long long issued = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < c.total; tile += c.grid_eff) {
-      const TileCoord t = decode_tile(tile, c, s_blk_off, a.E, BT, a.num_nt, a.kblocks);
+      const TileCoord t = decode_tile(tile, c, s_blk_off, a.E, BT, a.num_nt, a.kblocks, G::kTileN);
       for (int kb = t.kb0; kb < t.kb1; ++kb) {
         if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1, abort_flag, DEV_TIMEOUT_PRODUCER)) {
           ok = false;
@@ -166,11 +213,11 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         }
         const uint32_t full = smem_u32(&bar_full[stage]);
         mbar_arrive_expect_tx(full, static_cast<uint32_t>(stage_bytes));
-        const uint32_t sa = smem_u32(smem + static_cast<size_t>(stage) * stage_bytes);
+        const uint32_t sw = smem_u32(smem + static_cast<size_t>(stage) * stage_bytes);
         const int k0 = kb * (kStageKBytes / static_cast<int>(sizeof(T)));
-        tma_load_3d(sa, &tm_w, full, k0, t.n0, t.e);
-        if (MODE == 0) tma_load_3d(sa + kTileBytes, &tm_w, full, k0, a.up_row_off + t.n0, t.e);
-        tma_load_2d(sa + A_BYTES, &tm_x, full, k0, t.row0);
+        tma_load_3d(sw, &tm_w, full, k0, t.n0, t.e);
+        if (MODE == 0) tma_load_3d(sw + kTileBytes, &tm_w, full, k0, a.up_row_off + t.n0, t.e);
+        tma_load_2d(sw + W_BYTES, &tm_x, full, k0, t.row0);
         ++issued;
         if (++stage == stages) {
           stage = 0;
@@ -193,14 +240,14 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     }
   } else if (active && warp == 1 && lane == 0) {
     // =============================== MMA issuer =================================
-    const uint32_t idesc = make_idesc(sizeof(T) == 2 ? (a.dtype == B200MOE_DTYPE_BF16 ? 1u : 0u) : 0u,
-                                      kTileRows, static_cast<uint32_t>(BT));
-    constexpr int kSteps = kStageKBytes / 32;                      // MMAs per stage and accumulator
+    const uint32_t fmt = (a.dtype == B200MOE_DTYPE_BF16) ? 1u : 0u;
+    const uint32_t idesc = make_idesc(fmt, kTileRows, ORIENT == 1 ? 256u : static_cast<uint32_t>(BT));
+    constexpr int kSteps = kStageKBytes / 32;  // MMAs per stage and accumulator
     int stage = 0, acc = 0;
     uint32_t phase = 0, acc_phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < c.total; tile += c.grid_eff) {
-      const TileCoord t = decode_tile(tile, c, s_blk_off, a.E, BT, a.num_nt, a.kblocks);
+      const TileCoord t = decode_tile(tile, c, s_blk_off, a.E, BT, a.num_nt, a.kblocks, G::kTileN);
       if (!mbar_wait(smem_u32(&bar_tempty[acc]), acc_phase ^ 1, abort_flag, DEV_TIMEOUT_MMA)) break;
       tc_fence_after();
       const uint32_t d0 = tmem_base + static_cast<uint32_t>(acc * cols_per_acc);
@@ -210,17 +257,21 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
           break;
         }
         tc_fence_after();
-        const uint32_t sa = smem_u32(smem + static_cast<size_t>(stage) * stage_bytes);
-        const uint64_t da = smem_desc_k_sw128(sa);
-        const uint64_t db = smem_desc_k_sw128(sa + A_BYTES);
+        const uint32_t sw = smem_u32(smem + static_cast<size_t>(stage) * stage_bytes);
+        const uint64_t dw = smem_desc_k_sw128(sw);
+        const uint64_t dx = smem_desc_k_sw128(sw + W_BYTES);
 #pragma unroll
         for (int k = 0; k < kSteps; ++k) {
           const uint32_t accum = (kb > t.kb0 || k > 0) ? 1u : 0u;
           // advancing 32 bytes inside the 128-byte swizzle atom = +2 in 16-byte units
-          tc_mma_f16(d0, da + 2 * k, db + 2 * k, idesc, accum);
-          if (MODE == 0) {
-            const uint64_t du = smem_desc_k_sw128(sa + kTileBytes);
-            tc_mma_f16(d0 + static_cast<uint32_t>(BT), du + 2 * k, db + 2 * k, idesc, accum);
+          if (ORIENT == 1) {
+            tc_mma_f16(d0, dx + 2 * k, dw + 2 * k, idesc, accum);
+          } else {
+            tc_mma_f16(d0, dw + 2 * k, dx + 2 * k, idesc, accum);
+            if (MODE == 0) {
+              const uint64_t du = smem_desc_k_sw128(sw + kTileBytes);
+              tc_mma_f16(d0 + static_cast<uint32_t>(BT), du + 2 * k, dx + 2 * k, idesc, accum);
+            }
           }
         }
         tc_commit(smem_u32(&bar_empty[stage]));
@@ -238,66 +289,107 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     }
   } else if (active && warp >= 2) {
     // =============================== epilogue ===================================
-    const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
-    const int ep_tid = (warp - 2) * 32 + lane; // 0..127
-    const int lrow = quad * 32 + lane;         // accumulator row = weight row inside the tile
+    const int quad = warp & 3;                  // TMEM lane quadrant this warp may read
+    const int ep_tid = (warp - 2) * 32 + lane;  // 0..127
+    const int lrow = quad * 32 + lane;          // accumulator row (TMEM lane)
     const bool w_on_input = (a.flags & B200MOE_FLAG_WEIGHT_ON_INPUT) != 0;
     const bool mimic = (a.flags & B200MOE_FLAG_MIMIC_ROUNDING) != 0;
+    const bool round_pair = mimic && c.split == 1;
     int acc = 0, iter = 0;
     uint32_t acc_phase = 0;
     for (int tile = blockIdx.x; tile < c.total; tile += c.grid_eff, ++iter) {
-      const TileCoord t = decode_tile(tile, c, s_blk_off, a.E, BT, a.num_nt, a.kblocks);
-      const int buf = iter & 1;
-      int* col_row = s_col_row + buf * kMaxBT;
-      float* col_gam = s_col_gam + buf * kMaxBT;
-      for (int cidx = ep_tid; cidx < BT; cidx += 128) {
-        const int slot = a.sorted_ids[t.row0 + cidx];
-        const bool valid = slot >= 0 && slot < a.P;
-        col_row[cidx] = valid ? (MODE == 1 ? slot / a.topk : slot) : -1;
-        col_gam[cidx] = valid ? a.row_gamma[t.row0 + cidx] : 0.f;
-      }
-      named_bar_sync(1, 128);
-      if (!mbar_wait(smem_u32(&bar_tfull[acc]), acc_phase, abort_flag, DEV_TIMEOUT_EPILOGUE)) break;
-      tc_fence_after();
+      const TileCoord t = decode_tile(tile, c, s_blk_off, a.E, BT, a.num_nt, a.kblocks, G::kTileN);
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
                              static_cast<uint32_t>(acc * cols_per_acc);
-      const int n = t.n0 + lrow;
-      const bool n_ok = n < a.N;
-      if (MODE == 0) {
-        T* out = reinterpret_cast<T*>(a.out);
-        for (int c0 = 0; c0 < BT; c0 += 16) {
-          float g[16], u[16];
-          tmem_ld16x2_wait(taddr + c0, taddr + BT + c0, g, u);
+      if (ORIENT == 1) {
+        // ---- accumulator row = token: contiguous output columns per thread
+        const int r = t.row0 + lrow;
+        const int slot = a.sorted_ids[r];
+        const bool valid = slot >= 0 && slot < a.P;
+        const float gam = valid ? a.row_gamma[r] : 0.f;
+        if (!mbar_wait(smem_u32(&bar_tfull[acc]), acc_phase, abort_flag, DEV_TIMEOUT_EPILOGUE)) break;
+        tc_fence_after();
+        if (MODE == 0) {
+          T* orow = reinterpret_cast<T*>(a.out) + static_cast<size_t>(r) * a.ld_out + t.n0;
+#pragma unroll 1
+          for (int c0 = 0; c0 < 128; c0 += 16) {
+            float g[16], u[16];
+            tmem_ld16x2_wait(taddr + c0, taddr + 128 + c0, g, u);
+            uint32_t pk[8];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            float gv = g[j], uv = u[j];
-            if (w_on_input) {
-              const float gam = col_gam[c0 + j];
-              gv *= gam;
-              uv *= gam;
+            for (int j = 0; j < 8; ++j) {
+              const float lo = act_mul<T>(g[2 * j], u[2 * j], w_on_input, gam, mimic, a.activation);
+              const float hi = act_mul<T>(g[2 * j + 1], u[2 * j + 1], w_on_input, gam, mimic, a.activation);
+              pk[j] = pack2<T>(lo, hi);
             }
-            if (mimic) {
-              gv = to_f32<T>(from_f32<T>(gv));
-              uv = to_f32<T>(from_f32<T>(uv));
+            if (t.n0 + c0 + 8 <= a.N) *reinterpret_cast<uint4*>(orow + c0) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            if (t.n0 + c0 + 16 <= a.N)
+              *reinterpret_cast<uint4*>(orow + c0 + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+          }
+        } else {
+          const int orow_idx = valid ? slot / a.topk : 0;
+          float* orow = reinterpret_cast<float*>(a.out) + static_cast<size_t>(orow_idx) * a.ld_out + t.n0;
+          const float scale = w_on_input ? 1.0f : gam;
+#pragma unroll 1
+          for (int c0 = 0; c0 < 256; c0 += 16) {
+            float v[16];
+            tmem_ld16_wait(taddr + c0, v);
+            if (valid) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                v[j] *= scale;
+                if (round_pair) v[j] = to_f32<T>(from_f32<T>(v[j]));
+              }
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                if (t.n0 + c0 + 4 * q + 4 <= a.N)
+                  red_add_v4(orow + c0 + 4 * q, v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
             }
-            const float av = (a.activation == B200MOE_ACT_SILU ? silu_f32(gv) : gelu_f32(gv)) * uv;
-            if (n_ok) out[static_cast<size_t>(t.row0 + c0 + j) * a.ld_out + n] = from_f32<T>(av);
           }
         }
       } else {
-        float* out = reinterpret_cast<float*>(a.out);
-        const bool round_pair = mimic && c.split == 1;
-        for (int c0 = 0; c0 < BT; c0 += 16) {
-          float v[16];
-          tmem_ld16_wait(taddr + c0, v);
+        // ---- accumulator row = weight row: one output column (token) at a time
+        const int buf = iter & 1;
+        int* col_row = s_col_row + buf * kMaxBT;
+        float* col_gam = s_col_gam + buf * kMaxBT;
+        for (int cidx = ep_tid; cidx < BT; cidx += 128) {
+          const int slot = a.sorted_ids[t.row0 + cidx];
+          const bool valid = slot >= 0 && slot < a.P;
+          col_row[cidx] = valid ? (MODE == 1 ? slot / a.topk : slot) : -1;
+          col_gam[cidx] = valid ? a.row_gamma[t.row0 + cidx] : 0.f;
+        }
+        named_bar_sync(1, 128);
+        if (!mbar_wait(smem_u32(&bar_tfull[acc]), acc_phase, abort_flag, DEV_TIMEOUT_EPILOGUE)) break;
+        tc_fence_after();
+        const int n = t.n0 + lrow;
+        const bool n_ok = n < a.N;
+        if (MODE == 0) {
+          T* out = reinterpret_cast<T*>(a.out) + static_cast<size_t>(t.row0) * a.ld_out + n;
+#pragma unroll 1
+          for (int c0 = 0; c0 < BT; c0 += 16) {
+            float g[16], u[16];
+            tmem_ld16x2_wait(taddr + c0, taddr + BT + c0, g, u);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int orow = col_row[c0 + j];
-            if (orow >= 0 && n_ok) {
-              float y = v[j];
-              if (!w_on_input) y *= col_gam[c0 + j];
-              if (round_pair) y = to_f32<T>(from_f32<T>(y));
-              atomicAdd(out + static_cast<size_t>(orow) * a.ld_out + n, y);
+            for (int j = 0; j < 16; ++j) {
+              const float av = act_mul<T>(g[j], u[j], w_on_input, col_gam[c0 + j], mimic, a.activation);
+              if (n_ok) out[static_cast<size_t>(c0 + j) * a.ld_out] = from_f32<T>(av);
+            }
+          }
+        } else {
+          float* out = reinterpret_cast<float*>(a.out) + n;
+#pragma unroll 1
+          for (int c0 = 0; c0 < BT; c0 += 16) {
+            float v[16];
+            tmem_ld16_wait(taddr + c0, v);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int orow = col_row[c0 + j];
+              if (orow >= 0 && n_ok) {
+                float y = v[j];
+                if (!w_on_input) y *= col_gam[c0 + j];
+                if (round_pair) y = to_f32<T>(from_f32<T>(y));
+                atomicAdd(out + static_cast<size_t>(orow) * a.ld_out, y);
+              }
             }
           }
         }
@@ -325,21 +417,27 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 
 }  // namespace
 
+static size_t stage_bytes_of(const GemmArgs& a) {
+  const size_t w = (a.orient == 1) ? 2 * kTileBytes : static_cast<size_t>(a.mode == 0 ? 2 : 1) * kTileBytes;
+  return w + static_cast<size_t>(a.BT) * kStageKBytes;
+}
+
+static size_t ctrl_bytes_of(const GemmArgs& a) {
+  return 512 /*barriers*/ + 2 * kMaxBT * 8 + static_cast<size_t>(a.E + 1) * 4 + 64;
+}
+
 void gemm_plan(GemmArgs* a) {
   const int kelems = (a->wmode == B200MOE_W_FP8_BLOCK) ? 128 : 64;
-  a->num_nt = (a->N + kTileRows - 1) / kTileRows;
+  const int tile_n = (a->orient == 1 && a->mode == 1) ? 256 : kTileRows;
+  a->num_nt = (a->N + tile_n - 1) / tile_n;
   a->kblocks = (a->K + kelems - 1) / kelems;
-  const int cols = (a->mode == 0 ? 2 : 1) * a->BT;
+  const int cols = (a->orient == 1) ? 256 : (a->mode == 0 ? 2 : 1) * a->BT;
   a->acc_stages = (2 * cols <= 512) ? 2 : 1;
   int need = a->acc_stages * cols;
   int tc = 32;
   while (tc < need) tc <<= 1;
   a->tmem_cols = tc;
-  const size_t stage_bytes = static_cast<size_t>(a->mode == 0 ? 2 : 1) * kTileBytes +
-                             static_cast<size_t>(a->BT) * kStageKBytes;
-  const size_t ctrl = 1024 /*alignment slack*/ + 512 /*barriers*/ + 2 * kMaxBT * 8 +
-                      static_cast<size_t>(a->E + 1) * 4 + 64;
-  int st = static_cast<int>((kSmemLimit - ctrl) / stage_bytes);
+  int st = static_cast<int>((kSmemLimit - 1024 - ctrl_bytes_of(*a)) / stage_bytes_of(*a));
   if (st > 10) st = 10;
   if (st < 2) st = 2;
   a->stages = st;
@@ -347,35 +445,39 @@ void gemm_plan(GemmArgs* a) {
 }
 
 size_t gemm_smem_bytes(const GemmArgs& a) {
-  const size_t stage_bytes = static_cast<size_t>(a.mode == 0 ? 2 : 1) * kTileBytes +
-                             static_cast<size_t>(a.BT) * kStageKBytes;
-  return 1024 + static_cast<size_t>(a.stages) * stage_bytes + 512 + 2 * kMaxBT * 8 +
-         static_cast<size_t>(a.E + 1) * 4 + 64;
+  return 1024 + static_cast<size_t>(a.stages) * stage_bytes_of(a) + ctrl_bytes_of(a);
 }
 
-template <int MODE, typename T>
+template <int MODE, typename T, int ORIENT>
 static int launch_one(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmArgs& a, int num_sms,
                       cudaStream_t stream) {
   const size_t smem = gemm_smem_bytes(a);
   if (smem > kSmemLimit) return B200MOE_ERR_TOO_LARGE;
-  cudaError_t err = cudaFuncSetAttribute(moe_gemm_tc_kernel<MODE, T>,
+  cudaError_t err = cudaFuncSetAttribute(moe_gemm_tc_kernel<MODE, T, ORIENT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem));
   if (err != cudaSuccess) return B200MOE_ERR_CUDA;
-  moe_gemm_tc_kernel<MODE, T><<<num_sms, kThreads, smem, stream>>>(tm_w, tm_x, a);
+  moe_gemm_tc_kernel<MODE, T, ORIENT><<<num_sms, kThreads, smem, stream>>>(tm_w, tm_x, a);
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
+}
+
+template <typename T>
+static int launch_typed(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmArgs& a, int num_sms,
+                        cudaStream_t stream) {
+  if (a.orient == 1)
+    return a.mode == 0 ? launch_one<0, T, 1>(tm_w, tm_x, a, num_sms, stream)
+                       : launch_one<1, T, 1>(tm_w, tm_x, a, num_sms, stream);
+  return a.mode == 0 ? launch_one<0, T, 0>(tm_w, tm_x, a, num_sms, stream)
+                     : launch_one<1, T, 0>(tm_w, tm_x, a, num_sms, stream);
 }
 
 int launch_gemm_tc(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmArgs& a, int num_sms,
                    cudaStream_t stream) {
   if (a.BT < 16 || a.BT > kMaxBT || a.BT % 16 != 0) return B200MOE_ERR_BAD_ARG;
+  if (a.orient == 1 && a.BT != 128) return B200MOE_ERR_BAD_ARG;
   if (a.wmode != B200MOE_W_16BIT) return B200MOE_ERR_UNSUPPORTED;
-  if (a.dtype == B200MOE_DTYPE_BF16) {
-    return a.mode == 0 ? launch_one<0, __nv_bfloat16>(tm_w, tm_x, a, num_sms, stream)
-                       : launch_one<1, __nv_bfloat16>(tm_w, tm_x, a, num_sms, stream);
-  }
-  return a.mode == 0 ? launch_one<0, __half>(tm_w, tm_x, a, num_sms, stream)
-                     : launch_one<1, __half>(tm_w, tm_x, a, num_sms, stream);
+  if (a.dtype == B200MOE_DTYPE_BF16) return launch_typed<__nv_bfloat16>(tm_w, tm_x, a, num_sms, stream);
+  return launch_typed<__half>(tm_w, tm_x, a, num_sms, stream);
 }
 
 }  // namespace b200moe

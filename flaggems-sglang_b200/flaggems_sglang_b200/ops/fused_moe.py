@@ -88,6 +88,8 @@ def _env_flags() -> int:
         f |= _lib.FLAG_SIMT
     if os.environ.get("B200MOE_NO_SPLIT_K", "0") == "1":
         f |= _lib.FLAG_NO_SPLIT_K
+    if os.environ.get("B200MOE_NO_GRID_BALANCE", "0") == "1":
+        f |= _lib.FLAG_NO_GRID_BALANCE
     return f
 
 
