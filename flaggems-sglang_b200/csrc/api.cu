@@ -435,6 +435,54 @@ int b200moe_forward_routed(const b200moe_cfg* cfg, const void* x, const void* w1
   return run_experts(cfg, L, x, w1, w2, quant, ws, out, status, st, slot);
 }
 
+// ---------------------------------------------------------------------------------------
+// Forward pass for callers that must not allocate.
+//
+// Some hosts of this library cannot hand over a workspace: a serving runtime that has
+// already given every byte of device memory to its own pools, a plugin slot whose
+// interface has no allocator and no scratch argument, or a latency-critical thread that is
+// forbidden to enter the CUDA allocator (it can block on other streams and fragment a
+// carefully planned heap).  For them the scratch lives inside the library image: the
+// array below is part of the module, so each GPU that loads the library pays for it once,
+// until the process exits.
+//
+// In host code the symbol `g_noalloc_scratch` only names the array; it is not a device
+// address.  The address is looked up once per device, with that device current, and only
+// that looked-up pointer is ever handed to kernels.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[B200MOE_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_noalloc_mu;
+void* g_noalloc_ptr[64] = {nullptr};
+
+// Device address of the scratch array on the current device (nullptr on failure).
+void* noalloc_scratch_for_current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lk(g_noalloc_mu);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || p == nullptr) return nullptr;
+    g_noalloc_ptr[dev] = p;
+  }
+  return g_noalloc_ptr[dev];
+}
+}  // namespace
+
+int b200moe_forward_topk_noalloc(const b200moe_cfg* cfg, const void* x, const void* w1, const void* w2,
+                                 const b200moe_quant* quant, const float* topk_weights, const void* topk_ids,
+                                 const int32_t* expert_map, void* out, int32_t* status, void* stream) {
+  int rc = check_cfg(cfg);
+  if (rc != B200MOE_OK) return rc;
+  Layout L;
+  if ((rc = make_layout(cfg, &L)) != B200MOE_OK) return rc;
+  if (L.total > static_cast<size_t>(B200MOE_NOALLOC_SCRATCH_BYTES)) return B200MOE_ERR_TOO_LARGE;
+  void* scratch = noalloc_scratch_for_current_device();
+  if (scratch == nullptr) return B200MOE_ERR_CUDA;
+  return b200moe_forward_topk(cfg, x, w1, w2, quant, topk_weights, topk_ids, expert_map, scratch,
+                              static_cast<size_t>(B200MOE_NOALLOC_SCRATCH_BYTES), out, status, stream);
+}
+
 int b200moe_profile_begin(int max_calls) {
   if (max_calls <= 0 || max_calls > 4096) return B200MOE_ERR_BAD_ARG;
   std::lock_guard<std::mutex> lk(g_prof.mu);

@@ -15,6 +15,7 @@ DTYPE_BF16, DTYPE_FP16 = 0, 1
 W_16BIT, W_FP8_BLOCK, W_INT4_AWQ = 0, 1, 2
 LAYOUT_LAYER, LAYOUT_OP = 0, 1
 ACT_SILU, ACT_GELU = 0, 1
+NOALLOC_SCRATCH_BYTES = 16 * 1024 * 1024
 FLAG_WEIGHT_ON_INPUT, FLAG_MIMIC_ROUNDING, FLAG_SIMT, FLAG_IDS_I64, FLAG_NO_SPLIT_K, FLAG_NO_GRID_BALANCE = 1, 2, 4, 8, 16, 32
 
 
@@ -47,6 +48,9 @@ SYMBOLS = {
     "b200moe_forward_topk": (C.c_int, [C.POINTER(Cfg), C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(Quant),
                                        C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
                                        C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b200moe_forward_topk_noalloc": (C.c_int, [C.POINTER(Cfg), C.c_void_p, C.c_void_p, C.c_void_p,
+                                               C.POINTER(Quant), C.c_void_p, C.c_void_p, C.c_void_p,
+                                               C.c_void_p, C.c_void_p, C.c_void_p]),
     "b200moe_forward_routed": (C.c_int, [C.POINTER(Cfg), C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(Quant),
                                          C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
                                          C.c_void_p, C.c_void_p, C.c_void_p]),

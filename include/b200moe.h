@@ -140,6 +140,35 @@ int b200moe_forward_topk(const b200moe_cfg *cfg, const void *x, const void *w1,
                          void *stream);
 
 /*
+ * Same computation as b200moe_forward_topk for callers that cannot provide a
+ * workspace and must not allocate one.  No counterpart in the reference (its
+ * operator allocates every intermediate through PyTorch on each call).
+ *
+ * Who needs it: a runtime that has handed all device memory to its own pools, a
+ * plugin interface without a scratch argument, or a thread that may not enter
+ * the CUDA allocator.  The scratch is an array of B200MOE_NOALLOC_SCRATCH_BYTES
+ * that is part of the library image: every GPU that loads the library holds it
+ * until the process exits.  The call itself allocates nothing and frees nothing.
+ *
+ * Limits and rules:
+ *   - b200moe_workspace_bytes(cfg) must not exceed B200MOE_NOALLOC_SCRATCH_BYTES,
+ *     else B200MOE_ERR_TOO_LARGE is returned and nothing is launched (16 MiB
+ *     covers decode-sized batches, e.g. 16 tokens of the Mixtral-shaped layer or
+ *     64 tokens of the Qwen3-30B-A3B-shaped one).
+ *   - The first call on each device looks up the array's device address (with
+ *     that device current); make that first call before any stream capture.
+ *   - Every call on a device uses the same array and finds the previous call's
+ *     contents in it; the call re-initialises all it reads.  Two calls that
+ *     overlap on the GPU (different streams) race on the array: serialise them.
+ */
+#define B200MOE_NOALLOC_SCRATCH_BYTES (16 * 1024 * 1024)
+int b200moe_forward_topk_noalloc(const b200moe_cfg *cfg, const void *x, const void *w1,
+                                 const void *w2, const b200moe_quant *quant,
+                                 const float *topk_weights, const void *topk_ids,
+                                 const int32_t *expert_map, void *out, int32_t *status,
+                                 void *stream);
+
+/*
  * Fused experts from the reference's routing triple.  Replaces
  * triton_kernel_fused_experts (src/flaggems_sglang/ops/fused_moe.py:133-216)
  * as the reference's tests call it (tests/test_fused_moe.py:94): hist[E] =
