@@ -101,7 +101,7 @@ int pick_bt(const b200moe_cfg* c) {
   const double avg = static_cast<double>(c->M) * c->topk / (c->E > 0 ? c->E : 1);
   if (avg <= 10) return 16;
   if (avg <= 20) return 32;
-  if (avg <= 40) return 64;
+  if (avg <= 40 || c->wmode == B200MOE_W_FP8_BLOCK) return 64;  // FP8 keeps its accumulators in registers
   return 128;
 }
 
@@ -118,6 +118,9 @@ int check_cfg(const b200moe_cfg* c) {
     if (c->w_layout != B200MOE_LAYOUT_LAYER) return B200MOE_ERR_UNSUPPORTED;
   } else if (c->wmode == B200MOE_W_FP8_BLOCK) {
     if (c->H % 128 != 0 || c->I % 128 != 0) return B200MOE_ERR_UNSUPPORTED;
+    if (c->block_tokens != 0 && c->block_tokens != 16 && c->block_tokens != 32 && c->block_tokens != 64)
+      return B200MOE_ERR_UNSUPPORTED;
+    if (c->flags & B200MOE_FLAG_SIMT) return B200MOE_ERR_UNSUPPORTED;
   } else {
     return B200MOE_ERR_UNSUPPORTED;
   }
@@ -221,7 +224,8 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
     rc = launch_group_quant_fp8(x, c->dtype, xs, reinterpret_cast<float*>(ws + L.xs_scale), sorted_ids, meta,
                                 L.P, c->topk, L.cap, c->H, 1, L.cap, sms, st);
   } else {
-    rc = launch_gather_rows(x, xs, sorted_ids, meta, L.P, c->topk, c->H * 2, L.cap, sms, st);
+    rc = launch_gather_rows(x, xs, sorted_ids, meta, L.P, c->topk, c->H * 2, L.cap, out32,
+                            static_cast<size_t>(c->M) * c->H * 4, sms, st);
   }
   if (rc != B200MOE_OK) return rc;
 
@@ -254,7 +258,7 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
     g1.out_q = reinterpret_cast<uint8_t*>(a2);
     g1.out_scale = reinterpret_cast<float*>(ws + L.a2_scale);
   }
-  gemm_plan(&g1);
+  if (fp8) gemm_plan_fp8(&g1); else gemm_plan(&g1);
 
   GemmArgs g2 = g1;
   g2.mode = 1;
@@ -264,7 +268,7 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
   g2.out = out32;
   g2.ld_out = c->H;
   g2.max_split = 0;
-  if (c->flags & B200MOE_FLAG_MIMIC_ROUNDING) {
+  if (!fp8 && (c->flags & B200MOE_FLAG_MIMIC_ROUNDING)) {
     if (reference_rounds_pairs(L.P, c->E, c->H, c->I, sms)) g2.flags |= B200MOE_FLAG_NO_SPLIT_K;
     else g2.flags &= ~B200MOE_FLAG_MIMIC_ROUNDING;
   }
@@ -274,13 +278,13 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
     g2.x_scale = reinterpret_cast<float*>(ws + L.a2_scale);
     g2.out_q = nullptr;
     g2.out_scale = nullptr;
+    g2.flags &= ~B200MOE_FLAG_MIMIC_ROUNDING;
   }
-  gemm_plan(&g2);
+  if (fp8) gemm_plan_fp8(&g2); else gemm_plan(&g2);
 
   if (c->flags & B200MOE_FLAG_SIMT) {
     rc = launch_gemm_simt(w1, xs, g1, st, L.cap);
     if (rc != B200MOE_OK) return rc;
-    if (cudaMemsetAsync(out32, 0, static_cast<size_t>(c->M) * c->H * 4, st) != cudaSuccess) return B200MOE_ERR_CUDA;
     rc = launch_gemm_simt(w2, a2, g2, st, L.cap);
     if (rc != B200MOE_OK) return rc;
   } else {
@@ -294,12 +298,13 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
       return rc;
     if ((rc = make_tmap_2d(&tm_a2, dt, eb, a2, c->I, L.cap, kbox, L.BT)) != B200MOE_OK) return rc;
     prof_mark(slot, 1, st);
-    rc = launch_gemm_tc(tm_w1, tm_x, g1, sms, st);
+    rc = fp8 ? launch_gemm_fp8(tm_w1, tm_x, g1, sms, st) : launch_gemm_tc(tm_w1, tm_x, g1, sms, st);
     prof_mark(slot, 2, st);
     if (rc != B200MOE_OK) return rc;
-    if (cudaMemsetAsync(out32, 0, static_cast<size_t>(c->M) * c->H * 4, st) != cudaSuccess) return B200MOE_ERR_CUDA;
+    if (fp8 && cudaMemsetAsync(out32, 0, static_cast<size_t>(c->M) * c->H * 4, st) != cudaSuccess)
+      return B200MOE_ERR_CUDA;
     prof_mark(slot, 3, st);
-    rc = launch_gemm_tc(tm_w2, tm_a2, g2, sms, st);
+    rc = fp8 ? launch_gemm_fp8(tm_w2, tm_a2, g2, sms, st) : launch_gemm_tc(tm_w2, tm_a2, g2, sms, st);
     prof_mark(slot, 4, st);
     if (rc != B200MOE_OK) return rc;
   }

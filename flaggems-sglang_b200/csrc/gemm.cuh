@@ -48,6 +48,9 @@ void gemm_plan(GemmArgs* a);  // fills stages / acc_stages / tmem_cols / num_nt 
 
 int launch_gemm_tc(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmArgs& a, int num_sms,
                    cudaStream_t stream);
+void gemm_plan_fp8(GemmArgs* a);
+int launch_gemm_fp8(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmArgs& a, int num_sms,
+                    cudaStream_t stream);
 int launch_gemm_simt(const void* w, const void* x, const GemmArgs& a, cudaStream_t stream, int cap);
 
 }  // namespace b200moe

@@ -1,0 +1,326 @@
+// Grouped expert GEMMs for FP8 (e4m3) weights with one fp32 scale per 128x128 block and
+// activations quantised per token and 128-wide group.
+//
+// The hardware's block-scaled MMA wants power-of-two scales per 32 elements, not fp32 scales
+// per 128, so the scaling is done on the CUDA cores: every 128-wide slice of the reduction
+// (one pipeline stage = one swizzle row of FP8) is multiplied into a fresh partial
+// accumulator in tensor memory (4 x tcgen05.mma.kind::f8f6f4, K = 32 each); the epilogue
+// warps read it back, scale it by a_scale[token, kb] * w_scale[row block, kb] and add it to
+// accumulators they keep in registers, while the MMA thread is already filling the other
+// partial buffer.  Weight rows sit on the MMA's M side, the token block (16/32/64) on N, so
+// the promotion costs 2*BT FMAs per thread and slice.
+//
+// mode 0: gate/up projection; tail = SiLU*mul, rounding to the 16-bit type, dynamic 1x128
+//         quantisation (the 128 lanes of a tile are exactly one group) -> e4m3 + scale.
+// mode 1: down projection; tail = routing weight and red.global.add.f32 into the combine
+//         buffer (K may be split across CTAs).
+#include "gemm_sched.cuh"
+
+namespace b200moe {
+
+namespace {
+
+template <int MODE, int BT>
+__global__ void __launch_bounds__(kThreads, 1)
+moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                    const GemmArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  constexpr int W_BYTES = (MODE == 0 ? 2 : 1) * kTileBytes;
+  constexpr int X_BYTES = BT * kStageKBytes;
+  constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
+  constexpr int PCOLS = (MODE == 0 ? 2 : 1) * BT;  // columns of one partial accumulator
+  const int stages = a.stages;
+
+  uint8_t* ctrl_base = smem + static_cast<size_t>(stages) * STAGE_BYTES;
+  uint64_t* bar_full = reinterpret_cast<uint64_t*>(ctrl_base);
+  uint64_t* bar_empty = bar_full + stages;
+  uint64_t* bar_pfull = bar_empty + stages;
+  uint64_t* bar_pempty = bar_pfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_pempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* s_col_row = reinterpret_cast<int*>(tmem_slot + 4);               // [2][kMaxBT]
+  float* s_col_gam = reinterpret_cast<float*>(s_col_row + 2 * kMaxBT);  // [2][kMaxBT]
+  float* s_red = s_col_gam + 2 * kMaxBT;                                // [2][4][64]
+  int* s_blk_off = reinterpret_cast<int*>(s_red + 2 * 4 * 64);          // [E+1]
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&bar_pfull[s]), 1);
+      mbar_init(smem_u32(&bar_pempty[s]), 4);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+    prefetch_tmap(&tm_w);
+    prefetch_tmap(&tm_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), static_cast<uint32_t>(a.tmem_cols));
+    tmem_relinquish();
+  }
+  for (int e = threadIdx.x; e <= a.E; e += blockDim.x) s_blk_off[e] = a.blk_off[e];
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const Ctrl c = make_ctrl(a, MODE == 1);
+  const bool active = static_cast<int>(blockIdx.x) < c.grid_eff;
+
+  if (active && warp == 0 && lane == 0) {
+    // =============================== TMA producer ===============================
+    int stage = 0;
+    uint32_t phase = 0;
+    long long issued = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < c.total; tile += c.grid_eff) {
+      const TileCoord t = decode_tile(tile, c, s_blk_off, a.E, BT, a.num_nt, a.kblocks, kTileRows);
+      for (int kb = t.kb0; kb < t.kb1; ++kb) {
+        if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1, abort_flag, DEV_TIMEOUT_PRODUCER)) {
+          ok = false;
+          break;
+        }
+        const uint32_t full = smem_u32(&bar_full[stage]);
+        mbar_arrive_expect_tx(full, static_cast<uint32_t>(STAGE_BYTES));
+        const uint32_t sw = smem_u32(smem + static_cast<size_t>(stage) * STAGE_BYTES);
+        const int k0 = kb * kStageKBytes;  // one byte per element
+        tma_load_3d(sw, &tm_w, full, k0, t.n0, t.e);
+        if (MODE == 0) tma_load_3d(sw + kTileBytes, &tm_w, full, k0, a.up_row_off + t.n0, t.e);
+        tma_load_2d(sw + W_BYTES, &tm_x, full, k0, t.row0);
+        ++issued;
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+    if (!ok) {
+      const int n = static_cast<int>(issued < stages ? issued : stages);
+      for (int i = 1; i <= n; ++i) {
+        int s = stage - i;
+        uint32_t ph = phase;
+        if (s < 0) {
+          s += stages;
+          ph ^= 1;
+        }
+        mbar_wait_brief(smem_u32(&bar_full[s]), ph);
+      }
+    }
+  } else if (active && warp == 1 && lane == 0) {
+    // =============================== MMA issuer =================================
+    const uint32_t idesc = make_idesc(0u /* e4m3 */, kTileRows, static_cast<uint32_t>(BT));
+    int stage = 0;
+    uint32_t phase = 0, j = 0;  // j counts reduction slices over the whole launch
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < c.total; tile += c.grid_eff) {
+      const TileCoord t = decode_tile(tile, c, s_blk_off, a.E, BT, a.num_nt, a.kblocks, kTileRows);
+      for (int kb = t.kb0; kb < t.kb1; ++kb, ++j) {
+        const uint32_t pb = j & 1u;
+        if (!mbar_wait(smem_u32(&bar_full[stage]), phase, abort_flag, DEV_TIMEOUT_MMA) ||
+            !mbar_wait(smem_u32(&bar_pempty[pb]), ((j >> 1) & 1u) ^ 1u, abort_flag, DEV_TIMEOUT_MMA)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d0 = tmem_base + pb * PCOLS;
+        const uint32_t sw = smem_u32(smem + static_cast<size_t>(stage) * STAGE_BYTES);
+        const uint64_t dw = smem_desc_k_sw128(sw);
+        const uint64_t dx = smem_desc_k_sw128(sw + W_BYTES);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          tc_mma_f8(d0, dw + 2 * k, dx + 2 * k, idesc, k > 0 ? 1u : 0u);
+          if (MODE == 0) {
+            const uint64_t du = smem_desc_k_sw128(sw + kTileBytes);
+            tc_mma_f8(d0 + BT, du + 2 * k, dx + 2 * k, idesc, k > 0 ? 1u : 0u);
+          }
+        }
+        tc_commit(smem_u32(&bar_empty[stage]));
+        tc_commit(smem_u32(&bar_pfull[pb]));
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else if (active && warp >= 2) {
+    // =============================== promotion + tail ===========================
+    const int quad = warp & 3;
+    const int ep_tid = (warp - 2) * 32 + lane;
+    const int lrow = quad * 32 + lane;
+    const bool w_on_input = (a.flags & B200MOE_FLAG_WEIGHT_ON_INPUT) != 0;
+    const int kb_total = a.kblocks;
+    uint32_t j = 0;
+    int iter = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < c.total; tile += c.grid_eff, ++iter) {
+      const TileCoord t = decode_tile(tile, c, s_blk_off, a.E, BT, a.num_nt, a.kblocks, kTileRows);
+      const int buf = iter & 1;
+      int* col_row = s_col_row + buf * kMaxBT;
+      float* col_gam = s_col_gam + buf * kMaxBT;
+      for (int cidx = ep_tid; cidx < BT; cidx += 128) {
+        const int slot = a.sorted_ids[t.row0 + cidx];
+        const bool valid = slot >= 0 && slot < a.P;
+        col_row[cidx] = valid ? (MODE == 1 ? slot / a.topk : slot) : -1;
+        col_gam[cidx] = valid ? a.row_gamma[t.row0 + cidx] : 0.f;
+      }
+      named_bar_sync(1, 128);
+
+      float accg[BT], accu[MODE == 0 ? BT : 1];
+#pragma unroll
+      for (int i = 0; i < BT; ++i) accg[i] = 0.f;
+      if (MODE == 0) {
+#pragma unroll
+        for (int i = 0; i < BT; ++i) accu[i] = 0.f;
+      }
+      const float* wsg = a.w_scale + (static_cast<size_t>(t.e) * a.w_scale_rows + t.n0 / 128) * kb_total;
+      const float* wsu = a.w_scale + (static_cast<size_t>(t.e) * a.w_scale_rows + (a.up_row_off + t.n0) / 128) * kb_total;
+
+      for (int kb = t.kb0; kb < t.kb1; ++kb, ++j) {
+        const float swg = __ldg(wsg + kb);
+        const float swu = (MODE == 0) ? __ldg(wsu + kb) : 0.f;
+        const float4* sx = reinterpret_cast<const float4*>(a.x_scale + static_cast<size_t>(kb) * a.ld_xscale + t.row0);
+        const uint32_t pb = j & 1u;
+        if (!mbar_wait(smem_u32(&bar_pfull[pb]), (j >> 1) & 1u, abort_flag, DEV_TIMEOUT_EPILOGUE)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + pb * PCOLS;
+#pragma unroll
+        for (int c0 = 0; c0 < BT; c0 += 16) {
+          float g[16], u[16];
+          if (MODE == 0) tmem_ld16x2_wait(taddr + c0, taddr + BT + c0, g, u);
+          else tmem_ld16_wait(taddr + c0, g);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float4 s4 = __ldg(sx + c0 / 4 + q);
+            const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              accg[c0 + 4 * q + i] = fmaf(g[4 * q + i], swg * sv[i], accg[c0 + 4 * q + i]);
+              if (MODE == 0) accu[c0 + 4 * q + i] = fmaf(u[4 * q + i], swu * sv[i], accu[c0 + 4 * q + i]);
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_pempty[pb]));
+      }
+      if (!ok) break;
+
+      const int n = t.n0 + lrow;
+      if (MODE == 0) {
+        // activation, rounding to the 16-bit type, then one 1x128 group per (token, tile)
+        float* red = s_red + buf * 4 * 64;
+#pragma unroll
+        for (int i = 0; i < BT; ++i) {
+          float av = act_mul<__nv_bfloat16>(accg[i], accu[i], w_on_input, col_gam[i], false, a.activation);
+          av = (a.dtype == B200MOE_DTYPE_BF16) ? __bfloat162float(__float2bfloat16_rn(av))
+                                               : __half2float(__float2half_rn(av));
+          accg[i] = av;
+          float m = fabsf(av);
+#pragma unroll
+          for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+          if (lane == 0) red[(warp - 2) * 64 + i] = m;
+        }
+        named_bar_sync(2, 128);
+        uint8_t* outq = a.out_q + static_cast<size_t>(t.row0) * a.ld_out + n;
+#pragma unroll
+        for (int i = 0; i < BT; ++i) {
+          const float amax = fmaxf(fmaxf(red[i], red[64 + i]), fmaxf(red[128 + i], red[192 + i]));
+          const float s = __fdiv_rn(fmaxf(amax, 1e-10f), 448.0f);
+          outq[static_cast<size_t>(i) * a.ld_out] =
+              static_cast<uint8_t>(__nv_cvt_float_to_fp8(__fdiv_rn(accg[i], s), __NV_SATFINITE, __NV_E4M3));
+          if (lrow == i) a.out_scale[static_cast<size_t>(t.n0 / 128) * a.ld_xscale + t.row0 + i] = s;
+        }
+      } else {
+        float* out = reinterpret_cast<float*>(a.out) + n;
+#pragma unroll
+        for (int i = 0; i < BT; ++i) {
+          const int orow = col_row[i];
+          if (orow >= 0) {
+            float y = accg[i];
+            if (!w_on_input) y *= col_gam[i];
+            atomicAdd(out + static_cast<size_t>(orow) * a.ld_out, y);
+          }
+        }
+      }
+    }
+  }
+
+  // ---- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, static_cast<uint32_t>(a.tmem_cols));
+  }
+  if (threadIdx.x == 0 && *abort_flag != 0) atomicCAS(a.status, 0, *abort_flag);
+}
+
+size_t fp8_stage_bytes(const GemmArgs& a) {
+  return static_cast<size_t>(a.mode == 0 ? 2 : 1) * kTileBytes + static_cast<size_t>(a.BT) * kStageKBytes;
+}
+size_t fp8_ctrl_bytes(const GemmArgs& a) {
+  return 512 + 2 * kMaxBT * 8 + 2 * 4 * 64 * 4 + static_cast<size_t>(a.E + 1) * 4 + 64;
+}
+
+template <int MODE, int BT>
+int launch_fp8(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmArgs& a, int num_sms,
+               cudaStream_t stream) {
+  const size_t smem = 1024 + static_cast<size_t>(a.stages) * fp8_stage_bytes(a) + fp8_ctrl_bytes(a);
+  if (smem > kSmemLimit) return B200MOE_ERR_TOO_LARGE;
+  if (cudaFuncSetAttribute(moe_gemm_fp8_kernel<MODE, BT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(smem)) != cudaSuccess)
+    return B200MOE_ERR_CUDA;
+  moe_gemm_fp8_kernel<MODE, BT><<<num_sms, kThreads, smem, stream>>>(tm_w, tm_x, a);
+  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
+}
+
+}  // namespace
+
+void gemm_plan_fp8(GemmArgs* a) {
+  a->orient = 0;
+  a->num_nt = (a->N + kTileRows - 1) / kTileRows;
+  a->kblocks = (a->K + 127) / 128;
+  const int cols = 2 * (a->mode == 0 ? 2 : 1) * a->BT;  // two partial buffers
+  int tc = 32;
+  while (tc < cols) tc <<= 1;
+  a->tmem_cols = tc;
+  a->acc_stages = 2;
+  int st = static_cast<int>((kSmemLimit - 1024 - fp8_ctrl_bytes(*a)) / fp8_stage_bytes(*a));
+  if (st > 10) st = 10;
+  if (st < 2) st = 2;
+  a->stages = st;
+  if (a->max_split <= 0) a->max_split = 16;
+}
+
+int launch_gemm_fp8(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmArgs& a, int num_sms,
+                    cudaStream_t stream) {
+  if (a.wmode != B200MOE_W_FP8_BLOCK) return B200MOE_ERR_BAD_ARG;
+  if (a.K % 128 != 0 || a.N % 128 != 0) return B200MOE_ERR_UNSUPPORTED;
+#define B200MOE_FP8_CASE(bt)                                                              \
+  case bt:                                                                                \
+    return a.mode == 0 ? launch_fp8<0, bt>(tm_w, tm_x, a, num_sms, stream)                \
+                       : launch_fp8<1, bt>(tm_w, tm_x, a, num_sms, stream);
+  switch (a.BT) {
+    B200MOE_FP8_CASE(16)
+    B200MOE_FP8_CASE(32)
+    B200MOE_FP8_CASE(64)
+    default:
+      return B200MOE_ERR_BAD_ARG;
+  }
+#undef B200MOE_FP8_CASE
+}
+
+}  // namespace b200moe

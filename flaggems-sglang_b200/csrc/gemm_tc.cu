@@ -15,74 +15,11 @@
 //
 // Every wait is bounded; on a time-out the CTA raises an abort flag, all roles leave their
 // loops, the status word is set, TMEM is freed and the kernel returns.
-#include "gemm.cuh"
+#include "gemm_sched.cuh"
 
 namespace b200moe {
 
 namespace {
-
-constexpr int kThreads = 192;
-constexpr int kTileRows = 128;           // weight rows per MMA (the instruction's M)
-constexpr int kStageKBytes = 128;        // bytes of the reduction dim per stage row (one swizzle atom)
-constexpr int kTileBytes = kTileRows * kStageKBytes;  // 16 KiB
-constexpr int kMaxBT = 256;
-constexpr size_t kSmemLimit = 232448;    // 227 KiB
-
-struct Ctrl {
-  int nblocks;
-  int units_per_block;  // num_nt (* split)
-  int split;
-  int total;
-  int grid_eff;
-};
-
-__device__ __forceinline__ int pick_split(int tiles, int kblocks, int grid, int max_split) {
-  int best = 1;
-  float best_eff = -1.f;
-  int smax = min(max_split, max(1, kblocks / 4));
-  for (int s = 1; s <= smax; ++s) {
-    int total = tiles * s;
-    int waves = (total + grid - 1) / grid;
-    float eff = static_cast<float>(total) / static_cast<float>(waves * grid);
-    if (eff > best_eff + 0.04f) {
-      best_eff = eff;
-      best = s;
-    }
-  }
-  return best;
-}
-
-struct TileCoord {
-  int e;      // expert
-  int row0;   // first padded row of the token block
-  int n0;     // first weight row inside the expert
-  int kb0, kb1;  // k-block range
-};
-
-__device__ __forceinline__ TileCoord decode_tile(int id, const Ctrl& c, const int* s_blk_off, int E,
-                                                 int BT, int num_nt, int kblocks, int tile_n) {
-  // largest e with blk_off[e] * units <= id
-  int lo = 0, hi = E;
-  const int u = c.units_per_block;
-  while (hi - lo > 1) {
-    int mid = (lo + hi) >> 1;
-    if (s_blk_off[mid] * u <= id) lo = mid; else hi = mid;
-  }
-  TileCoord t;
-  t.e = lo;
-  const int first = s_blk_off[lo];
-  const int nb = s_blk_off[lo + 1] - first;
-  const int local = id - first * u;
-  const int b = local % nb;
-  const int rest = local / nb;
-  const int s = rest % c.split;
-  const int nt = rest / c.split;
-  t.row0 = (first + b) * BT;
-  t.n0 = nt * tile_n;
-  t.kb0 = static_cast<int>((static_cast<long long>(s) * kblocks) / c.split);
-  t.kb1 = static_cast<int>((static_cast<long long>(s + 1) * kblocks) / c.split);
-  return t;
-}
 
 // Geometry of one pipeline stage and one accumulator for (MODE, ORIENT).
 //   ORIENT 0 ("weights on M"): decode-sized token blocks (BT = 16..256 tokens on the N side).
@@ -111,21 +48,6 @@ template <>
 __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
   __half2 v = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
-}
-
-template <typename T>
-__device__ __forceinline__ float act_mul(float g, float u, bool w_on_input, float gam, bool mimic,
-                                         int activation) {
-  if (w_on_input) {
-    g *= gam;
-    u *= gam;
-  }
-  if (mimic) {
-    g = to_f32<T>(from_f32<T>(g));
-    u = to_f32<T>(from_f32<T>(u));
-  }
-  const float s = (activation == B200MOE_ACT_SILU) ? __fdividef(g, 1.0f + __expf(-g)) : gelu_f32(g);
-  return s * u;
 }
 
 template <int MODE, typename T, int ORIENT>
@@ -181,20 +103,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // ---- work decomposition, identical in every thread of every CTA
-  Ctrl c;
-  c.nblocks = a.meta[0];
-  c.split = 1;
-  if (MODE == 1 && !(a.flags & B200MOE_FLAG_NO_SPLIT_K))
-    c.split = pick_split(c.nblocks * a.num_nt, a.kblocks, gridDim.x, a.max_split);
-  c.units_per_block = a.num_nt * c.split;
-  c.total = c.nblocks * c.units_per_block;
-  {
-    // spread the tiles evenly: with w waves, ceil(total / w) CTAs do w tiles each
-    int waves = (c.total + gridDim.x - 1) / static_cast<int>(gridDim.x);
-    c.grid_eff = waves > 0 ? (c.total + waves - 1) / waves : 1;
-    if (a.flags & B200MOE_FLAG_NO_GRID_BALANCE) c.grid_eff = gridDim.x;
-  }
+  const Ctrl c = make_ctrl(a, MODE == 1);
   const int cols_per_acc = (ORIENT == 1) ? 256 : (MODE == 0 ? 2 : 1) * BT;
   const bool active = static_cast<int>(blockIdx.x) < c.grid_eff;
 

@@ -7,22 +7,27 @@ namespace b200moe {
 
 namespace {
 
-// One warp per padded row; 16-byte chunks.  Rows beyond meta[1] are left alone,
-// padding rows are zero-filled.
+// One thread per 16-byte chunk of a padded row (grid-stride), so that a handful of rows at
+// decode sizes still spreads over many threads.  Rows beyond meta[1] are left alone, padding
+// rows are zero-filled.  The same launch clears the fp32 combine buffer (`zero`, `zero_chunks`).
 __global__ void __launch_bounds__(256)
 gather_rows_kernel(const uint4* __restrict__ x, uint4* __restrict__ xs, const int* __restrict__ sorted_ids,
-                   const int* __restrict__ meta, int P, int topk, int chunks_per_row, int cap) {
-  const int warps_per_cta = blockDim.x >> 5;
-  const int lane = threadIdx.x & 31;
+                   const int* __restrict__ meta, int P, int topk, int chunks_per_row, int cap,
+                   uint4* __restrict__ zero, long long zero_chunks) {
   const int rows = min(meta[1], cap);
-  for (int r = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); r < rows; r += gridDim.x * warps_per_cta) {
-    const int slot = sorted_ids[r];
-    uint4* dst = xs + static_cast<size_t>(r) * chunks_per_row;
-    if (slot < 0 || slot >= P) {
-      for (int c = lane; c < chunks_per_row; c += 32) dst[c] = make_uint4(0, 0, 0, 0);
+  const long long n_copy = static_cast<long long>(rows) * chunks_per_row;
+  const long long total = n_copy + zero_chunks;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    if (i < n_copy) {
+      const int r = static_cast<int>(i / chunks_per_row);
+      const int c = static_cast<int>(i - static_cast<long long>(r) * chunks_per_row);
+      const int slot = sorted_ids[r];
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (slot >= 0 && slot < P) v = __ldg(x + static_cast<size_t>(slot / topk) * chunks_per_row + c);
+      xs[i] = v;
     } else {
-      const uint4* src = x + static_cast<size_t>(slot / topk) * chunks_per_row;
-      for (int c = lane; c < chunks_per_row; c += 32) dst[c] = __ldg(src + c);
+      zero[i - n_copy] = make_uint4(0, 0, 0, 0);
     }
   }
 }
@@ -103,13 +108,16 @@ finalize_kernel(const float4* __restrict__ acc, T* __restrict__ out, size_t n4, 
 }  // namespace
 
 int launch_gather_rows(const void* x, void* xs, const int* sorted_ids, const int* meta, int P, int topk,
-                       int row_bytes, int cap, int num_sms, cudaStream_t stream) {
-  if (row_bytes % 16 != 0) return B200MOE_ERR_UNSUPPORTED;
-  int ctas = (cap + 7) / 8;
-  if (ctas > num_sms * 8) ctas = num_sms * 8;
+                       int row_bytes, int cap, void* zero, size_t zero_bytes, int num_sms,
+                       cudaStream_t stream) {
+  if (row_bytes % 16 != 0 || zero_bytes % 16 != 0) return B200MOE_ERR_UNSUPPORTED;
+  const long long work = static_cast<long long>(cap) * (row_bytes / 16) + static_cast<long long>(zero_bytes / 16);
+  long long ctas = (work + 255) / 256;
+  if (ctas > static_cast<long long>(num_sms) * 8) ctas = static_cast<long long>(num_sms) * 8;
   if (ctas < 1) ctas = 1;
-  gather_rows_kernel<<<ctas, 256, 0, stream>>>(reinterpret_cast<const uint4*>(x), reinterpret_cast<uint4*>(xs),
-                                              sorted_ids, meta, P, topk, row_bytes / 16, cap);
+  gather_rows_kernel<<<static_cast<int>(ctas), 256, 0, stream>>>(
+      reinterpret_cast<const uint4*>(x), reinterpret_cast<uint4*>(xs), sorted_ids, meta, P, topk, row_bytes / 16,
+      cap, reinterpret_cast<uint4*>(zero), static_cast<long long>(zero_bytes / 16));
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
 }
 

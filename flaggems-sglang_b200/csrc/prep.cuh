@@ -4,9 +4,11 @@
 
 namespace b200moe {
 
-// xs[r] = x[sorted_ids[r] / topk] for r < meta[1]; padding rows zero-filled.
+// xs[r] = x[sorted_ids[r] / topk] for r < meta[1]; padding rows zero-filled.  Also clears
+// `zero_bytes` bytes at `zero` (the fp32 combine buffer) in the same launch.
 int launch_gather_rows(const void* x, void* xs, const int* sorted_ids, const int* meta, int P, int topk,
-                       int row_bytes, int cap, int num_sms, cudaStream_t stream);
+                       int row_bytes, int cap, void* zero, size_t zero_bytes, int num_sms,
+                       cudaStream_t stream);
 
 // Per-token-group (1x128) FP8 quantisation, optionally gathering rows through
 // sorted_ids like launch_gather_rows.  scale_t: store scales group-major.

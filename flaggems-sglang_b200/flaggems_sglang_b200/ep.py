@@ -1,0 +1,84 @@
+"""Expert parallelism: experts partitioned across ranks, tokens dispatched and
+combined with all-to-all.
+
+Rank r of R holds experts [r*E_loc, (r+1)*E_loc).  Every rank brings its own
+tokens with routing over the *global* expert ids.  One call does
+
+  dispatch   all_to_all: each peer receives this rank's token rows together with
+             the top-k entries that point at the peer's experts (the other
+             entries are masked to -1), in a fixed slot per (peer, token) so that
+             no counts have to be exchanged and nothing on the host reads device
+             data;
+  local op   the single-GPU fused experts over the received rows (masked entries
+             are dropped by the alignment kernel, so a token without a local
+             expert costs no GEMM work and yields a zero row);
+  combine    the per-(token, rank) partial sums travel back with the inverse
+             all_to_all and the owner adds at most R of them in rank order.
+
+The reference has no counterpart: it rejects `expert_map`
+(src/flaggems_sglang/ops/fused_moe.py:160-162) and contains no communication.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+
+def dispatch_tables(topk_ids: torch.Tensor, topk_weights: torch.Tensor, n_local_experts: int, world: int):
+    """Per-destination routing tables.
+
+    Returns (ids [R, m, k] int32 with local expert ids or -1, weights [R, m, k]
+    fp32 with 0 where masked)."""
+    ids = topk_ids.to(torch.int64)
+    dest = torch.div(ids, n_local_experts, rounding_mode="floor")
+    ranks = torch.arange(world, device=ids.device).view(world, 1, 1)
+    mine = dest.unsqueeze(0) == ranks
+    local = (ids.unsqueeze(0) - ranks * n_local_experts)
+    out_ids = torch.where(mine, local, torch.full_like(local, -1)).to(torch.int32)
+    out_w = torch.where(mine, topk_weights.to(torch.float32).unsqueeze(0), torch.zeros((), device=ids.device))
+    return out_ids.contiguous(), out_w.contiguous()
+
+
+def ep_fused_experts(
+    hidden_states: torch.Tensor,
+    w13_local: torch.Tensor,
+    w2_local: torch.Tensor,
+    topk_weights: torch.Tensor,
+    topk_ids: torch.Tensor,
+    group: Optional[dist.ProcessGroup] = None,
+    local_fn: Optional[Callable] = None,
+    **kwargs,
+) -> torch.Tensor:
+    """Expert-parallel fused MoE for this rank's tokens ``hidden_states [m, H]``.
+
+    Every rank must call with the same ``m`` (pad the last batch if needed).
+    ``local_fn(x, w13, w2, topk_weights, topk_ids, **kwargs)`` computes the local
+    experts; it defaults to the CUDA operator of this package.
+    """
+    if local_fn is None:
+        from .ops.fused_moe import fused_experts as local_fn
+    world = dist.get_world_size(group)
+    m, h = hidden_states.shape
+    k = topk_ids.shape[1]
+    e_loc = w13_local.shape[0]
+    if world == 1:
+        return local_fn(hidden_states, w13_local, w2_local, topk_weights, topk_ids.to(torch.int32), **kwargs)
+
+    ids_t, w_t = dispatch_tables(topk_ids, topk_weights, e_loc, world)
+    send_x = hidden_states.unsqueeze(0).expand(world, m, h).contiguous()
+    recv_x = torch.empty_like(send_x)
+    # ids and weights share one int32 payload: [R, m, 2k]
+    meta = torch.cat([ids_t, w_t.view(torch.int32)], dim=2).contiguous()
+    recv_meta = torch.empty_like(meta)
+    dist.all_to_all_single(recv_x, send_x, group=group)
+    dist.all_to_all_single(recv_meta, meta, group=group)
+
+    r_ids = recv_meta[:, :, :k].reshape(world * m, k).contiguous()
+    r_w = recv_meta[:, :, k:].contiguous().view(torch.float32).reshape(world * m, k)
+    partial = local_fn(recv_x.view(world * m, h), w13_local, w2_local, r_w, r_ids, **kwargs)
+
+    back = torch.empty(world, m, h, dtype=partial.dtype, device=partial.device)
+    dist.all_to_all_single(back, partial.view(world, m, h).contiguous(), group=group)
+    return back.float().sum(dim=0).to(hidden_states.dtype)
