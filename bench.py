@@ -35,9 +35,16 @@ WORKLOADS = {
     "mixtral": (4096, 14336, 8, 2, "bf16"),
     "qwen3-30b-a3b": (2048, 768, 128, 8, "bf16"),
     "reference-bench": (1280, 3072, 64, 8, "bf16"),
+    # FP8 e4m3 weights with 128x128 block scales, zipf-skewed routing; with --gpus N the
+    # experts are partitioned over the ranks (expert parallelism) and M is the global batch
+    "deepseek-v3": (7168, 2048, 256, 8, "fp8"),
+    "deepseek-v3-e32": (7168, 2048, 32, 8, "fp8"),        # 32-expert slice of the same layer (small profiling case)
+    # int4 AWQ w4a16: uint4 group-128 weights with zero points, fp16 activations
+    "mixtral-awq": (4096, 14336, 8, 2, "int4"),
 }
 SWEEP_M = {"mixtral": [1, 16, 128, 1024, 4096], "qwen3-30b-a3b": [1, 8, 32, 64, 128, 256],
-           "reference-bench": [1, 4, 17, 64, 1024, 2048, 4096]}
+           "reference-bench": [1, 4, 17, 64, 1024, 2048, 4096], "deepseek-v3": [1, 64, 512, 4096],
+           "deepseek-v3-e32": [1, 64, 512], "mixtral-awq": [1, 32, 256, 2048]}
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
@@ -55,8 +62,73 @@ def load_peaks():
 
 
 def algorithmic_work(h, i, k, m, experts_hit, bytes_w=2):
-    """bytes = D*3*H*I*b_w + M*H*(b_x + b_out); flops = 6*M*k*H*I."""
-    return experts_hit * 3 * h * i * bytes_w + m * h * 4, 6 * m * k * h * i
+    """bytes = D*(3*H*I*b_w + S_e) + M*H*(b_x + b_out); flops = 6*M*k*H*I.
+    S_e = per-expert scale bytes (FP8: one fp32 per 128x128 block)."""
+    s_e = 0
+    if bytes_w == 1:
+        s_e = 3 * h * i // (128 * 128) * 4
+    elif bytes_w == 0.5:
+        s_e = 3 * h * i // 128 * 2.5            # fp16 scale + packed uint4 zero per group and output row
+    return int(experts_hit * (3 * h * i * bytes_w + s_e) + m * h * 4), 6 * m * k * h * i
+
+
+class Layer:
+    """The benchmarked MoE layer on one rank: weights (all experts, or this rank's
+    share under expert parallelism) and the forward call."""
+
+    def __init__(self, workload, dev, rank, world):
+        import flaggems_sglang_b200 as F
+        from flaggems_sglang_b200.testing import make_weights
+        self.F = F
+        self.h, self.i, self.e, self.k, self.dt = WORKLOADS[workload]
+        self.fp8 = self.dt == "fp8"
+        self.int4 = self.dt == "int4"
+        self.act_dtype = torch.float16 if self.int4 else torch.bfloat16
+        self.ep = self.fp8 and world > 1
+        self.world = world
+        e_ids = range(self.e)
+        if self.ep:
+            assert self.e % world == 0
+            e_loc = self.e // world
+            e_ids = range(rank * e_loc, (rank + 1) * e_loc)
+        if self.fp8:
+            from flaggems_sglang_b200.quant import quantize_fp8_block
+            qs = [[], [], [], []]
+            for ei in e_ids:                      # expert by expert keeps the bf16 temporaries small
+                a, b = make_weights(self.h, self.i, self.e, device=dev, seed=0, expert_ids=[ei])
+                aq, as_ = quantize_fp8_block(a)
+                bq, bs_ = quantize_fp8_block(b)
+                for lst, t in zip(qs, (aq, as_, bq, bs_)):
+                    lst.append(t)
+            self.w13, self.s13, self.w2, self.s2 = (torch.cat(l, dim=0).contiguous() for l in qs)
+            self.kw = dict(use_fp8_w8a8=True, w13_scale=self.s13, w2_scale=self.s2)
+            self.bytes_w = 1
+        elif self.int4:
+            from flaggems_sglang_b200.quant import quantize_awq, repack_awq_for_kernel
+            qs = [[], [], [], []]
+            for ei in e_ids:
+                a, b = make_weights(self.h, self.i, self.e, dtype=torch.float16, device=dev, seed=0, expert_ids=[ei])
+                p1, z1 = repack_awq_for_kernel(*quantize_awq(a.transpose(1, 2).contiguous()))
+                p2, z2 = repack_awq_for_kernel(*quantize_awq(b.transpose(1, 2).contiguous()))
+                for lst, t in zip(qs, (p1, z1, p2, z2)):
+                    lst.append(t)
+            self.w13, z13, self.w2, z2 = (torch.cat(l, dim=0).contiguous() for l in qs)
+            self.kw = dict(use_int4_w4a16=True, w13_sz=z13, w2_sz=z2)
+            self.bytes_w = 0.5
+        else:
+            self.w13, self.w2 = make_weights(self.h, self.i, self.e, device=dev, seed=0)
+            self.kw = {}
+            self.bytes_w = 2
+
+    def tokens(self, m, dev, seed):
+        from flaggems_sglang_b200.testing import make_tokens
+        return make_tokens(m, self.h, self.e, self.k, dtype=self.act_dtype, device=dev, seed=seed, skew=self.fp8)
+
+    def forward(self, x, tw, ids):
+        if self.ep:
+            from flaggems_sglang_b200.ep import ep_fused_experts
+            return ep_fused_experts(x, self.w13, self.w2, tw, ids, **self.kw)
+        return self.F.fused_experts(x, self.w13, self.w2, tw, ids, **self.kw)
 
 
 class ClockSampler:
@@ -194,10 +266,26 @@ def time_calls(fn, steps, warmup, barrier=None):
     return ev0.elapsed_time(ev1)  # ms
 
 
+def time_graph_replays(fn, steps, warmup=3):
+    """Captures one call of `fn` in a CUDA graph and times replays (device time per
+    replay in ms), the way a serving stack issues decode steps; returns None if the
+    capture fails."""
+    try:
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        return time_calls(g.replay, steps, warmup) / steps
+    except Exception as ex:  # noqa: BLE001
+        sys.stderr.write(f"[bench] CUDA graph capture failed: {ex!r}\n")
+        return None
+
+
 def run_ours(args, rank, local_rank, world):
     import flaggems_sglang_b200 as F
     from flaggems_sglang_b200 import _lib
-    from flaggems_sglang_b200.testing import make_tokens, make_weights
 
     h, i, e, k, dt = WORKLOADS[args.workload]
     dev = torch.device(f"cuda:{local_rank}")
@@ -211,12 +299,14 @@ def run_ours(args, rank, local_rank, world):
         dist.init_process_group("nccl", device_id=dev)
     barrier = (lambda: dist.barrier()) if dist else None
 
-    w13, w2 = make_weights(h, i, e, device=dev, seed=0)
-    m = args.M
+    layer = Layer(args.workload, dev, rank, world)
+    # expert parallelism: M is the global batch, split evenly; otherwise every rank has its own M tokens
+    m = args.M // world if layer.ep else args.M
+    m = max(m, 1)
 
     def make_step(mm, seed):
-        x, tw, ids = make_tokens(mm, h, e, k, device=dev, seed=seed)
-        return x, tw, ids, (lambda: F.fused_experts(x, w13, w2, tw, ids))
+        x, tw, ids = layer.tokens(mm, dev, seed)
+        return x, tw, ids, (lambda: layer.forward(x, tw, ids))
 
     # ---- headline: device-resident inputs
     x, tw, ids, step = make_step(m, rank)
@@ -239,13 +329,26 @@ def run_ours(args, rank, local_rank, world):
     n_calls = max(1, calls.value)
     g1_ms, g2_ms, tot_ms = g1.value / n_calls, g2.value / n_calls, tot.value / n_calls
 
-    hit = int(torch.unique(ids).numel())
-    bytes_alg, flops_alg = algorithmic_work(h, i, k, m, hit)
+    if layer.ep:
+        all_ids = [torch.empty_like(ids) for _ in range(world)]
+        dist.all_gather(all_ids, ids)
+        e_loc = e // world
+        gids = torch.cat(all_ids)
+        hit = int(torch.unique(gids[(gids // e_loc) == rank]).numel())   # experts of this rank that got tokens
+        m_eff, slots = m * world, int(((gids // e_loc) == rank).sum())
+    else:
+        hit = int(torch.unique(ids).numel())
+        m_eff, slots = m, m * k
+    bw = layer.bytes_w
+    bytes_alg, flops_alg = algorithmic_work(h, i, k, m_eff if not layer.ep else slots // k, hit, bw)
     # dominant kernel: the gate/up grouped GEMM (2/3 of the weights and of the flops)
-    g1_flops = 4 * m * k * h * i
-    g1_bytes = hit * 2 * h * i * 2 + m * k * h * 2 + m * k * i * 2
+    g1_flops = 4 * slots * h * i
+    g1_bytes = hit * 2 * h * i * bw + slots * h * bw + slots * i * bw
     t_tensor = g1_flops / (peaks["bf16_tflops"] * 1e12)
     t_hbm = g1_bytes / (peaks["hbm_gbs"] * 1e9)
+    g1_bytes = int(g1_bytes)
+    if bw == 1:
+        t_tensor = 0.0          # FP8 dense peak is not among the measured peaks; this layer is HBM-bound at every M
     if t_tensor >= t_hbm:
         ach = g1_flops / (g1_ms / 1e3) / 1e12
         roof = {"bound": "tensor", "achieved": ach, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
@@ -254,7 +357,9 @@ def run_ours(args, rank, local_rank, world):
         ach = g1_bytes / (g1_ms / 1e3) / 1e9
         roof = {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": ach / peaks["hbm_gbs"]}
-    roof.update({"traffic": NCU_TRAFFIC_BYTES.get((args.workload, m)), "kernel": "moe_gemm_tc_kernel<0> (gate/up + SiLU*mul)",
+    roof.update({"traffic": NCU_TRAFFIC_BYTES.get((args.workload, m)),
+                 "kernel": ("moe_gemm_fp8_kernel<0>" if bw == 1 else "moe_gemm_tc_kernel<0>") + " (gate/up + SiLU*mul)"
+                           + (", int4 dequant warps" if bw == 0.5 else ""),
                  "peak_source": peaks["source"], "kernel_ms": g1_ms, "gemm2_ms": g2_ms, "call_ms": tot_ms,
                  "algorithmic_bytes": g1_bytes, "algorithmic_flops": g1_flops})
 
@@ -267,7 +372,7 @@ def run_ours(args, rank, local_rank, world):
         dx.copy_(hx, non_blocking=True)
         dtw.copy_(htw, non_blocking=True)
         dids.copy_(hids, non_blocking=True)
-        out = F.fused_experts(dx, w13, w2, dtw, dids)
+        out = layer.forward(dx, dtw, dids)
         hout.copy_(out, non_blocking=True)
 
     e2e_steps = max(3, min(args.steps, 20))
@@ -295,18 +400,23 @@ def run_ours(args, rank, local_rank, world):
         for mm in SWEEP_M[args.workload]:
             _, _, ids_m, st = make_step(mm, 0)
             n = max(5, min(args.steps, 30))
-            t_ms = time_calls(st, n, 3) / n
+            t_eager = time_calls(st, n, 3) / n
+            t_graph = time_graph_replays(st, n)
+            t_ms = min(t_eager, t_graph) if t_graph else t_eager
             hit_m = int(torch.unique(ids_m).numel())
-            b, f = algorithmic_work(h, i, k, mm, hit_m)
-            t_roof = max(b / (peaks["hbm_gbs"] * 1e9), f / (peaks["bf16_tflops"] * 1e12))
-            sweep.append({"M": mm, "us": t_ms * 1e3, "tokens_per_s": mm / (t_ms / 1e3), "experts_hit": hit_m,
+            b, f = algorithmic_work(h, i, k, mm, hit_m, bw)
+            t_tc = 0.0 if bw == 1 else f / (peaks["bf16_tflops"] * 1e12)
+            t_roof = max(b / (peaks["hbm_gbs"] * 1e9), t_tc)
+            sweep.append({"M": mm, "us": t_ms * 1e3, "us_eager": t_eager * 1e3,
+                          "us_cuda_graph": t_graph * 1e3 if t_graph else None,
+                          "tokens_per_s": mm / (t_ms / 1e3), "experts_hit": hit_m,
                           "gbs": b / (t_ms / 1e3) / 1e9, "tflops": f / (t_ms / 1e3) / 1e12,
-                          "bound": "hbm" if b / (peaks["hbm_gbs"] * 1e9) >= f / (peaks["bf16_tflops"] * 1e12) else "tensor",
+                          "bound": "hbm" if b / (peaks["hbm_gbs"] * 1e9) >= t_tc else "tensor",
                           "roofline_frac": t_roof / (t_ms / 1e3)})
         F.check_status()
 
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu:
+    if rank == 0 and world == 1 and not args.no_cpu and not layer.fp8 and not layer.int4:
         del x, tw, ids
         cpu = cpu_arm(args, h, i, e, k, m, 3, 1, budget_s=15.0)
         cpu = {kk: cpu[kk] for kk in ("value", "unit", "cores", "kind", "sample")}
@@ -315,10 +425,13 @@ def run_ours(args, rank, local_rank, world):
         line = {
             "metric": "fused_moe_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dt, "data": "synthetic",
+            "higher_is_better": True, "scaling": "strong" if layer.ep else "weak", "vs_baseline": None,
+            "dtype": dt, "data": "synthetic",
             "config": {"workload": f"{args.workload} H{h} I{i} E{e} top{k} M{m} per GPU, layer-layout weights",
-                       "l2": "expert weights (2.8 GB for mixtral) exceed the 126 MB L2; no flush between steps",
-                       "parallelism": "single GPU" if world == 1 else f"{world} independent replicas (no collective)"},
+                       "l2": "expert weights (GBs) exceed the 126 MB L2; no flush between steps",
+                       "parallelism": ("single GPU" if world == 1 else
+                                       f"expert parallel over {world} ranks, all-to-all dispatch/combine, global M {m * world}"
+                                       if layer.ep else f"{world} independent replicas (no collective)")},
             "clocks": clocks.summary(), "e2e": e2e,
             "gpu_launches": 5 * args.steps, "launches_per_step": {"kernels": 5, "memsets": 1},
             "roofline": roof, "cpu_baseline": cpu, "sweep": sweep,

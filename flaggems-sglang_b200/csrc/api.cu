@@ -50,7 +50,8 @@ int make_tmap_2d(CUtensorMap* m, CUtensorMapDataType dt, int elem_bytes, const v
 
 // [experts, rows, inner] tensor, box = {box_inner, box_rows, 1}.
 int make_tmap_3d(CUtensorMap* m, CUtensorMapDataType dt, int elem_bytes, const void* base, uint64_t inner,
-                 uint64_t rows, uint64_t experts, uint32_t box_inner, uint32_t box_rows) {
+                 uint64_t rows, uint64_t experts, uint32_t box_inner, uint32_t box_rows,
+                 CUtensorMapSwizzle swz = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return B200MOE_ERR_CUDA;
   cuuint64_t dims[3] = {inner, rows, experts};
@@ -58,7 +59,7 @@ int make_tmap_3d(CUtensorMap* m, CUtensorMapDataType dt, int elem_bytes, const v
   cuuint32_t box[3] = {box_inner, box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(m, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? B200MOE_OK : B200MOE_ERR_CUDA;
 }
@@ -120,6 +121,10 @@ int check_cfg(const b200moe_cfg* c) {
     if (c->H % 128 != 0 || c->I % 128 != 0) return B200MOE_ERR_UNSUPPORTED;
     if (c->block_tokens != 0 && c->block_tokens != 16 && c->block_tokens != 32 && c->block_tokens != 64)
       return B200MOE_ERR_UNSUPPORTED;
+    if (c->flags & B200MOE_FLAG_SIMT) return B200MOE_ERR_UNSUPPORTED;
+  } else if (c->wmode == B200MOE_W_INT4_AWQ) {
+    if (c->H % 128 != 0 || c->I % 128 != 0) return B200MOE_ERR_UNSUPPORTED;   // whole groups of 128
+    if (c->dtype != B200MOE_DTYPE_FP16) return B200MOE_ERR_UNSUPPORTED;
     if (c->flags & B200MOE_FLAG_SIMT) return B200MOE_ERR_UNSUPPORTED;
   } else {
     return B200MOE_ERR_UNSUPPORTED;
@@ -217,7 +222,9 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
   void* a2 = ws + L.a2;
   float* out32 = reinterpret_cast<float*>(ws + L.out32);
   const bool fp8 = c->wmode == B200MOE_W_FP8_BLOCK;
+  const bool w4 = c->wmode == B200MOE_W_INT4_AWQ;
   int rc;
+  if (w4 && (quant == nullptr || quant->w1_sz == nullptr || quant->w2_sz == nullptr)) return B200MOE_ERR_BAD_ARG;
 
   if (fp8) {
     if (quant == nullptr || quant->w1_scale == nullptr || quant->w2_scale == nullptr) return B200MOE_ERR_BAD_ARG;
@@ -258,6 +265,10 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
     g1.out_q = reinterpret_cast<uint8_t*>(a2);
     g1.out_scale = reinterpret_cast<float*>(ws + L.a2_scale);
   }
+  if (w4) {
+    g1.w_sz = quant->w1_sz;
+    g1.w_rows = 2 * c->I;
+  }
   if (fp8) gemm_plan_fp8(&g1); else gemm_plan(&g1);
 
   GemmArgs g2 = g1;
@@ -268,6 +279,10 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
   g2.out = out32;
   g2.ld_out = c->H;
   g2.max_split = 0;
+  if (w4) {
+    g2.w_sz = quant->w2_sz;
+    g2.w_rows = c->H;
+  }
   if (!fp8 && (c->flags & B200MOE_FLAG_MIMIC_ROUNDING)) {
     if (reference_rounds_pairs(L.P, c->E, c->H, c->I, sms)) g2.flags |= B200MOE_FLAG_NO_SPLIT_K;
     else g2.flags &= ~B200MOE_FLAG_MIMIC_ROUNDING;
@@ -292,10 +307,20 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
     const CUtensorMapDataType dt = tmap_dtype(c->dtype, eb);
     const uint32_t kbox = 128 / eb;
     CUtensorMap tm_w1, tm_x, tm_w2, tm_a2;
-    if ((rc = make_tmap_3d(&tm_w1, dt, eb, w1, c->H, 2ull * c->I, c->E, kbox, 128)) != B200MOE_OK) return rc;
+    if (w4) {
+      // packed int4 rows: K/2 bytes per row, 32 bytes (64 k) per stage, plain row-major staging
+      if ((rc = make_tmap_3d(&tm_w1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w1, c->H / 2, 2ull * c->I, c->E, 32, 128,
+                             CU_TENSOR_MAP_SWIZZLE_NONE)) != B200MOE_OK)
+        return rc;
+      if ((rc = make_tmap_3d(&tm_w2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w2, c->I / 2, c->H, c->E, 32, 128,
+                             CU_TENSOR_MAP_SWIZZLE_NONE)) != B200MOE_OK)
+        return rc;
+    } else {
+      if ((rc = make_tmap_3d(&tm_w1, dt, eb, w1, c->H, 2ull * c->I, c->E, kbox, 128)) != B200MOE_OK) return rc;
+      if ((rc = make_tmap_3d(&tm_w2, dt, eb, w2, c->I, c->H, c->E, kbox, L.orient == 1 ? 256 : 128)) != B200MOE_OK)
+        return rc;
+    }
     if ((rc = make_tmap_2d(&tm_x, dt, eb, xs, c->H, L.cap, kbox, L.BT)) != B200MOE_OK) return rc;
-    if ((rc = make_tmap_3d(&tm_w2, dt, eb, w2, c->I, c->H, c->E, kbox, L.orient == 1 ? 256 : 128)) != B200MOE_OK)
-      return rc;
     if ((rc = make_tmap_2d(&tm_a2, dt, eb, a2, c->I, L.cap, kbox, L.BT)) != B200MOE_OK) return rc;
     prof_mark(slot, 1, st);
     rc = fp8 ? launch_gemm_fp8(tm_w1, tm_x, g1, sms, st) : launch_gemm_tc(tm_w1, tm_x, g1, sms, st);

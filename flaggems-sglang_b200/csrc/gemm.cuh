@@ -39,6 +39,8 @@ struct GemmArgs {
   const float* x_scale;   // [K/128][ld_xscale] group-major activation scales
   int ld_xscale;
   int w_scale_rows;       // scale rows per expert
+  const void* w_sz;       // int4: per (expert, group of 128 k, weight row) fp16 scale | fp16 (1024 + zero)
+  int w_rows;             // int4: weight rows per expert (2I for mode 0, H for mode 1)
   uint8_t* out_q;         // mode 0 FP8: quantised activations [cap, N]
   float* out_scale;       // mode 0 FP8: [N/128][ld_xscale]
 };

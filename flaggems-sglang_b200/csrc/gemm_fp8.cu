@@ -20,6 +20,8 @@ namespace b200moe {
 
 namespace {
 
+constexpr int kMaxKB = 64;  // 128-wide reduction slices per tile whose scales are staged in shared memory
+
 template <int MODE, int BT>
 __global__ void __launch_bounds__(kThreads, 1)
 moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
@@ -43,7 +45,9 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   int* s_col_row = reinterpret_cast<int*>(tmem_slot + 4);               // [2][kMaxBT]
   float* s_col_gam = reinterpret_cast<float*>(s_col_row + 2 * kMaxBT);  // [2][kMaxBT]
   float* s_red = s_col_gam + 2 * kMaxBT;                                // [2][4][64]
-  int* s_blk_off = reinterpret_cast<int*>(s_red + 2 * 4 * 64);          // [E+1]
+  float* s_ws = s_red + 2 * 4 * 64;                                     // [2][2][kMaxKB] weight scales of a tile
+  float* s_xs = s_ws + 2 * 2 * kMaxKB;                                  // [2][kMaxKB][BT] activation scales
+  int* s_blk_off = reinterpret_cast<int*>(s_xs + 2 * kMaxKB * BT);      // [E+1]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -172,6 +176,20 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         col_row[cidx] = valid ? (MODE == 1 ? slot / a.topk : slot) : -1;
         col_gam[cidx] = valid ? a.row_gamma[t.row0 + cidx] : 0.f;
       }
+      // scales of this tile: activations [slice][token], weights [gate|up][slice]
+      const float* wsg = a.w_scale + (static_cast<size_t>(t.e) * a.w_scale_rows + t.n0 / 128) * kb_total;
+      const float* wsu = a.w_scale + (static_cast<size_t>(t.e) * a.w_scale_rows + (a.up_row_off + t.n0) / 128) * kb_total;
+      const int nkb = t.kb1 - t.kb0;
+      float* xs_t = s_xs + buf * kMaxKB * BT;
+      float* ws_t = s_ws + buf * 2 * kMaxKB;
+      for (int idx = ep_tid; idx < nkb * BT; idx += 128) {
+        const int kbl = idx / BT, cc = idx - kbl * BT;
+        xs_t[idx] = a.x_scale[static_cast<size_t>(t.kb0 + kbl) * a.ld_xscale + t.row0 + cc];
+      }
+      for (int idx = ep_tid; idx < nkb; idx += 128) {
+        ws_t[idx] = wsg[t.kb0 + idx];
+        if (MODE == 0) ws_t[kMaxKB + idx] = wsu[t.kb0 + idx];
+      }
       named_bar_sync(1, 128);
 
       float accg[BT], accu[MODE == 0 ? BT : 1];
@@ -181,13 +199,11 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 #pragma unroll
         for (int i = 0; i < BT; ++i) accu[i] = 0.f;
       }
-      const float* wsg = a.w_scale + (static_cast<size_t>(t.e) * a.w_scale_rows + t.n0 / 128) * kb_total;
-      const float* wsu = a.w_scale + (static_cast<size_t>(t.e) * a.w_scale_rows + (a.up_row_off + t.n0) / 128) * kb_total;
 
       for (int kb = t.kb0; kb < t.kb1; ++kb, ++j) {
-        const float swg = __ldg(wsg + kb);
-        const float swu = (MODE == 0) ? __ldg(wsu + kb) : 0.f;
-        const float4* sx = reinterpret_cast<const float4*>(a.x_scale + static_cast<size_t>(kb) * a.ld_xscale + t.row0);
+        const float swg = ws_t[kb - t.kb0];
+        const float swu = (MODE == 0) ? ws_t[kMaxKB + kb - t.kb0] : 0.f;
+        const float4* sx = reinterpret_cast<const float4*>(xs_t + (kb - t.kb0) * BT);
         const uint32_t pb = j & 1u;
         if (!mbar_wait(smem_u32(&bar_pfull[pb]), (j >> 1) & 1u, abort_flag, DEV_TIMEOUT_EPILOGUE)) {
           ok = false;
@@ -202,7 +218,7 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           else tmem_ld16_wait(taddr + c0, g);
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            const float4 s4 = __ldg(sx + c0 / 4 + q);
+            const float4 s4 = sx[c0 / 4 + q];
             const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -272,7 +288,8 @@ size_t fp8_stage_bytes(const GemmArgs& a) {
   return static_cast<size_t>(a.mode == 0 ? 2 : 1) * kTileBytes + static_cast<size_t>(a.BT) * kStageKBytes;
 }
 size_t fp8_ctrl_bytes(const GemmArgs& a) {
-  return 512 + 2 * kMaxBT * 8 + 2 * 4 * 64 * 4 + static_cast<size_t>(a.E + 1) * 4 + 64;
+  return 512 + 2 * kMaxBT * 8 + 2 * 4 * 64 * 4 + 2 * 2 * kMaxKB * 4 + 2 * static_cast<size_t>(kMaxKB) * a.BT * 4 +
+         static_cast<size_t>(a.E + 1) * 4 + 64;
 }
 
 template <int MODE, int BT>
@@ -308,7 +325,7 @@ void gemm_plan_fp8(GemmArgs* a) {
 int launch_gemm_fp8(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmArgs& a, int num_sms,
                     cudaStream_t stream) {
   if (a.wmode != B200MOE_W_FP8_BLOCK) return B200MOE_ERR_BAD_ARG;
-  if (a.K % 128 != 0 || a.N % 128 != 0) return B200MOE_ERR_UNSUPPORTED;
+  if (a.K % 128 != 0 || a.N % 128 != 0 || a.K / 128 > kMaxKB) return B200MOE_ERR_UNSUPPORTED;
 #define B200MOE_FP8_CASE(bt)                                                              \
   case bt:                                                                                \
     return a.mode == 0 ? launch_fp8<0, bt>(tm_w, tm_x, a, num_sms, stream)                \

@@ -50,10 +50,36 @@ __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int MODE, typename T, int ORIENT>
-__global__ void __launch_bounds__(kThreads, 1)
+// Dequantise 32 packed uint4 weights (16 bytes: four words of eight consecutive k, element
+// 2i in nibble i and element 2i+1 in nibble 4+i) into 32 fp16 values = four 16-byte chunks.
+// (w >> 4i) & 0x000F000F | 0x64006400 reads as the fp16 pair (1024 + q_2i, 1024 + q_2i+1);
+// subtracting (1024 + zero) is exact, the product with the scale rounds once.
+__device__ __forceinline__ void dequant_w4x32(const uint4 packed, const __half2 scale, const __half2 zero1024,
+                                              uint4 (&out)[4]) {
+  const uint32_t w[4] = {packed.x, packed.y, packed.z, packed.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t r[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint32_t t = ((w[j] >> (4 * i)) & 0x000F000Fu) | 0x64006400u;
+      __half2 h = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&t), zero1024), scale);
+      r[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    out[j] = make_uint4(r[0], r[1], r[2], r[3]);
+  }
+}
+
+constexpr int kDequantWarps = 8;
+constexpr int kThreadsW4 = kThreads + 32 * kDequantWarps;
+
+// W4: the weight operand is int4 (AWQ, group 128, pre-packed): TMA stages the packed rows,
+// eight extra warps dequantise them into the swizzled fp16 operand tile the MMA reads.
+template <int MODE, typename T, int ORIENT, bool W4>
+__global__ void __launch_bounds__(W4 ? kThreadsW4 : kThreads, 1)
 moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                    const GemmArgs a) {
+  static_assert(!(W4 && ORIENT == 1), "int4 weights use the weights-on-M orientation");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -61,13 +87,15 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   constexpr int W_BYTES = G::kWBytes;
   const int BT = a.BT;
   const int x_bytes = BT * kStageKBytes;
-  const int stage_bytes = W_BYTES + x_bytes;
+  constexpr int PK_BYTES = W4 ? W_BYTES / 4 : 0;  // packed int4 rows: 32 bytes per row and stage
+  const int stage_bytes = W_BYTES + x_bytes + PK_BYTES;
   const int stages = a.stages;
 
   uint8_t* ctrl_base = smem + static_cast<size_t>(stages) * stage_bytes;
   uint64_t* bar_full = reinterpret_cast<uint64_t*>(ctrl_base);
   uint64_t* bar_empty = bar_full + stages;
-  uint64_t* bar_tfull = bar_empty + stages;
+  uint64_t* bar_dq = bar_empty + stages;  // W4: operand tile dequantised
+  uint64_t* bar_tfull = bar_dq + stages;
   uint64_t* bar_tempty = bar_tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -82,6 +110,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     for (int s = 0; s < stages; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);
+      mbar_init(smem_u32(&bar_dq[s]), kDequantWarps);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(smem_u32(&bar_tfull[s]), 1);
@@ -121,11 +150,19 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
           break;
         }
         const uint32_t full = smem_u32(&bar_full[stage]);
-        mbar_arrive_expect_tx(full, static_cast<uint32_t>(stage_bytes));
         const uint32_t sw = smem_u32(smem + static_cast<size_t>(stage) * stage_bytes);
         const int k0 = kb * (kStageKBytes / static_cast<int>(sizeof(T)));
-        tma_load_3d(sw, &tm_w, full, k0, t.n0, t.e);
-        if (MODE == 0) tma_load_3d(sw + kTileBytes, &tm_w, full, k0, a.up_row_off + t.n0, t.e);
+        if (W4) {
+          // packed rows: 64 k = 32 bytes per row, 128 rows per box, no swizzle
+          mbar_arrive_expect_tx(full, static_cast<uint32_t>(PK_BYTES + x_bytes));
+          const uint32_t spk = sw + W_BYTES + x_bytes;
+          tma_load_3d(spk, &tm_w, full, kb * 32, t.n0, t.e);
+          if (MODE == 0) tma_load_3d(spk + kTileRows * 32, &tm_w, full, kb * 32, a.up_row_off + t.n0, t.e);
+        } else {
+          mbar_arrive_expect_tx(full, static_cast<uint32_t>(stage_bytes));
+          tma_load_3d(sw, &tm_w, full, k0, t.n0, t.e);
+          if (MODE == 0) tma_load_3d(sw + kTileBytes, &tm_w, full, k0, a.up_row_off + t.n0, t.e);
+        }
         tma_load_2d(sw + W_BYTES, &tm_x, full, k0, t.row0);
         ++issued;
         if (++stage == stages) {
@@ -161,7 +198,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       tc_fence_after();
       const uint32_t d0 = tmem_base + static_cast<uint32_t>(acc * cols_per_acc);
       for (int kb = t.kb0; kb < t.kb1; ++kb) {
-        if (!mbar_wait(smem_u32(&bar_full[stage]), phase, abort_flag, DEV_TIMEOUT_MMA)) {
+        if (!mbar_wait(smem_u32(W4 ? &bar_dq[stage] : &bar_full[stage]), phase, abort_flag, DEV_TIMEOUT_MMA)) {
           ok = false;
           break;
         }
@@ -196,7 +233,57 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         acc_phase ^= 1;
       }
     }
-  } else if (active && warp >= 2) {
+  } else if (W4 && active && warp >= 6) {
+    // =============================== int4 -> fp16 operand tile ==================
+    constexpr int ROWS = (MODE == 0 ? 2 : 1) * kTileRows;        // packed rows per stage
+    constexpr int UNITS_PER_THREAD = ROWS * 2 / (32 * kDequantWarps);  // 16-byte units per thread (2 or 1)
+    const int dt = threadIdx.x - 6 * 32;                          // 0..255
+    const int row = (UNITS_PER_THREAD == 2) ? dt : (dt >> 1);     // packed row this thread converts
+    const int half0 = (UNITS_PER_THREAD == 2) ? 0 : (dt & 1);
+    const uint32_t* sz = reinterpret_cast<const uint32_t*>(a.w_sz);
+    const int groups = (a.K + 127) / 128;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < c.total; tile += c.grid_eff) {
+      const TileCoord t = decode_tile(tile, c, s_blk_off, a.E, BT, a.num_nt, a.kblocks, G::kTileN);
+      // output row of this packed row inside the expert (gate rows first, then the up rows)
+      const int n = (row < kTileRows) ? t.n0 + row : a.up_row_off + t.n0 + (row - kTileRows);
+      const bool n_ok = n < a.w_rows;
+      const uint32_t* szrow = sz + static_cast<size_t>(t.e) * groups * a.w_rows + n;
+      for (int kb = t.kb0; kb < t.kb1; ++kb) {
+        uint32_t szv = 0;
+        if (n_ok) szv = __ldg(szrow + static_cast<size_t>(kb >> 1) * a.w_rows);
+        if (!mbar_wait(smem_u32(&bar_full[stage]), phase, abort_flag, DEV_TIMEOUT_MMA)) {
+          ok = false;
+          break;
+        }
+        const __half2 sc = __half2half2(__ushort_as_half(static_cast<unsigned short>(szv & 0xFFFFu)));
+        const __half2 zp = __half2half2(__ushort_as_half(static_cast<unsigned short>(szv >> 16)));
+        uint8_t* sbase = smem + static_cast<size_t>(stage) * stage_bytes;
+        const uint4* pk = reinterpret_cast<const uint4*>(sbase + W_BYTES + x_bytes + row * 32);
+        uint8_t* orow = sbase + (row >> 7) * kTileBytes + (row & 127) * kStageKBytes;
+#pragma unroll
+        for (int u = 0; u < UNITS_PER_THREAD; ++u) {
+          const int half = half0 + u;
+          uint4 o[4];
+          dequant_w4x32(pk[half], sc, zp, o);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int chunk = (half * 4 + j) ^ (row & 7);   // 128-byte swizzle of the operand tile
+            *reinterpret_cast<uint4*>(orow + chunk * 16) = o[j];
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_dq[stage]));
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else if (active && warp >= 2 && warp < 6) {
     // =============================== epilogue ===================================
     const int quad = warp & 3;                  // TMEM lane quadrant this warp may read
     const int ep_tid = (warp - 2) * 32 + lane;  // 0..127
@@ -328,11 +415,12 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 
 static size_t stage_bytes_of(const GemmArgs& a) {
   const size_t w = (a.orient == 1) ? 2 * kTileBytes : static_cast<size_t>(a.mode == 0 ? 2 : 1) * kTileBytes;
-  return w + static_cast<size_t>(a.BT) * kStageKBytes;
+  const size_t packed = (a.wmode == B200MOE_W_INT4_AWQ) ? w / 4 : 0;
+  return w + packed + static_cast<size_t>(a.BT) * kStageKBytes;
 }
 
 static size_t ctrl_bytes_of(const GemmArgs& a) {
-  return 512 /*barriers*/ + 2 * kMaxBT * 8 + static_cast<size_t>(a.E + 1) * 4 + 64;
+  return 768 /*barriers*/ + 2 * kMaxBT * 8 + static_cast<size_t>(a.E + 1) * 4 + 64;
 }
 
 void gemm_plan(GemmArgs* a) {
@@ -357,16 +445,16 @@ size_t gemm_smem_bytes(const GemmArgs& a) {
   return 1024 + static_cast<size_t>(a.stages) * stage_bytes_of(a) + ctrl_bytes_of(a);
 }
 
-template <int MODE, typename T, int ORIENT>
+template <int MODE, typename T, int ORIENT, bool W4 = false>
 static int launch_one(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmArgs& a, int num_sms,
                       cudaStream_t stream) {
   const size_t smem = gemm_smem_bytes(a);
   if (smem > kSmemLimit) return B200MOE_ERR_TOO_LARGE;
-  cudaError_t err = cudaFuncSetAttribute(moe_gemm_tc_kernel<MODE, T, ORIENT>,
+  cudaError_t err = cudaFuncSetAttribute(moe_gemm_tc_kernel<MODE, T, ORIENT, W4>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem));
   if (err != cudaSuccess) return B200MOE_ERR_CUDA;
-  moe_gemm_tc_kernel<MODE, T, ORIENT><<<num_sms, kThreads, smem, stream>>>(tm_w, tm_x, a);
+  moe_gemm_tc_kernel<MODE, T, ORIENT, W4><<<num_sms, W4 ? kThreadsW4 : kThreads, smem, stream>>>(tm_w, tm_x, a);
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
 }
 
@@ -384,6 +472,11 @@ int launch_gemm_tc(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmA
                    cudaStream_t stream) {
   if (a.BT < 16 || a.BT > kMaxBT || a.BT % 16 != 0) return B200MOE_ERR_BAD_ARG;
   if (a.orient == 1 && a.BT != 128) return B200MOE_ERR_BAD_ARG;
+  if (a.wmode == B200MOE_W_INT4_AWQ) {
+    if (a.orient != 0 || a.dtype != B200MOE_DTYPE_FP16 || a.w_sz == nullptr) return B200MOE_ERR_UNSUPPORTED;
+    return a.mode == 0 ? launch_one<0, __half, 0, true>(tm_w, tm_x, a, num_sms, stream)
+                       : launch_one<1, __half, 0, true>(tm_w, tm_x, a, num_sms, stream);
+  }
   if (a.wmode != B200MOE_W_16BIT) return B200MOE_ERR_UNSUPPORTED;
   if (a.dtype == B200MOE_DTYPE_BF16) return launch_typed<__nv_bfloat16>(tm_w, tm_x, a, num_sms, stream);
   return launch_typed<__half>(tm_w, tm_x, a, num_sms, stream);

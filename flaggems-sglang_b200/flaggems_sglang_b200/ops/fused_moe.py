@@ -77,6 +77,16 @@ def _layer_layout(w: torch.Tensor) -> torch.Tensor:
     return ent[2]
 
 
+def _awq_repacked(qweight: torch.Tensor, scales: torch.Tensor, qzeros: torch.Tensor):
+    """AWQ checkpoint tensors -> kernel layout, once per qweight tensor object."""
+    from ..quant import repack_awq_for_kernel
+    ent = _relayout.get(qweight)
+    if ent is None or ent[0] != qweight._version or ent[1] != qweight.data_ptr():
+        ent = (qweight._version, qweight.data_ptr(), repack_awq_for_kernel(qweight, scales, qzeros))
+        _relayout[qweight] = ent
+    return ent[2]
+
+
 def _make_cfg(m, h, i, e, k, dtype, wmode, activation, flags, block_tokens, routed_scaling) -> _lib.Cfg:
     return _lib.Cfg(C.sizeof(_lib.Cfg), m, h, i, e, k, dtype, wmode, _lib.LAYOUT_LAYER, activation, flags,
                     block_tokens, routed_scaling, 0)
@@ -115,8 +125,15 @@ def fused_experts(
     use_fp8_w8a8: bool = False,
     w13_scale: Optional[torch.Tensor] = None,
     w2_scale: Optional[torch.Tensor] = None,
+    use_int4_w4a16: bool = False,
+    w13_sz: Optional[torch.Tensor] = None,
+    w2_sz: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """Fused experts on layer-layout weights ``w13 [E, 2I, H]``, ``w2 [E, H, I]``.
+
+    ``use_int4_w4a16``: ``w13`` / ``w2`` are the packed int4 rows ``[E, 2I, H/8]`` /
+    ``[E, H, I/8]`` int32 and ``w13_sz`` / ``w2_sz`` the scale/zero tables from
+    ``quant.repack_awq_for_kernel``; activations must be fp16.
 
     Routing is either ``(topk_weights [M, k], topk_ids [M, k])`` or
     ``routing=(hist [E], topk_indx [P], gate_scal [P])`` taken from the
@@ -131,8 +148,9 @@ def fused_experts(
     m, h = x.shape
     e, two_i, hw = w13.shape
     i = two_i // 2
-    assert hw == h, "hidden size mismatch"
-    assert w2.shape[0] == e and w2.shape[1] == h and w2.shape[2] == i, "intermediate size mismatch"
+    pack = 8 if use_int4_w4a16 else 1
+    assert hw * pack == h, "hidden size mismatch"
+    assert w2.shape[0] == e and w2.shape[1] == h and w2.shape[2] * pack == i, "intermediate size mismatch"
     assert w13.is_contiguous() and w2.is_contiguous(), "weights must be contiguous"
     dtype = _DTYPES[x.dtype]
 
@@ -151,6 +169,15 @@ def fused_experts(
         s1 = w13_scale.to(torch.float32).contiguous()
         s2 = w2_scale.to(torch.float32).contiguous()
         quant = _lib.Quant(s1.data_ptr(), s2.data_ptr(), None, None)
+    elif use_int4_w4a16:
+        wmode = _lib.W_INT4_AWQ
+        assert x.dtype == torch.float16, "int4 w4a16 takes fp16 activations"
+        assert w13.dtype == torch.int32 and w2.dtype == torch.int32, "packed int4 weights must be int32"
+        assert w13_sz is not None and w2_sz is not None, "scale/zero tables are required"
+        assert w13_sz.dtype == torch.int32 and w13_sz.shape == (e, h // 128, 2 * i), "w13_sz must be [E, H/128, 2I] int32"
+        assert w2_sz.dtype == torch.int32 and w2_sz.shape == (e, i // 128, h), "w2_sz must be [E, I/128, H] int32"
+        z1, z2 = w13_sz.contiguous(), w2_sz.contiguous()
+        quant = _lib.Quant(None, None, z1.data_ptr(), z2.data_ptr())
     else:
         assert w13.dtype == x.dtype and w2.dtype == x.dtype, "weights must have the activation dtype"
 
@@ -224,6 +251,11 @@ def triton_kernel_fused_experts(
     a1_scale: Optional[torch.Tensor] = None,
     a2_scale: Optional[torch.Tensor] = None,
     block_shape: Optional[list[int]] = None,
+    *,
+    use_int4_w4a16: bool = False,
+    w1_zp: Optional[torch.Tensor] = None,
+    w2_zp: Optional[torch.Tensor] = None,
+    group_size: int = 128,
 ) -> torch.Tensor:
     """Same signature and results as the reference's op
     (src/flaggems_sglang/ops/fused_moe.py:133-216): ``w1 [E, H, 2I]``,
@@ -231,7 +263,11 @@ def triton_kernel_fused_experts(
 
     Beyond the reference: ``use_fp8_w8a8=True`` with ``w1_scale``/``w2_scale``
     and ``block_shape=[128, 128]`` runs the block-quantised FP8 path (weights
-    then come in layer layout ``[E, 2I, H]`` / ``[E, H, I]``).
+    then come in layer layout ``[E, 2I, H]`` / ``[E, H, I]``).  Keyword-only
+    ``use_int4_w4a16=True`` takes AWQ checkpoint tensors: ``w1`` / ``w2`` =
+    qweight ``[E, K, N/8]`` int32, ``w1_scale`` / ``w2_scale`` = fp16 scales
+    ``[E, K/128, N]``, ``w1_zp`` / ``w2_zp`` = qzeros ``[E, K/128, N/8]`` (K the
+    reduction dim), fp16 activations; they are repacked once per tensor object.
     """
     logger.debug("FLAGGEMS_SGLANG FUSED_MOE")
     assert per_channel_quant is False, _UNSUPPORTED_FEATURE_MSG.format(name="per_channel_quant")
@@ -245,6 +281,17 @@ def triton_kernel_fused_experts(
 
     top_k = routing_data.n_expts_act
     routing = (routing_data.expt_hist, gather_indx.src_indx, routing_data.gate_scal, top_k)
+
+    if use_int4_w4a16:
+        assert group_size == 128, "only group_size 128 is supported"
+        assert hidden_states.dtype == torch.float16, "int4 w4a16 takes fp16 activations"
+        assert w1_scale is not None and w2_scale is not None and w1_zp is not None and w2_zp is not None, \
+            "scales and zero points are required"
+        p1, z1 = _awq_repacked(w1, w1_scale, w1_zp)
+        p2, z2 = _awq_repacked(w2, w2_scale, w2_zp)
+        return fused_experts(hidden_states, p1, p2, routing=routing, activation=activation,
+                             apply_router_weight_on_input=apply_router_weight_on_input,
+                             use_int4_w4a16=True, w13_sz=z1, w2_sz=z2)
 
     if use_fp8_w8a8:
         assert block_shape is not None and list(block_shape) == [128, 128], "block_shape must be [128, 128]"

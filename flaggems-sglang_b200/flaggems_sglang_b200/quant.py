@@ -52,3 +52,41 @@ def pack_awq(v: torch.Tensor) -> torch.Tensor:
         out += (g[..., j] & 0xF) << sh
     out = torch.where(out >= 2 ** 31, out - 2 ** 32, out)
     return out.to(torch.int32)
+
+
+def unpack_awq(p: torch.Tensor) -> torch.Tensor:
+    """int32 [..., R, N/8] in the AWQ nibble order -> int32 values 0..15 [..., R, N]."""
+    u = p.to(torch.int64) & 0xFFFFFFFF
+    cols = [((u >> sh) & 0xF) for sh in _AWQ_SHIFTS]
+    return torch.stack(cols, dim=-1).reshape(*p.shape[:-1], p.shape[-1] * 8).to(torch.int32)
+
+
+def repack_awq_for_kernel(qweight: torch.Tensor, scales: torch.Tensor, qzeros: torch.Tensor, group: int = 128):
+    """AWQ checkpoint tensors -> the layout the int4 kernels stream (one-time set-up).
+
+    qweight [E, K, N/8] int32, scales [E, K/g, N] fp16, qzeros [E, K/g, N/8] int32
+    (K = reduction dim, N = output dim) become
+
+      wp [E, N, K/8] int32   one output row per line, reduction dim contiguous; a word
+                             holds eight consecutive k: element 2i in nibble i, element
+                             2i+1 in nibble 4+i, so that (w >> 4i) & 0x000F000F is the
+                             adjacent pair (2i, 2i+1) as two 16-bit lanes;
+      sz [E, K/g, N] int32   per (group, output row): fp16 scale in the low half,
+                             fp16(1024 + zero) in the high half.
+    """
+    assert group == 128
+    e, k, n8 = qweight.shape
+    n = n8 * 8
+    q = unpack_awq(qweight).transpose(1, 2).contiguous()          # [E, N, K]
+    g8 = q.view(e, n, k // 8, 8).to(torch.int64)
+    wp = torch.zeros(e, n, k // 8, dtype=torch.int64, device=q.device)
+    for i in range(4):
+        wp += (g8[..., 2 * i] & 0xF) << (4 * i)
+        wp += (g8[..., 2 * i + 1] & 0xF) << (16 + 4 * i)
+    wp = torch.where(wp >= 2 ** 31, wp - 2 ** 32, wp).to(torch.int32)
+    z = unpack_awq(qzeros).to(torch.float16) + 1024.0              # [E, K/g, N], exact in fp16
+    s_bits = scales.to(torch.float16).contiguous().view(torch.int16).to(torch.int64) & 0xFFFF
+    z_bits = z.contiguous().view(torch.int16).to(torch.int64) & 0xFFFF
+    sz = s_bits | (z_bits << 16)
+    sz = torch.where(sz >= 2 ** 31, sz - 2 ** 32, sz).to(torch.int32)
+    return wp.contiguous(), sz.contiguous()

@@ -37,15 +37,27 @@ def zipf_bias(n_experts: int, s: float = 1.1, seed: int = 0) -> torch.Tensor:
     return bias
 
 
-def make_weights(h: int, i: int, e: int, dtype=torch.bfloat16, device="cpu", scale=0.02, seed=0):
+def make_weights(h: int, i: int, e: int, dtype=torch.bfloat16, device="cpu", scale=0.02, seed=0,
+                 expert_ids=None):
     """Layer-layout weights w13 [E, 2I, H], w2 [E, H, I] ~ randn * scale, generated
-    expert by expert on the target device."""
-    g = torch.Generator(device=device).manual_seed(seed)
-    w13 = torch.empty(e, 2 * i, h, dtype=dtype, device=device)
-    w2 = torch.empty(e, h, i, dtype=dtype, device=device)
-    for ei in range(e):
-        w13[ei] = (torch.randn(2 * i, h, generator=g, device=device, dtype=torch.float32) * scale).to(dtype)
-        w2[ei] = (torch.randn(h, i, generator=g, device=device, dtype=torch.float32) * scale).to(dtype)
+    expert by expert on the target device.  With ``expert_ids`` only those experts
+    are generated, each from its own seed, so that an expert-parallel shard holds
+    the same values whatever the number of ranks."""
+    if expert_ids is None:
+        g = torch.Generator(device=device).manual_seed(seed)
+        w13 = torch.empty(e, 2 * i, h, dtype=dtype, device=device)
+        w2 = torch.empty(e, h, i, dtype=dtype, device=device)
+        for ei in range(e):
+            w13[ei] = (torch.randn(2 * i, h, generator=g, device=device, dtype=torch.float32) * scale).to(dtype)
+            w2[ei] = (torch.randn(h, i, generator=g, device=device, dtype=torch.float32) * scale).to(dtype)
+        return w13, w2
+    ids = list(expert_ids)
+    w13 = torch.empty(len(ids), 2 * i, h, dtype=dtype, device=device)
+    w2 = torch.empty(len(ids), h, i, dtype=dtype, device=device)
+    for j, ei in enumerate(ids):
+        g = torch.Generator(device=device).manual_seed(seed * 1000003 + ei + 1)
+        w13[j] = (torch.randn(2 * i, h, generator=g, device=device, dtype=torch.float32) * scale).to(dtype)
+        w2[j] = (torch.randn(h, i, generator=g, device=device, dtype=torch.float32) * scale).to(dtype)
     return w13, w2
 
 

@@ -39,7 +39,7 @@ extern "C" {
 /* weight storage */
 #define B200MOE_W_16BIT 0     /* same 16-bit type as the activations               */
 #define B200MOE_W_FP8_BLOCK 1 /* e4m3fn, fp32 scale per 128x128 block              */
-#define B200MOE_W_INT4_AWQ 2  /* uint4 g128, packed by b200moe_awq_repack           */
+#define B200MOE_W_INT4_AWQ 2  /* uint4 g128 in the kernel layout (see b200moe_quant)  */
 
 /* weight layout (16-bit weights only) */
 #define B200MOE_LAYOUT_LAYER 0 /* w1 [E,2I,H], w2 [E,H,I]: reduction dim contiguous */
@@ -77,7 +77,11 @@ typedef struct b200moe_cfg {
 typedef struct b200moe_quant {
   const float *w1_scale;  /* FP8: [E, ceil(2I/128), ceil(H/128)]                 */
   const float *w2_scale;  /* FP8: [E, ceil(H/128), ceil(I/128)]                  */
-  const void *w1_sz;      /* AWQ: repacked scale/zero table from b200moe_awq_repack */
+  /* int4 AWQ (fp16 activations).  w1 / w2 then point at packed rows [E, rows, K/8] int32,
+   * one output row per line, eight consecutive k per word (element 2i in nibble i, element
+   * 2i+1 in nibble 4+i); w*_sz are [E, K/128, rows] int32 = fp16 scale | fp16(1024 + zero) << 16.
+   * flaggems_sglang_b200.quant.repack_awq_for_kernel builds both from AWQ checkpoint tensors. */
+  const void *w1_sz;
   const void *w2_sz;
 } b200moe_quant;
 

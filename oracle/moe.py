@@ -108,7 +108,7 @@ def fused_experts(
     k = topk_ids.shape[1]
     out_dtype = out_dtype or x.dtype
     if round_y2 is None:
-        i_dim = (w2.shape[2] if hasattr(w2, "shape") else None)
+        i_dim = (w2.shape[2] if hasattr(w2, "shape") else getattr(w2, "i_dim", None))
         round_y2 = mimic_rounding and (i_dim is None or reference_rounds_pairs(m * k, _n_local(w1), h, i_dim))
     n_local = w1.shape[0] if hasattr(w1, "shape") else w1.n_experts
     get1 = (lambda e: w1[e].float()) if hasattr(w1, "shape") else w1
@@ -157,8 +157,9 @@ def fused_experts(
 
 # ------------------------------------------------------------------ quantised variants
 class _LazyWeights:
-    def __init__(self, n_experts, fn):
+    def __init__(self, n_experts, fn, i_dim=None):
         self.n_experts = n_experts
+        self.i_dim = i_dim
         self._fn = fn
 
     def __call__(self, e):
@@ -187,5 +188,6 @@ def fused_experts_awq(x, w1_qweight, w1_scales, w1_qzeros, w2_qweight, w2_scales
     [E, K/g, N] fp16, qzeros [E, K/g, N/8] int32; fp16 activations."""
     e = w1_qweight.shape[0]
     w1 = _LazyWeights(e, lambda i: Q.dequant_weight_awq(w1_qweight[i], w1_scales[i], w1_qzeros[i], group).t())
-    w2 = _LazyWeights(e, lambda i: Q.dequant_weight_awq(w2_qweight[i], w2_scales[i], w2_qzeros[i], group).t())
+    w2 = _LazyWeights(e, lambda i: Q.dequant_weight_awq(w2_qweight[i], w2_scales[i], w2_qzeros[i], group).t(),
+                      i_dim=w2_qweight.shape[1])
     return fused_experts(x, w1, w2, topk_weights, topk_ids, **kw)

@@ -1,0 +1,77 @@
+"""GPU (two or more devices): expert parallelism end to end — NCCL all-to-all
+dispatch, the CUDA fused experts on each rank's share, all-to-all combine —
+against the single-process oracle over all experts."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, fp8, ret):
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    for p in (root, root / "flaggems-sglang_b200", root / "tests"):
+        sys.path.insert(0, str(p))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dev = torch.device(f"cuda:{rank}")
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import flaggems_sglang_b200 as F
+        from flaggems_sglang_b200.ep import ep_fused_experts
+        from flaggems_sglang_b200.quant import quantize_fp8_block
+        from flaggems_sglang_b200.testing import make_tokens, make_weights
+        from oracle import moe as OM
+        h, i, e, k, m = 512, 256, 16, 4, 24
+        e_loc = e // world
+        w13, w2 = make_weights(h, i, e, seed=0)
+        x, tw, ids = make_tokens(m, h, e, k, seed=10 + rank, skew=True)
+        lo, hi = rank * e_loc, (rank + 1) * e_loc
+        if fp8:
+            w13q, s13 = quantize_fp8_block(w13)
+            w2q, s2 = quantize_fp8_block(w2)
+            out = ep_fused_experts(x.to(dev), w13q[lo:hi].contiguous().to(dev), w2q[lo:hi].contiguous().to(dev),
+                                   tw.to(dev), ids.to(dev), use_fp8_w8a8=True,
+                                   w13_scale=s13[lo:hi].contiguous().to(dev), w2_scale=s2[lo:hi].contiguous().to(dev))
+            ref = OM.fused_experts_fp8(x, w13q, w2q, s13, s2, tw, ids).float()
+        else:
+            out = ep_fused_experts(x.to(dev), w13[lo:hi].contiguous().to(dev), w2[lo:hi].contiguous().to(dev),
+                                   tw.to(dev), ids.to(dev), mimic_reference_rounding=False)
+            ref = OM.fused_experts(x, w13, w2, tw, ids, mimic_rounding=False).float()
+        torch.cuda.synchronize()
+        F.check_status()
+        err = (out.float().cpu() - ref).abs()
+        # the per-rank partial sums are rounded to bf16 before the combine: allow for it
+        ret[rank] = (float(err.max()), float(ref.abs().max()), float((err <= 2e-2 + 2e-2 * ref.abs()).float().mean()))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("fp8", [False, True], ids=["bf16", "fp8"])
+def test_ep_two_gpus(fp8):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    port = _free_port()
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_worker, args=(world, port, fp8, ret), nprocs=world, join=True)
+        assert len(ret) == world
+        for r in range(world):
+            max_err, scale, frac = ret[r]
+            assert frac >= 0.99 and max_err <= 2e-2 * max(1.0, scale) + 2e-2 * scale, (r, ret[r])
