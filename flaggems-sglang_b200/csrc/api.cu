@@ -223,16 +223,18 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
   float* out32 = reinterpret_cast<float*>(ws + L.out32);
   const bool fp8 = c->wmode == B200MOE_W_FP8_BLOCK;
   const bool w4 = c->wmode == B200MOE_W_INT4_AWQ;
+  const bool pdl = (c->flags & B200MOE_FLAG_NO_PDL) == 0;
   int rc;
   if (w4 && (quant == nullptr || quant->w1_sz == nullptr || quant->w2_sz == nullptr)) return B200MOE_ERR_BAD_ARG;
 
   if (fp8) {
     if (quant == nullptr || quant->w1_scale == nullptr || quant->w2_scale == nullptr) return B200MOE_ERR_BAD_ARG;
     rc = launch_group_quant_fp8(x, c->dtype, xs, reinterpret_cast<float*>(ws + L.xs_scale), sorted_ids, meta,
-                                L.P, c->topk, L.cap, c->H, 1, L.cap, sms, st);
+                                L.P, c->topk, L.cap, c->H, 1, L.cap, out32, static_cast<size_t>(c->M) * c->H * 4,
+                                sms, st, pdl);
   } else {
     rc = launch_gather_rows(x, xs, sorted_ids, meta, L.P, c->topk, c->H * 2, L.cap, out32,
-                            static_cast<size_t>(c->M) * c->H * 4, sms, st);
+                            static_cast<size_t>(c->M) * c->H * 4, sms, st, pdl);
   }
   if (rc != B200MOE_OK) return rc;
 
@@ -257,6 +259,7 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
   g1.out = a2;
   g1.ld_out = c->I;
   g1.status = status;
+  g1.pdl = pdl ? 1 : 0;
   if (fp8) {
     g1.w_scale = quant->w1_scale;
     g1.w_scale_rows = (2 * c->I + 127) / 128;
@@ -326,14 +329,12 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
     rc = fp8 ? launch_gemm_fp8(tm_w1, tm_x, g1, sms, st) : launch_gemm_tc(tm_w1, tm_x, g1, sms, st);
     prof_mark(slot, 2, st);
     if (rc != B200MOE_OK) return rc;
-    if (fp8 && cudaMemsetAsync(out32, 0, static_cast<size_t>(c->M) * c->H * 4, st) != cudaSuccess)
-      return B200MOE_ERR_CUDA;
     prof_mark(slot, 3, st);
     rc = fp8 ? launch_gemm_fp8(tm_w2, tm_a2, g2, sms, st) : launch_gemm_tc(tm_w2, tm_a2, g2, sms, st);
     prof_mark(slot, 4, st);
     if (rc != B200MOE_OK) return rc;
   }
-  rc = launch_finalize(out32, out, c->dtype, static_cast<size_t>(c->M) * c->H, c->routed_scaling, sms, st);
+  rc = launch_finalize(out32, out, c->dtype, static_cast<size_t>(c->M) * c->H, c->routed_scaling, sms, st, pdl);
   prof_mark(slot, 5, st);
   return rc;
 }
@@ -557,8 +558,8 @@ int b200moe_per_token_group_quant_fp8(const void* x, int dtype, int rows, int K,
   if (rows < 0 || K <= 0 || !x || !q || !scales) return B200MOE_ERR_BAD_ARG;
   if (dtype != B200MOE_DTYPE_BF16 && dtype != B200MOE_DTYPE_FP16) return B200MOE_ERR_BAD_ARG;
   if (rows == 0) return B200MOE_OK;
-  return launch_group_quant_fp8(x, dtype, q, scales, nullptr, nullptr, 0, 1, rows, K, 0, 0, 148,
-                                static_cast<cudaStream_t>(stream));
+  return launch_group_quant_fp8(x, dtype, q, scales, nullptr, nullptr, 0, 1, rows, K, 0, 0, nullptr, 0, 148,
+                                static_cast<cudaStream_t>(stream), false);
 }
 
 }  // extern "C"

@@ -27,6 +27,7 @@ struct GemmArgs {
   int flags;       // B200MOE_FLAG_*
   int activation;  // B200MOE_ACT_*
   int max_split;   // mode 1: upper bound for the reduction split
+  int pdl;         // launch with programmatic stream serialisation
   const int* meta;        // [0] = token blocks, [1] = padded rows
   const int* blk_off;     // [E+1] first block of each expert
   const int* sorted_ids;  // [cap] slot of each padded row (>= P: padding)

@@ -71,6 +71,10 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     tmem_alloc(smem_u32(tmem_slot), static_cast<uint32_t>(a.tmem_cols));
     tmem_relinquish();
   }
+  // everything above touched only shared / tensor memory and kernel parameters; the routing
+  // tables and activations below come from the preceding kernels
+  griddep_wait();
+  griddep_launch_dependents();
   for (int e = threadIdx.x; e <= a.E; e += blockDim.x) s_blk_off[e] = a.blk_off[e];
   tc_fence_before();
   __syncthreads();
@@ -300,8 +304,9 @@ int launch_fp8(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmArgs&
   if (cudaFuncSetAttribute(moe_gemm_fp8_kernel<MODE, BT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(smem)) != cudaSuccess)
     return B200MOE_ERR_CUDA;
-  moe_gemm_fp8_kernel<MODE, BT><<<num_sms, kThreads, smem, stream>>>(tm_w, tm_x, a);
-  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
+  cudaError_t err = launch_kernel(moe_gemm_fp8_kernel<MODE, BT>, dim3(num_sms), dim3(kThreads), smem, stream,
+                                  a.pdl != 0, tm_w, tm_x, a);
+  return err == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
 }
 
 }  // namespace

@@ -126,6 +126,10 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     tmem_alloc(smem_u32(tmem_slot), static_cast<uint32_t>(a.tmem_cols));
     tmem_relinquish();
   }
+  // everything above touched only shared / tensor memory and kernel parameters; the routing
+  // tables and activations below come from the preceding kernels
+  griddep_wait();
+  griddep_launch_dependents();
   for (int e = threadIdx.x; e <= a.E; e += blockDim.x) s_blk_off[e] = a.blk_off[e];
   tc_fence_before();
   __syncthreads();
@@ -454,8 +458,9 @@ static int launch_one(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const Ge
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem));
   if (err != cudaSuccess) return B200MOE_ERR_CUDA;
-  moe_gemm_tc_kernel<MODE, T, ORIENT, W4><<<num_sms, W4 ? kThreadsW4 : kThreads, smem, stream>>>(tm_w, tm_x, a);
-  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
+  err = launch_kernel(moe_gemm_tc_kernel<MODE, T, ORIENT, W4>, dim3(num_sms), dim3(W4 ? kThreadsW4 : kThreads), smem,
+                      stream, a.pdl != 0, tm_w, tm_x, a);
+  return err == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
 }
 
 template <typename T>

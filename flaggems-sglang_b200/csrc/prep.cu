@@ -14,6 +14,8 @@ __global__ void __launch_bounds__(256)
 gather_rows_kernel(const uint4* __restrict__ x, uint4* __restrict__ xs, const int* __restrict__ sorted_ids,
                    const int* __restrict__ meta, int P, int topk, int chunks_per_row, int cap,
                    uint4* __restrict__ zero, long long zero_chunks) {
+  griddep_wait();
+  griddep_launch_dependents();
   const int rows = min(meta[1], cap);
   const long long n_copy = static_cast<long long>(rows) * chunks_per_row;
   const long long total = n_copy + zero_chunks;
@@ -57,7 +59,14 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 group_quant_fp8_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scales,
                        const int* __restrict__ sorted_ids, const int* __restrict__ meta, int P, int topk,
-                       int n_rows_static, int K, int scale_t, int ld_scale) {
+                       int n_rows_static, int K, int scale_t, int ld_scale, uint4* __restrict__ zero,
+                       long long zero_chunks) {
+  griddep_wait();
+  griddep_launch_dependents();
+  // clear the fp32 combine buffer alongside (grid-stride, 16 bytes per thread)
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < zero_chunks;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    zero[i] = make_uint4(0, 0, 0, 0);
   const int groups = K >> 7;
   const int lane = threadIdx.x & 31;
   const int rows = (meta != nullptr) ? min(meta[1], n_rows_static) : n_rows_static;
@@ -96,6 +105,8 @@ group_quant_fp8_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* 
 template <typename T>
 __global__ void __launch_bounds__(256)
 finalize_kernel(const float4* __restrict__ acc, T* __restrict__ out, size_t n4, float scale) {
+  griddep_wait();
+  griddep_launch_dependents();
   for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4;
        i += static_cast<size_t>(gridDim.x) * blockDim.x) {
     float4 v = acc[i];
@@ -109,51 +120,55 @@ finalize_kernel(const float4* __restrict__ acc, T* __restrict__ out, size_t n4, 
 
 int launch_gather_rows(const void* x, void* xs, const int* sorted_ids, const int* meta, int P, int topk,
                        int row_bytes, int cap, void* zero, size_t zero_bytes, int num_sms,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, bool pdl) {
   if (row_bytes % 16 != 0 || zero_bytes % 16 != 0) return B200MOE_ERR_UNSUPPORTED;
   const long long work = static_cast<long long>(cap) * (row_bytes / 16) + static_cast<long long>(zero_bytes / 16);
   long long ctas = (work + 255) / 256;
   if (ctas > static_cast<long long>(num_sms) * 8) ctas = static_cast<long long>(num_sms) * 8;
   if (ctas < 1) ctas = 1;
-  gather_rows_kernel<<<static_cast<int>(ctas), 256, 0, stream>>>(
-      reinterpret_cast<const uint4*>(x), reinterpret_cast<uint4*>(xs), sorted_ids, meta, P, topk, row_bytes / 16,
-      cap, reinterpret_cast<uint4*>(zero), static_cast<long long>(zero_bytes / 16));
-  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
+  cudaError_t err = launch_kernel(gather_rows_kernel, dim3(static_cast<unsigned>(ctas)), dim3(256), 0, stream, pdl,
+                                  reinterpret_cast<const uint4*>(x), reinterpret_cast<uint4*>(xs), sorted_ids, meta,
+                                  P, topk, row_bytes / 16, cap, reinterpret_cast<uint4*>(zero),
+                                  static_cast<long long>(zero_bytes / 16));
+  return err == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
 }
 
 int launch_group_quant_fp8(const void* x, int dtype, void* q, float* scales, const int* sorted_ids,
                            const int* meta, int P, int topk, int rows, int K, int scale_t, int ld_scale,
-                           int num_sms, cudaStream_t stream) {
-  if (K % 128 != 0) return B200MOE_ERR_UNSUPPORTED;
+                           void* zero, size_t zero_bytes, int num_sms, cudaStream_t stream, bool pdl) {
+  if (K % 128 != 0 || zero_bytes % 16 != 0) return B200MOE_ERR_UNSUPPORTED;
   long long warps = static_cast<long long>(rows) * (K / 128);
   long long ctas = (warps + 7) / 8;
   if (ctas > num_sms * 16) ctas = num_sms * 16;
   if (ctas < 1) ctas = 1;
+  cudaError_t err;
+  const long long zc = static_cast<long long>(zero_bytes / 16);
   if (dtype == B200MOE_DTYPE_BF16)
-    group_quant_fp8_kernel<__nv_bfloat16><<<static_cast<int>(ctas), 256, 0, stream>>>(
-        reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<uint8_t*>(q), scales, sorted_ids, meta,
-        P, topk, rows, K, scale_t, ld_scale);
+    err = launch_kernel(group_quant_fp8_kernel<__nv_bfloat16>, dim3(static_cast<unsigned>(ctas)), dim3(256), 0, stream,
+                        pdl, reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<uint8_t*>(q), scales,
+                        sorted_ids, meta, P, topk, rows, K, scale_t, ld_scale, reinterpret_cast<uint4*>(zero), zc);
   else
-    group_quant_fp8_kernel<__half><<<static_cast<int>(ctas), 256, 0, stream>>>(
-        reinterpret_cast<const __half*>(x), reinterpret_cast<uint8_t*>(q), scales, sorted_ids, meta, P, topk,
-        rows, K, scale_t, ld_scale);
-  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
+    err = launch_kernel(group_quant_fp8_kernel<__half>, dim3(static_cast<unsigned>(ctas)), dim3(256), 0, stream, pdl,
+                        reinterpret_cast<const __half*>(x), reinterpret_cast<uint8_t*>(q), scales, sorted_ids, meta, P,
+                        topk, rows, K, scale_t, ld_scale, reinterpret_cast<uint4*>(zero), zc);
+  return err == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
 }
 
 int launch_finalize(const float* acc, void* out, int dtype, size_t n, float scale, int num_sms,
-                    cudaStream_t stream) {
+                    cudaStream_t stream, bool pdl) {
   if (n % 4 != 0) return B200MOE_ERR_UNSUPPORTED;
   size_t n4 = n / 4;
   size_t ctas = (n4 + 255) / 256;
   if (ctas > static_cast<size_t>(num_sms) * 8) ctas = static_cast<size_t>(num_sms) * 8;
   if (ctas < 1) ctas = 1;
+  cudaError_t err;
   if (dtype == B200MOE_DTYPE_BF16)
-    finalize_kernel<__nv_bfloat16><<<static_cast<int>(ctas), 256, 0, stream>>>(
-        reinterpret_cast<const float4*>(acc), reinterpret_cast<__nv_bfloat16*>(out), n4, scale);
+    err = launch_kernel(finalize_kernel<__nv_bfloat16>, dim3(static_cast<unsigned>(ctas)), dim3(256), 0, stream, pdl,
+                        reinterpret_cast<const float4*>(acc), reinterpret_cast<__nv_bfloat16*>(out), n4, scale);
   else
-    finalize_kernel<__half><<<static_cast<int>(ctas), 256, 0, stream>>>(
-        reinterpret_cast<const float4*>(acc), reinterpret_cast<__half*>(out), n4, scale);
-  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
+    err = launch_kernel(finalize_kernel<__half>, dim3(static_cast<unsigned>(ctas)), dim3(256), 0, stream, pdl,
+                        reinterpret_cast<const float4*>(acc), reinterpret_cast<__half*>(out), n4, scale);
+  return err == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
 }
 
 }  // namespace b200moe

@@ -16,7 +16,8 @@ W_16BIT, W_FP8_BLOCK, W_INT4_AWQ = 0, 1, 2
 LAYOUT_LAYER, LAYOUT_OP = 0, 1
 ACT_SILU, ACT_GELU = 0, 1
 NOALLOC_SCRATCH_BYTES = 16 * 1024 * 1024
-FLAG_WEIGHT_ON_INPUT, FLAG_MIMIC_ROUNDING, FLAG_SIMT, FLAG_IDS_I64, FLAG_NO_SPLIT_K, FLAG_NO_GRID_BALANCE = 1, 2, 4, 8, 16, 32
+FLAG_WEIGHT_ON_INPUT, FLAG_MIMIC_ROUNDING, FLAG_SIMT, FLAG_IDS_I64, FLAG_NO_SPLIT_K, \
+    FLAG_NO_GRID_BALANCE, FLAG_NO_PDL = 1, 2, 4, 8, 16, 32, 64
 
 
 class Cfg(C.Structure):

@@ -100,6 +100,8 @@ def _env_flags() -> int:
         f |= _lib.FLAG_NO_SPLIT_K
     if os.environ.get("B200MOE_NO_GRID_BALANCE", "0") == "1":
         f |= _lib.FLAG_NO_GRID_BALANCE
+    if os.environ.get("B200MOE_NO_PDL", "0") == "1":
+        f |= _lib.FLAG_NO_PDL
     return f
 
 

@@ -55,6 +55,7 @@ extern "C" {
 #define B200MOE_FLAG_IDS_I64 8          /* topk_ids are int64 instead of int32                 */
 #define B200MOE_FLAG_NO_SPLIT_K 16      /* keep GEMM-2's reduction in one piece                */
 #define B200MOE_FLAG_NO_GRID_BALANCE 32 /* tuning aid: every CTA takes tiles round-robin       */
+#define B200MOE_FLAG_NO_PDL 64          /* launch every kernel fully serialised                */
 
 typedef struct b200moe_cfg {
   int32_t struct_bytes;   /* sizeof(b200moe_cfg), checked                      */
