@@ -116,6 +116,15 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, 
       : "memory");
 }
 
+// Untiled bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16),
+// completing on an mbarrier like the tiled loads.
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
 // ---------------------------------------------------------------- tcgen05 / tensor memory
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
@@ -198,6 +207,42 @@ __device__ __forceinline__ void tmem_ld16x2_wait(uint32_t taddr0, uint32_t taddr
   for (int i = 0; i < 16; ++i) {
     v0[i] = __uint_as_float(r[i]);
     v1[i] = __uint_as_float(r[16 + i]);
+  }
+}
+
+#define B200MOE_R32(r, o) B200MOE_R16(r, o), B200MOE_R16(r, o + 16)
+// 32 consecutive fp32 columns of the thread's TMEM lane (load + wait in one statement).
+__device__ __forceinline__ void tmem_ld32_wait(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, "
+      "%14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : B200MOE_R32(r, 0)
+      : "r"(taddr)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Two 32-column loads in flight before the single wait.
+__device__ __forceinline__ void tmem_ld32x2_wait(uint32_t taddr0, uint32_t taddr1, float (&v0)[32],
+                                                 float (&v1)[32]) {
+  uint32_t r[64];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, "
+      "%14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%64];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, "
+      "%44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, "
+      "[%65];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : B200MOE_R32(r, 0), B200MOE_R32(r, 32)
+      : "r"(taddr0), "r"(taddr1)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    v0[i] = __uint_as_float(r[i]);
+    v1[i] = __uint_as_float(r[32 + i]);
   }
 }
 
