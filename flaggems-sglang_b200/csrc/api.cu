@@ -272,7 +272,8 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
     g1.w_sz = quant->w1_sz;
     g1.w_rows = 2 * c->I;
   }
-  if (fp8) gemm_plan_fp8(&g1); else gemm_plan(&g1);
+  const bool w4p = w4 && L.BT <= 32;   // decode-sized int4: group-promoted kernels
+  if (fp8) gemm_plan_fp8(&g1); else if (w4p) gemm_plan_w4(&g1); else gemm_plan(&g1);
 
   GemmArgs g2 = g1;
   g2.mode = 1;
@@ -298,7 +299,7 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
     g2.out_scale = nullptr;
     g2.flags &= ~B200MOE_FLAG_MIMIC_ROUNDING;
   }
-  if (fp8) gemm_plan_fp8(&g2); else gemm_plan(&g2);
+  if (fp8) gemm_plan_fp8(&g2); else if (w4p) gemm_plan_w4(&g2); else gemm_plan(&g2);
 
   if (c->flags & B200MOE_FLAG_SIMT) {
     rc = launch_gemm_simt(w1, xs, g1, st, L.cap);
@@ -326,11 +327,13 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
     if ((rc = make_tmap_2d(&tm_x, dt, eb, xs, c->H, L.cap, kbox, L.BT)) != B200MOE_OK) return rc;
     if ((rc = make_tmap_2d(&tm_a2, dt, eb, a2, c->I, L.cap, kbox, L.BT)) != B200MOE_OK) return rc;
     prof_mark(slot, 1, st);
-    rc = fp8 ? launch_gemm_fp8(tm_w1, tm_x, g1, sms, st) : launch_gemm_tc(tm_w1, tm_x, g1, sms, st);
+    rc = fp8 ? launch_gemm_fp8(tm_w1, tm_x, g1, sms, st)
+             : (w4p ? launch_gemm_w4(tm_w1, tm_x, g1, sms, st) : launch_gemm_tc(tm_w1, tm_x, g1, sms, st));
     prof_mark(slot, 2, st);
     if (rc != B200MOE_OK) return rc;
     prof_mark(slot, 3, st);
-    rc = fp8 ? launch_gemm_fp8(tm_w2, tm_a2, g2, sms, st) : launch_gemm_tc(tm_w2, tm_a2, g2, sms, st);
+    rc = fp8 ? launch_gemm_fp8(tm_w2, tm_a2, g2, sms, st)
+             : (w4p ? launch_gemm_w4(tm_w2, tm_a2, g2, sms, st) : launch_gemm_tc(tm_w2, tm_a2, g2, sms, st));
     prof_mark(slot, 4, st);
     if (rc != B200MOE_OK) return rc;
   }

@@ -54,6 +54,10 @@ int launch_gemm_tc(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmA
 void gemm_plan_fp8(GemmArgs* a);
 int launch_gemm_fp8(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmArgs& a, int num_sms,
                     cudaStream_t stream);
+// int4 AWQ, token blocks of 16 / 32: exact (q - zero) operands, group scales applied to partial sums
+void gemm_plan_w4(GemmArgs* a);
+int launch_gemm_w4(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmArgs& a, int num_sms,
+                   cudaStream_t stream);
 int launch_gemm_simt(const void* w, const void* x, const GemmArgs& a, cudaStream_t stream, int cap);
 
 }  // namespace b200moe

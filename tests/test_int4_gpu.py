@@ -39,7 +39,7 @@ def test_int4_fused_experts(cuda_device, h, i, e, k, m):
     assert_parity(out, ref, rtol=2e-2, atol=2e-2, what=f"int4 {(h, i, e, k, m)}")
 
 
-@pytest.mark.parametrize("bt", [16, 64, 128, 256])
+@pytest.mark.parametrize("bt", [16, 32, 64, 128, 256])
 def test_int4_every_token_block(cuda_device, bt):
     import flaggems_sglang_b200 as F
     from flaggems_sglang_b200.quant import repack_awq_for_kernel
