@@ -50,7 +50,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the
 # ncu capture summarised under profiles/ (None until such a capture exists for the workload).
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {("mixtral", 4096): 2201926400}   # profiles/moe_gemm_tc_mixtral_m4096_launch_list.md
 
 
 def load_peaks():
@@ -433,7 +433,9 @@ def run_ours(args, rank, local_rank, world):
                                        f"expert parallel over {world} ranks, all-to-all dispatch/combine, global M {m * world}"
                                        if layer.ep else f"{world} independent replicas (no collective)")},
             "clocks": clocks.summary(), "e2e": e2e,
-            "gpu_launches": 5 * args.steps, "launches_per_step": {"kernels": 5, "memsets": 1},
+            "gpu_launches": 5 * args.steps,
+            "launches_per_step": {"kernels": 5, "names": ["align_block", "gather_rows | group_quant_fp8", "moe_gemm<gate/up>",
+                                                          "moe_gemm<down>", "finalize"]},
             "roofline": roof, "cpu_baseline": cpu, "sweep": sweep,
             "whole_call": {"algorithmic_bytes": bytes_alg, "algorithmic_flops": flops_alg, "experts_hit": hit},
         }
