@@ -100,9 +100,16 @@ struct Layout {
 int pick_bt(const b200moe_cfg* c) {
   if (c->block_tokens > 0) return c->block_tokens;
   const double avg = static_cast<double>(c->M) * c->topk / (c->E > 0 ? c->E : 1);
+  if (c->wmode == B200MOE_W_FP8_BLOCK) {
+    // many-expert FP8 layers route unevenly: hot experts hold several times the average, and every
+    // extra block of an expert streams its weights once more from L2, so lean towards larger blocks
+    if (avg <= 4) return 16;
+    if (avg <= 12) return 32;
+    return 64;   // blocks of 128 are available (block_tokens) but measured slower
+  }
   if (avg <= 10) return 16;
   if (avg <= 20) return 32;
-  if (avg <= 40 || c->wmode == B200MOE_W_FP8_BLOCK) return 64;  // FP8 keeps its accumulators in registers
+  if (avg <= 40) return 64;
   return 128;
 }
 
@@ -119,7 +126,8 @@ int check_cfg(const b200moe_cfg* c) {
     if (c->w_layout != B200MOE_LAYOUT_LAYER) return B200MOE_ERR_UNSUPPORTED;
   } else if (c->wmode == B200MOE_W_FP8_BLOCK) {
     if (c->H % 128 != 0 || c->I % 128 != 0) return B200MOE_ERR_UNSUPPORTED;
-    if (c->block_tokens != 0 && c->block_tokens != 16 && c->block_tokens != 32 && c->block_tokens != 64)
+    if (c->block_tokens != 0 && c->block_tokens != 16 && c->block_tokens != 32 && c->block_tokens != 64 &&
+        c->block_tokens != 128)
       return B200MOE_ERR_UNSUPPORTED;
     if (c->flags & B200MOE_FLAG_SIMT) return B200MOE_ERR_UNSUPPORTED;
   } else if (c->wmode == B200MOE_W_INT4_AWQ) {

@@ -50,7 +50,7 @@ def test_fp8_fused_experts(cuda_device, h, i, e, k, m):
     assert_parity(out, ref, what=f"fp8 {(h, i, e, k, m)}")
 
 
-@pytest.mark.parametrize("bt", [16, 32, 64])
+@pytest.mark.parametrize("bt", [16, 32, 64, 128])
 def test_fp8_every_token_block(cuda_device, bt):
     import flaggems_sglang_b200 as F
     x, tw, ids, w13q, s13, w2q, s2 = _fp8_case(512, 256, 4, 2, 150, seed=bt)
