@@ -143,7 +143,10 @@ int check_cfg(const b200moe_cfg* c) {
 int make_layout(const b200moe_cfg* c, Layout* L) {
   L->BT = pick_bt(c);
   // a block of 128 tokens sits on the M side of the MMA; smaller (and 256-token) blocks on the N side
-  L->orient = (L->BT == 128 && c->wmode == B200MOE_W_16BIT) ? 1 : 0;
+  // int4 always runs tokens-on-M (one MMA then covers 256 weight rows, which halves the number of
+  // MMA instructions per streamed byte; blocks below 128 tokens simply load fewer token rows)
+  if (c->wmode == B200MOE_W_INT4_AWQ) L->orient = (L->BT <= 128) ? 1 : 0;
+  else L->orient = (L->BT == 128 && c->wmode == B200MOE_W_16BIT) ? 1 : 0;
   L->P = c->M * c->topk;
   int cap = align_capacity(L->P, c->E, L->BT);
   if (cap < 0) return B200MOE_ERR_TOO_LARGE;
@@ -280,7 +283,8 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
     g1.w_sz = quant->w1_sz;
     g1.w_rows = 2 * c->I;
   }
-  const bool w4p = w4 && L.BT <= 32;   // decode-sized int4: group-promoted kernels
+  // decode-sized int4: operands dequantised into tensor memory, group scales applied to partial sums
+  const bool w4p = w4 && L.BT <= 32 && !(c->flags & B200MOE_FLAG_W4_SMEM_OPERANDS);
   if (fp8) gemm_plan_fp8(&g1); else if (w4p) gemm_plan_w4(&g1); else gemm_plan(&g1);
 
   GemmArgs g2 = g1;

@@ -79,7 +79,7 @@ template <int MODE, typename T, int ORIENT, bool W4>
 __global__ void __launch_bounds__(W4 ? kThreadsW4 : kThreads, 1)
 moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                    const GemmArgs a) {
-  static_assert(!(W4 && ORIENT == 1), "int4 weights use the weights-on-M orientation");
+
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -162,6 +162,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
           const uint32_t spk = sw + W_BYTES + x_bytes;
           tma_load_3d(spk, &tm_w, full, kb * 32, t.n0, t.e);
           if (MODE == 0) tma_load_3d(spk + kTileRows * 32, &tm_w, full, kb * 32, a.up_row_off + t.n0, t.e);
+          else if (ORIENT == 1) tma_load_3d(spk + kTileRows * 32, &tm_w, full, kb * 32, t.n0 + kTileRows, t.e);
         } else {
           mbar_arrive_expect_tx(full, static_cast<uint32_t>(stage_bytes));
           tma_load_3d(sw, &tm_w, full, k0, t.n0, t.e);
@@ -239,7 +240,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     }
   } else if (W4 && active && warp >= 6) {
     // =============================== int4 -> fp16 operand tile ==================
-    constexpr int ROWS = (MODE == 0 ? 2 : 1) * kTileRows;        // packed rows per stage
+    constexpr int ROWS = (MODE == 0 || ORIENT == 1 ? 2 : 1) * kTileRows;  // packed rows per stage
     constexpr int UNITS_PER_THREAD = ROWS * 2 / (32 * kDequantWarps);  // 16-byte units per thread (2 or 1)
     const int dt = threadIdx.x - 6 * 32;                          // 0..255
     const int row = (UNITS_PER_THREAD == 2) ? dt : (dt >> 1);     // packed row this thread converts
@@ -252,7 +253,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     for (int tile = blockIdx.x; ok && tile < c.total; tile += c.grid_eff) {
       const TileCoord t = decode_tile(tile, c, s_blk_off, a.E, BT, a.num_nt, a.kblocks, G::kTileN);
       // output row of this packed row inside the expert (gate rows first, then the up rows)
-      const int n = (row < kTileRows) ? t.n0 + row : a.up_row_off + t.n0 + (row - kTileRows);
+      const int n = (row < kTileRows || MODE == 1) ? t.n0 + row : a.up_row_off + t.n0 + (row - kTileRows);
       const bool n_ok = n < a.w_rows;
       const uint32_t* szrow = sz + static_cast<size_t>(t.e) * groups * a.w_rows + n;
       for (int kb = t.kb0; kb < t.kb1; ++kb) {
@@ -303,9 +304,12 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                              static_cast<uint32_t>(acc * cols_per_acc);
       if (ORIENT == 1) {
         // ---- accumulator row = token: contiguous output columns per thread
-        const int r = t.row0 + lrow;
+        // blocks smaller than 128 tokens load only their rows; the MMA still spans 128 rows and
+        // the accumulator rows beyond the block hold garbage that is never stored
+        const bool in_block = lrow < BT;
+        const int r = t.row0 + (in_block ? lrow : 0);
         const int slot = a.sorted_ids[r];
-        const bool valid = slot >= 0 && slot < a.P;
+        const bool valid = in_block && slot >= 0 && slot < a.P;
         const float gam = valid ? a.row_gamma[r] : 0.f;
         if (!mbar_wait(smem_u32(&bar_tfull[acc]), acc_phase, abort_flag, DEV_TIMEOUT_EPILOGUE)) break;
         tc_fence_after();
@@ -322,8 +326,9 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
               const float hi = act_mul<T>(g[2 * j + 1], u[2 * j + 1], w_on_input, gam, mimic, a.activation);
               pk[j] = pack2<T>(lo, hi);
             }
-            if (t.n0 + c0 + 8 <= a.N) *reinterpret_cast<uint4*>(orow + c0) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-            if (t.n0 + c0 + 16 <= a.N)
+            if (in_block && t.n0 + c0 + 8 <= a.N)
+              *reinterpret_cast<uint4*>(orow + c0) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            if (in_block && t.n0 + c0 + 16 <= a.N)
               *reinterpret_cast<uint4*>(orow + c0 + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
           }
         } else {
@@ -424,7 +429,10 @@ static size_t stage_bytes_of(const GemmArgs& a) {
 }
 
 static size_t ctrl_bytes_of(const GemmArgs& a) {
-  return 768 /*barriers*/ + 2 * kMaxBT * 8 + static_cast<size_t>(a.E + 1) * 4 + 64;
+  // with tokens on M and fewer than 128 token rows loaded, the MMA of the last stage reads up to
+  // 16 KiB past its token rows: keep that inside the allocation
+  const size_t overread = (a.orient == 1 && a.BT < 128) ? 16384 : 0;
+  return 768 /*barriers*/ + 2 * kMaxBT * 8 + static_cast<size_t>(a.E + 1) * 4 + 64 + overread;
 }
 
 void gemm_plan(GemmArgs* a) {
@@ -476,9 +484,12 @@ static int launch_typed(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const 
 int launch_gemm_tc(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmArgs& a, int num_sms,
                    cudaStream_t stream) {
   if (a.BT < 16 || a.BT > kMaxBT || a.BT % 16 != 0) return B200MOE_ERR_BAD_ARG;
-  if (a.orient == 1 && a.BT != 128) return B200MOE_ERR_BAD_ARG;
+  if (a.orient == 1 && a.BT > 128) return B200MOE_ERR_BAD_ARG;
   if (a.wmode == B200MOE_W_INT4_AWQ) {
-    if (a.orient != 0 || a.dtype != B200MOE_DTYPE_FP16 || a.w_sz == nullptr) return B200MOE_ERR_UNSUPPORTED;
+    if (a.dtype != B200MOE_DTYPE_FP16 || a.w_sz == nullptr) return B200MOE_ERR_UNSUPPORTED;
+    if (a.orient == 1)
+      return a.mode == 0 ? launch_one<0, __half, 1, true>(tm_w, tm_x, a, num_sms, stream)
+                         : launch_one<1, __half, 1, true>(tm_w, tm_x, a, num_sms, stream);
     return a.mode == 0 ? launch_one<0, __half, 0, true>(tm_w, tm_x, a, num_sms, stream)
                        : launch_one<1, __half, 0, true>(tm_w, tm_x, a, num_sms, stream);
   }

@@ -14,10 +14,13 @@
 // Tiles are two 128-row weight blocks sharing the token block (gate | up rows for the first
 // GEMM, rows n0.. | n0+128.. for the second), as in the FP8 kernels.
 //
-// Two shared-memory rings.  A packed stage is only 8 KiB of weights (+ the token block), so
-// the ring that TMA fills is deep (many small stages keep enough bytes in flight to cover
-// the HBM latency), while the ring of 32 KiB dequantised operand tiles is short (three
-// stages cover the dequantise -> MMA -> release round trip).
+// The dequantised operand never touches shared memory: staging fp16 tiles there costs four
+// times the bytes that arrive from HBM in shared-memory writes plus the same again in MMA
+// operand reads, and that bandwidth (128 B/clk) caps the kernel well below the HBM rate.
+// Instead each dequant thread owns one weight row = one TMEM lane and writes its 64 k-values
+// of a stage into tensor memory with tcgen05.st; the MMA takes its A operand from there
+// (tcgen05.mma with A in TMEM) and only the small token block as a shared-memory descriptor.
+// Shared memory then holds just a deep ring of small TMA stages (8 KiB packed + token block).
 //
 // Warps: 0 TMA producer, 1 MMA issuer, 2-5 promotion + tail, 6 per-tile table loader,
 // 7-14 dequantisation.
@@ -27,23 +30,28 @@ namespace b200moe {
 
 namespace {
 
+#ifdef B200MOE_STALL_STATS
+__device__ unsigned long long g_stall_w4[16];
+#define STALL_ADD(slot, v) atomicAdd(&g_stall_w4[slot], v)
+#else
+#define STALL_ADD(slot, v) ((void)0)
+#endif
+
 constexpr int kDqWarps = 8;
-constexpr int kOperandStages = 3;
+constexpr int kOperandStages = 4;   // A-operand stages in tensor memory, 64 columns each
 constexpr int kThreadsW4P = 7 * 32 + 32 * kDqWarps;  // 480
 
-// 32 packed uint4 (16 bytes) -> 32 fp16 values (q - zero), four 16-byte chunks.
-__device__ __forceinline__ void dequant_w4x32_centered(const uint4 packed, const __half2 zero1024, uint4 (&out)[4]) {
+// 32 packed uint4 (16 bytes) -> 16 words of two fp16 values (q - zero) each, k ascending.
+__device__ __forceinline__ void dequant_w4x32_centered(const uint4 packed, const __half2 zero1024, uint32_t* out) {
   const uint32_t w[4] = {packed.x, packed.y, packed.z, packed.w};
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    uint32_t r[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       uint32_t t = ((w[j] >> (4 * i)) & 0x000F000Fu) | 0x64006400u;  // fp16 pair (1024 + q, 1024 + q')
       __half2 h = __hsub2(*reinterpret_cast<__half2*>(&t), zero1024);
-      r[i] = *reinterpret_cast<uint32_t*>(&h);
+      out[4 * j + i] = *reinterpret_cast<uint32_t*>(&h);
     }
-    out[j] = make_uint4(r[0], r[1], r[2], r[3]);
   }
 }
 
@@ -54,7 +62,6 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  constexpr int W_BYTES = 2 * kTileBytes;           // dequantised operand: 256 rows x 64 k fp16
   constexpr int X_BYTES = BT * kStageKBytes;        // token block: BT rows x 64 k fp16
   constexpr int PK_BYTES = 2 * kTileRows * 32;      // packed rows: 256 x 32 bytes
   constexpr int STAGE_BYTES = X_BYTES + PK_BYTES;   // one stage of the TMA ring: [token block | packed rows]
@@ -62,8 +69,8 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   constexpr int NO = kOperandStages;
   const int stages = a.stages;                      // depth of the TMA ring
 
-  uint8_t* op_base = smem;                                           // operand ring
-  uint8_t* pk_base = smem + static_cast<size_t>(NO) * W_BYTES;       // TMA ring
+  uint8_t* pk_base = smem;                                           // TMA ring
+  constexpr uint32_t A_COL0 = 4 * BT;                                // TMEM: [0, 4*BT) partial sums, then A stages
   uint8_t* ctrl_base = pk_base + static_cast<size_t>(stages) * STAGE_BYTES;
   uint64_t* bar_full = reinterpret_cast<uint64_t*>(ctrl_base);
   uint64_t* bar_empty = bar_full + stages;
@@ -127,10 +134,12 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     uint32_t phase = 0;
     long long issued = 0;
     bool ok = true;
+    unsigned long long w_empty = 0;
+    const long long role_t0 = clock64();
     for (int tile = blockIdx.x; ok && tile < c.total; tile += c.grid_eff) {
       const TileCoord t = decode_tile(tile, c, s_blk_off, a.E, BT, a.num_nt, a.kblocks, kTileN);
       for (int ks = 2 * t.kb0; ks < 2 * t.kb1; ++ks) {  // ks: 64-wide k step
-        if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1, abort_flag, DEV_TIMEOUT_PRODUCER)) {
+        if (!mbar_wait_t(smem_u32(&bar_empty[stage]), phase ^ 1, abort_flag, DEV_TIMEOUT_PRODUCER, w_empty)) {
           ok = false;
           break;
         }
@@ -148,6 +157,8 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         }
       }
     }
+    STALL_ADD(0, w_empty);
+    STALL_ADD(8, static_cast<unsigned long long>(clock64() - role_t0));
     if (!ok) {
       const int n = static_cast<int>(issued < stages ? issued : stages);
       for (int i = 1; i <= n; ++i) {
@@ -166,11 +177,13 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     int stage = 0, ost = 0;
     uint32_t phase = 0, ophase = 0, j = 0;  // j counts groups over the whole launch
     bool ok = true;
+    unsigned long long w_pempty = 0, w_dq = 0;
+    const long long role_t0 = clock64();
     for (int tile = blockIdx.x; ok && tile < c.total; tile += c.grid_eff) {
       const TileCoord t = decode_tile(tile, c, s_blk_off, a.E, BT, a.num_nt, a.kblocks, kTileN);
       for (int kb = t.kb0; kb < t.kb1 && ok; ++kb, ++j) {
         const uint32_t pb = j & 1u;
-        if (!mbar_wait(smem_u32(&bar_pempty[pb]), ((j >> 1) & 1u) ^ 1u, abort_flag, DEV_TIMEOUT_MMA)) {
+        if (!mbar_wait_t(smem_u32(&bar_pempty[pb]), ((j >> 1) & 1u) ^ 1u, abort_flag, DEV_TIMEOUT_MMA, w_pempty)) {
           ok = false;
           break;
         }
@@ -179,20 +192,19 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         for (int h = 0; h < 2; ++h) {
           // the operand tile is written only after its TMA stage has landed, so this wait
           // also covers the token block of that stage
-          if (!mbar_wait(smem_u32(&bar_dq[ost]), ophase, abort_flag, DEV_TIMEOUT_MMA)) {
+          if (!mbar_wait_t(smem_u32(&bar_dq[ost]), ophase, abort_flag, DEV_TIMEOUT_MMA, w_dq)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t obase = smem_u32(op_base + static_cast<size_t>(ost) * W_BYTES);
-          const uint64_t dw = smem_desc_k_sw128(obase);
-          const uint64_t du = smem_desc_k_sw128(obase + kTileBytes);
+          // A operand: 64 TMEM columns of this stage (32 per weight block, 8 per 16-wide k slice)
+          const uint32_t a0 = tmem_base + A_COL0 + static_cast<uint32_t>(ost) * 64;
           const uint64_t dx = smem_desc_k_sw128(smem_u32(pk_base + static_cast<size_t>(stage) * STAGE_BYTES));
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const uint32_t accum = (h > 0 || k > 0) ? 1u : 0u;
-            tc_mma_f16(d0, dw + 2 * k, dx + 2 * k, idesc, accum);
-            tc_mma_f16(d0 + BT, du + 2 * k, dx + 2 * k, idesc, accum);
+            tc_mma_f16_ts(d0, a0 + 8 * k, dx + 2 * k, idesc, accum);
+            tc_mma_f16_ts(d0 + BT, a0 + 32 + 8 * k, dx + 2 * k, idesc, accum);
           }
           tc_commit(smem_u32(&bar_empty[stage]));
           tc_commit(smem_u32(&bar_oempty[ost]));
@@ -208,6 +220,9 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         if (ok) tc_commit(smem_u32(&bar_pfull[pb]));
       }
     }
+    STALL_ADD(1, w_pempty);
+    STALL_ADD(2, w_dq);
+    STALL_ADD(9, static_cast<unsigned long long>(clock64() - role_t0));
   } else if (active && warp == 6) {
     // =============================== per-tile table loader ======================
     int iter = 0;
@@ -226,12 +241,18 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     }
   } else if (active && warp >= 7) {
     // =============================== int4 -> centred fp16 operand ===============
-    const int row = threadIdx.x - 7 * 32;  // 0..255: packed row of the stage
+    // warp w may touch TMEM lanes 32 * (w % 4)..: warps 7-10 convert the first weight block,
+    // warps 11-14 the second, each thread the row that is its own TMEM lane
+    const int wblk = (warp - 7) >> 2;
+    const int quad = warp & 3;
+    const int row = wblk * kTileRows + quad * 32 + lane;  // packed row of the stage
     const uint32_t* sz = reinterpret_cast<const uint32_t*>(a.w_sz);
     const int groups = a.kblocks;
     int stage = 0, ost = 0;
     uint32_t phase = 0, ophase = 0;
     bool ok = true;
+    unsigned long long w_full = 0, w_oempty = 0;
+    const long long role_t0 = clock64();
     for (int tile = blockIdx.x; ok && tile < c.total; tile += c.grid_eff) {
       const TileCoord t = decode_tile(tile, c, s_blk_off, a.E, BT, a.num_nt, a.kblocks, kTileN);
       const int n = (row < kTileRows) ? t.n0 + row : second_off + t.n0 + (row - kTileRows);
@@ -252,26 +273,20 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         const __half2 zp = __half2half2(__ushort_as_half(static_cast<unsigned short>(szv >> 16)));
 #pragma unroll 1
         for (int h = 0; h < 2; ++h) {
-          if (!mbar_wait(smem_u32(&bar_full[stage]), phase, abort_flag, DEV_TIMEOUT_MMA) ||
-              !mbar_wait(smem_u32(&bar_oempty[ost]), ophase ^ 1, abort_flag, DEV_TIMEOUT_MMA)) {
+          if (!mbar_wait_t(smem_u32(&bar_full[stage]), phase, abort_flag, DEV_TIMEOUT_MMA, w_full) ||
+              !mbar_wait_t(smem_u32(&bar_oempty[ost]), ophase ^ 1, abort_flag, DEV_TIMEOUT_MMA, w_oempty)) {
             ok = false;
             break;
           }
           const uint4* pk = reinterpret_cast<const uint4*>(pk_base + static_cast<size_t>(stage) * STAGE_BYTES +
                                                            X_BYTES + row * 32);
-          uint8_t* orow = op_base + static_cast<size_t>(ost) * W_BYTES + (row >> 7) * kTileBytes +
-                          (row & 127) * kStageKBytes;
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            uint4 o[4];
-            dequant_w4x32_centered(pk[u], zp, o);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const int chunk = (u * 4 + q) ^ (row & 7);  // 128-byte swizzle of the operand tile
-              *reinterpret_cast<uint4*>(orow + chunk * 16) = o[q];
-            }
-          }
-          fence_proxy_async_smem();
+          uint32_t o[32];
+          dequant_w4x32_centered(pk[0], zp, o);
+          dequant_w4x32_centered(pk[1], zp, o + 16);
+          tc_fence_after();
+          tmem_st32_wait(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + A_COL0 +
+                             static_cast<uint32_t>(ost) * 64 + static_cast<uint32_t>(wblk) * 32, o);
+          tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(&bar_dq[ost]));
           if (++stage == stages) {
@@ -285,8 +300,15 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         }
       }
     }
+    if (threadIdx.x == 8 * 32) {
+      STALL_ADD(3, w_full);
+      STALL_ADD(4, w_oempty);
+      STALL_ADD(10, static_cast<unsigned long long>(clock64() - role_t0));
+    }
   } else if (active && warp >= 2 && warp < 6) {
     // =============================== promotion + tail ===========================
+    unsigned long long w_pfull = 0, w_sfull = 0;
+    const long long role_t0 = clock64();
     const int quad = warp & 3;
     const int lrow = quad * 32 + lane;
     const bool w_on_input = (a.flags & B200MOE_FLAG_WEIGHT_ON_INPUT) != 0;
@@ -313,7 +335,7 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       float s1 = ok1 ? scale_of(__ldg(sz1 + static_cast<size_t>(t.kb0) * a.w_rows)) : 0.f;
       float s0n = (ok0 && t.kb0 + 1 < t.kb1) ? scale_of(__ldg(sz0 + static_cast<size_t>(t.kb0 + 1) * a.w_rows)) : 0.f;
       float s1n = (ok1 && t.kb0 + 1 < t.kb1) ? scale_of(__ldg(sz1 + static_cast<size_t>(t.kb0 + 1) * a.w_rows)) : 0.f;
-      if (!mbar_wait(smem_u32(&bar_sfull[buf]), (iter >> 1) & 1, abort_flag, DEV_TIMEOUT_EPILOGUE)) break;
+      if (!mbar_wait_t(smem_u32(&bar_sfull[buf]), (iter >> 1) & 1, abort_flag, DEV_TIMEOUT_EPILOGUE, w_sfull)) break;
 
       float acc0[BT], acc1[BT];
 #pragma unroll
@@ -329,7 +351,7 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
           if (ok1) r1 = __ldg(sz1 + static_cast<size_t>(kb + 2) * a.w_rows);
         }
         const uint32_t pb = j & 1u;
-        if (!mbar_wait(smem_u32(&bar_pfull[pb]), (j >> 1) & 1u, abort_flag, DEV_TIMEOUT_EPILOGUE)) {
+        if (!mbar_wait_t(smem_u32(&bar_pfull[pb]), (j >> 1) & 1u, abort_flag, DEV_TIMEOUT_EPILOGUE, w_pfull)) {
           ok = false;
           break;
         }
@@ -391,6 +413,11 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_sempty[buf]));
     }
+    if (threadIdx.x == 2 * 32) {
+      STALL_ADD(5, w_pfull);
+      STALL_ADD(6, w_sfull);
+      STALL_ADD(11, static_cast<unsigned long long>(clock64() - role_t0));
+    }
   }
 
   // ---- teardown
@@ -407,8 +434,8 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 size_t w4_stage_bytes(const GemmArgs& a) {   // one stage of the TMA ring
   return static_cast<size_t>(a.BT) * kStageKBytes + 2 * kTileRows * 32;
 }
-size_t w4_ctrl_bytes(const GemmArgs& a) {    // operand ring + barriers + tables
-  return static_cast<size_t>(kOperandStages) * 2 * kTileBytes + 1024 + 2 * 32 * 8 + static_cast<size_t>(a.E + 1) * 4 + 64;
+size_t w4_ctrl_bytes(const GemmArgs& a) {    // barriers + tables
+  return 1024 + 2 * 32 * 8 + static_cast<size_t>(a.E + 1) * 4 + 64;
 }
 
 template <int MODE, int BT>
@@ -425,17 +452,28 @@ int launch_w4(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmArgs& 
 
 }  // namespace
 
+#ifdef B200MOE_STALL_STATS
+extern "C" int b200moe_debug_stalls_w4(unsigned long long* out16, int reset) {
+  if (cudaMemcpyFromSymbol(out16, g_stall_w4, sizeof(unsigned long long) * 16) != cudaSuccess) return -1;
+  if (reset) {
+    unsigned long long z[16] = {0};
+    cudaMemcpyToSymbol(g_stall_w4, z, sizeof(z));
+  }
+  return 0;
+}
+#endif
+
 void gemm_plan_w4(GemmArgs* a) {
   a->orient = 0;
   const int tile_n = (a->mode == 0) ? kTileRows : 2 * kTileRows;
   a->num_nt = (a->N + tile_n - 1) / tile_n;
   a->kblocks = (a->K + 127) / 128;  // reduction unit = one quantisation group
   int tc = 32;
-  while (tc < 4 * a->BT) tc <<= 1;
+  while (tc < 4 * a->BT + 64 * kOperandStages) tc <<= 1;   // partial sums + A-operand stages
   a->tmem_cols = tc;
   a->acc_stages = 2;
   int st = static_cast<int>((kSmemLimit - 1024 - w4_ctrl_bytes(*a)) / w4_stage_bytes(*a));
-  if (st > 12) st = 12;
+  if (st > 16) st = 16;
   if (st < 2) st = 2;
   a->stages = st;
   if (a->max_split <= 0) a->max_split = 16;

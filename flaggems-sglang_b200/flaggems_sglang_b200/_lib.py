@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
 from ._build import LIB_PATH
@@ -17,7 +18,7 @@ LAYOUT_LAYER, LAYOUT_OP = 0, 1
 ACT_SILU, ACT_GELU = 0, 1
 NOALLOC_SCRATCH_BYTES = 16 * 1024 * 1024
 FLAG_WEIGHT_ON_INPUT, FLAG_MIMIC_ROUNDING, FLAG_SIMT, FLAG_IDS_I64, FLAG_NO_SPLIT_K, \
-    FLAG_NO_GRID_BALANCE, FLAG_NO_PDL = 1, 2, 4, 8, 16, 32, 64
+    FLAG_NO_GRID_BALANCE, FLAG_NO_PDL, FLAG_W4_SMEM_OPERANDS = 1, 2, 4, 8, 16, 32, 64, 128
 
 
 class Cfg(C.Structure):
@@ -73,7 +74,7 @@ def lib() -> C.CDLL:
     """Load the shared object; there is no fallback when it is missing."""
     global _lib
     if _lib is None:
-        path = Path(LIB_PATH)
+        path = Path(os.environ.get("B200MOE_LIB", LIB_PATH))   # override: development builds
         if not path.exists():
             raise ExtensionMissing(
                 f"{path} is not built. Run `python -c 'import __graft_entry__ as g; g.build()'` "

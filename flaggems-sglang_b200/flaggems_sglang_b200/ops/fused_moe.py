@@ -102,6 +102,8 @@ def _env_flags() -> int:
         f |= _lib.FLAG_NO_GRID_BALANCE
     if os.environ.get("B200MOE_NO_PDL", "0") == "1":
         f |= _lib.FLAG_NO_PDL
+    if os.environ.get("B200MOE_W4_SMEM_OPERANDS", "0") == "1":
+        f |= _lib.FLAG_W4_SMEM_OPERANDS
     return f
 
 

@@ -56,6 +56,7 @@ extern "C" {
 #define B200MOE_FLAG_NO_SPLIT_K 16      /* keep GEMM-2's reduction in one piece                */
 #define B200MOE_FLAG_NO_GRID_BALANCE 32 /* tuning aid: every CTA takes tiles round-robin       */
 #define B200MOE_FLAG_NO_PDL 64          /* launch every kernel fully serialised                */
+#define B200MOE_FLAG_W4_SMEM_OPERANDS 128 /* int4: always stage fp16 operands in shared memory (tuning aid) */
 
 typedef struct b200moe_cfg {
   int32_t struct_bytes;   /* sizeof(b200moe_cfg), checked                      */
