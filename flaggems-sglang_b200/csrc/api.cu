@@ -105,7 +105,8 @@ int pick_bt(const b200moe_cfg* c) {
     // extra block of an expert streams its weights once more from L2, so lean towards larger blocks
     if (avg <= 4) return 16;
     if (avg <= 12) return 32;
-    return 64;   // blocks of 128 are available (block_tokens) but measured slower
+    if (avg < 24) return 64;
+    return 128;  // tokens-on-M kernels
   }
   if (avg <= 10) return 16;
   if (avg <= 20) return 32;
@@ -146,7 +147,9 @@ int make_layout(const b200moe_cfg* c, Layout* L) {
   // int4 always runs tokens-on-M (one MMA then covers 256 weight rows, which halves the number of
   // MMA instructions per streamed byte; blocks below 128 tokens simply load fewer token rows)
   if (c->wmode == B200MOE_W_INT4_AWQ) L->orient = (L->BT <= 128) ? 1 : 0;
-  else L->orient = (L->BT == 128 && c->wmode == B200MOE_W_16BIT) ? 1 : 0;
+  else if (c->wmode == B200MOE_W_FP8_BLOCK)
+    L->orient = (L->BT == 128) ? 1 : 0;
+  else L->orient = (L->BT == 128) ? 1 : 0;
   L->P = c->M * c->topk;
   int cap = align_capacity(L->P, c->E, L->BT);
   if (cap < 0) return B200MOE_ERR_TOO_LARGE;
@@ -333,7 +336,7 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
         return rc;
     } else {
       if ((rc = make_tmap_3d(&tm_w1, dt, eb, w1, c->H, 2ull * c->I, c->E, kbox, 128)) != B200MOE_OK) return rc;
-      if ((rc = make_tmap_3d(&tm_w2, dt, eb, w2, c->I, c->H, c->E, kbox, L.orient == 1 ? 256 : 128)) != B200MOE_OK)
+      if ((rc = make_tmap_3d(&tm_w2, dt, eb, w2, c->I, c->H, c->E, kbox, (L.orient == 1 && !fp8) ? 256 : 128)) != B200MOE_OK)
         return rc;
     }
     if ((rc = make_tmap_2d(&tm_x, dt, eb, xs, c->H, L.cap, kbox, L.BT)) != B200MOE_OK) return rc;

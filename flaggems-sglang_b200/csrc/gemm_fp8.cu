@@ -331,6 +331,352 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   if (threadIdx.x == 0 && *abort_flag != 0) atomicCAS(a.status, 0, *abort_flag);
 }
 
+// ------------------------------------------------------------------------------------------
+// Tokens-on-M variant for 128-token blocks (prefill-sized batches).
+//
+// One tcgen05.mma costs about the same issue time whatever its N, so with many tokens per
+// expert the token block goes on the M side (128 rows) and 256 weight rows on the N side:
+// four MMAs per 128-wide reduction slice instead of sixteen.  An accumulator row is then a
+// token, so the activation scale is one scalar per thread and slice, the weight scale one
+// scalar per 128 columns; two promotion groups split the 256 columns (gate columns
+// [64g, 64g+64) with the matching up columns for mode 0, columns [128g, 128g+128) for mode 1)
+// and keep 128 accumulators per thread.  The 1x128 quantisation group of a token is the 64
+// activations of its thread in group 0 plus the 64 of its thread in group 1: the two partial
+// maxima meet in shared memory, no shuffles.
+constexpr int kThreadsFp8TokM = 7 * 32 + 128;
+
+#ifdef B200MOE_STALL_STATS
+__device__ unsigned long long g_stall_fp8[16];
+#define STALL_ADD8(slot, v) atomicAdd(&g_stall_fp8[slot], v)
+#else
+#define STALL_ADD8(slot, v) ((void)0)
+#endif
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreadsFp8TokM, 1)
+moe_gemm_fp8_tokm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                         const GemmArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  constexpr int BT = 128;
+  constexpr int W_BYTES = 2 * kTileBytes;
+  constexpr int X_BYTES = BT * kStageKBytes;
+  constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
+  constexpr int PCOLS = 256;
+  const int stages = a.stages;
+
+  uint8_t* ctrl_base = smem + static_cast<size_t>(stages) * STAGE_BYTES;
+  float* s_xs = reinterpret_cast<float*>(ctrl_base);                    // [2][kMaxKB][128] activation scales
+  float* s_ws = s_xs + 2 * kMaxKB * BT;                                 // [2][2][kMaxKB] weight scales
+  uint64_t* bar_full = reinterpret_cast<uint64_t*>(s_ws + 2 * 2 * kMaxKB);
+  uint64_t* bar_empty = bar_full + stages;
+  uint64_t* bar_pfull = bar_empty + stages;
+  uint64_t* bar_pempty = bar_pfull + 2;
+  uint64_t* bar_sfull = bar_pempty + 2;
+  uint64_t* bar_sempty = bar_sfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_sempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* s_col_row = reinterpret_cast<int*>(tmem_slot + 4);               // [2][128] output row of each token
+  float* s_col_gam = reinterpret_cast<float*>(s_col_row + 2 * 128);     // [2][128]
+  float* s_red = s_col_gam + 2 * 128;                                   // [2][2][128] partial group maxima
+  int* s_blk_off = reinterpret_cast<int*>(s_red + 2 * 2 * 128);         // [E+1]
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&bar_pfull[s]), 1);
+      mbar_init(smem_u32(&bar_pempty[s]), 8);
+      mbar_init(smem_u32(&bar_sfull[s]), 1);
+      mbar_init(smem_u32(&bar_sempty[s]), 8);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+    prefetch_tmap(&tm_w);
+    prefetch_tmap(&tm_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), 512u);
+    tmem_relinquish();
+  }
+  griddep_wait();
+  griddep_launch_dependents();
+  for (int e = threadIdx.x; e <= a.E; e += blockDim.x) s_blk_off[e] = a.blk_off[e];
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const Ctrl c = make_ctrl(a, MODE == 1);
+  const bool active = static_cast<int>(blockIdx.x) < c.grid_eff;
+  constexpr int kTileN = (MODE == 0) ? kTileRows : 2 * kTileRows;
+  const int second_off = (MODE == 0) ? a.up_row_off : kTileRows;
+
+  if (active && warp == 0 && lane == 0) {
+    // =============================== TMA producer ===============================
+    int stage = 0;
+    uint32_t phase = 0;
+    long long issued = 0;
+    bool ok = true;
+    unsigned long long w_empty = 0;
+    const long long role_t0 = clock64();
+    for (int tile = blockIdx.x; ok && tile < c.total; tile += c.grid_eff) {
+      const TileCoord t = decode_tile(tile, c, s_blk_off, a.E, BT, a.num_nt, a.kblocks, kTileN);
+      for (int kb = t.kb0; kb < t.kb1; ++kb) {
+        if (!mbar_wait_t(smem_u32(&bar_empty[stage]), phase ^ 1, abort_flag, DEV_TIMEOUT_PRODUCER, w_empty)) {
+          ok = false;
+          break;
+        }
+        const uint32_t full = smem_u32(&bar_full[stage]);
+        mbar_arrive_expect_tx(full, static_cast<uint32_t>(STAGE_BYTES));
+        const uint32_t sw = smem_u32(smem + static_cast<size_t>(stage) * STAGE_BYTES);
+        const int k0 = kb * kStageKBytes;
+        tma_load_3d(sw, &tm_w, full, k0, t.n0, t.e);
+        tma_load_3d(sw + kTileBytes, &tm_w, full, k0, second_off + t.n0, t.e);
+        tma_load_2d(sw + W_BYTES, &tm_x, full, k0, t.row0);
+        ++issued;
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+    STALL_ADD8(0, w_empty);
+    STALL_ADD8(8, static_cast<unsigned long long>(clock64() - role_t0));
+    if (!ok) {
+      const int n = static_cast<int>(issued < stages ? issued : stages);
+      for (int i = 1; i <= n; ++i) {
+        int s = stage - i;
+        uint32_t ph = phase;
+        if (s < 0) {
+          s += stages;
+          ph ^= 1;
+        }
+        mbar_wait_brief(smem_u32(&bar_full[s]), ph);
+      }
+    }
+  } else if (active && warp == 1 && lane == 0) {
+    // =============================== MMA issuer =================================
+    const uint32_t idesc = make_idesc(0u /* e4m3 */, kTileRows, 256u);
+    int stage = 0;
+    uint32_t phase = 0, j = 0;
+    bool ok = true;
+    unsigned long long w_full = 0, w_pempty = 0;
+    const long long role_t0 = clock64();
+    for (int tile = blockIdx.x; ok && tile < c.total; tile += c.grid_eff) {
+      const TileCoord t = decode_tile(tile, c, s_blk_off, a.E, BT, a.num_nt, a.kblocks, kTileN);
+      for (int kb = t.kb0; kb < t.kb1; ++kb, ++j) {
+        const uint32_t pb = j & 1u;
+        if (!mbar_wait_t(smem_u32(&bar_full[stage]), phase, abort_flag, DEV_TIMEOUT_MMA, w_full) ||
+            !mbar_wait_t(smem_u32(&bar_pempty[pb]), ((j >> 1) & 1u) ^ 1u, abort_flag, DEV_TIMEOUT_MMA, w_pempty)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d0 = tmem_base + pb * PCOLS;
+        const uint32_t sw = smem_u32(smem + static_cast<size_t>(stage) * STAGE_BYTES);
+        const uint64_t dw = smem_desc_k_sw128(sw);             // 256 weight rows: N side
+        const uint64_t dx = smem_desc_k_sw128(sw + W_BYTES);   // 128 token rows: M side
+#pragma unroll
+        for (int k = 0; k < 4; ++k) tc_mma_f8(d0, dx + 2 * k, dw + 2 * k, idesc, k > 0 ? 1u : 0u);
+        tc_commit(smem_u32(&bar_empty[stage]));
+        tc_commit(smem_u32(&bar_pfull[pb]));
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+    STALL_ADD8(1, w_pempty);
+    STALL_ADD8(2, w_full);
+    STALL_ADD8(9, static_cast<unsigned long long>(clock64() - role_t0));
+  } else if (active && warp == 6) {
+    // =============================== per-tile table loader ======================
+    const int kb_total = a.kblocks;
+    int iter = 0;
+    for (int tile = blockIdx.x; tile < c.total; tile += c.grid_eff, ++iter) {
+      const TileCoord t = decode_tile(tile, c, s_blk_off, a.E, BT, a.num_nt, a.kblocks, kTileN);
+      const int buf = iter & 1;
+      if (!mbar_wait(smem_u32(&bar_sempty[buf]), ((iter >> 1) & 1) ^ 1, abort_flag, DEV_TIMEOUT_EPILOGUE)) break;
+      const int nkb = t.kb1 - t.kb0;
+      for (int cidx = lane; cidx < BT; cidx += 32) {
+        const int slot = a.sorted_ids[t.row0 + cidx];
+        const bool valid = slot >= 0 && slot < a.P;
+        s_col_row[buf * 128 + cidx] = valid ? (MODE == 1 ? slot / a.topk : slot) : -1;
+        s_col_gam[buf * 128 + cidx] = valid ? a.row_gamma[t.row0 + cidx] : 0.f;
+      }
+      const int nb0 = t.n0 / 128, nb1 = (second_off + t.n0) / 128;
+      const float* ws0 = a.w_scale + (static_cast<size_t>(t.e) * a.w_scale_rows + nb0) * kb_total + t.kb0;
+      const float* ws1 = a.w_scale + (static_cast<size_t>(t.e) * a.w_scale_rows + nb1) * kb_total + t.kb0;
+      const bool second_ok = nb1 < a.w_scale_rows;
+      float* ws_t = s_ws + buf * 2 * kMaxKB;
+      for (int i = lane; i < nkb; i += 32) {
+        ws_t[i] = __ldg(ws0 + i);
+        ws_t[kMaxKB + i] = second_ok ? __ldg(ws1 + i) : 0.f;
+      }
+      __syncwarp();
+      const uint32_t sfull = smem_u32(&bar_sfull[buf]);
+      if (lane == 0) mbar_arrive_expect_tx(sfull, static_cast<uint32_t>(nkb * BT * 4));
+      __syncwarp();
+      for (int i = lane; i < nkb; i += 32)
+        bulk_copy_g2s(smem_u32(s_xs + (buf * kMaxKB + i) * BT),
+                      a.x_scale + static_cast<size_t>(t.kb0 + i) * a.ld_xscale + t.row0, BT * 4, sfull);
+    }
+  } else if (active && warp >= 2 && warp != 6) {
+    // =============================== promotion + tail ===========================
+    const int grp = warp < 6 ? 0 : 1;
+    const int quad = warp & 3;
+    const int lrow = quad * 32 + lane;  // token row inside the block = TMEM lane
+    const bool w_on_input = (a.flags & B200MOE_FLAG_WEIGHT_ON_INPUT) != 0;
+    // columns of this thread: mode 0 -> gate [64g, 64g+64) and up [128+64g, ..+64); mode 1 -> [128g, 128g+128)
+    const uint32_t colA = (MODE == 0) ? 64u * grp : 128u * grp;
+    const uint32_t colB = (MODE == 0) ? 128u + 64u * grp : 128u * grp + 64u;
+    uint32_t j = 0;
+    int iter = 0;
+    bool ok = true;
+    unsigned long long w_pfull = 0, w_sfull = 0, t_tail = 0;
+    const long long role_t0 = clock64();
+    for (int tile = blockIdx.x; ok && tile < c.total; tile += c.grid_eff, ++iter) {
+      const TileCoord t = decode_tile(tile, c, s_blk_off, a.E, BT, a.num_nt, a.kblocks, kTileN);
+      const int buf = iter & 1;
+      const float* xs_t = s_xs + buf * kMaxKB * BT;
+      const float* ws_t = s_ws + buf * 2 * kMaxKB;
+      if (!mbar_wait_t(smem_u32(&bar_sfull[buf]), (iter >> 1) & 1, abort_flag, DEV_TIMEOUT_EPILOGUE, w_sfull)) break;
+      const int orow = s_col_row[buf * 128 + lrow];
+      const float gam = s_col_gam[buf * 128 + lrow];
+
+      float accA[64], accB[64];
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        accA[i] = 0.f;
+        accB[i] = 0.f;
+      }
+      for (int kb = t.kb0; kb < t.kb1; ++kb, ++j) {
+        const float sx = xs_t[(kb - t.kb0) * BT + lrow];
+        // mode 0: A columns belong to the first weight block, B columns to the second;
+        // mode 1: group g works entirely inside weight block g
+        const float fA = sx * ws_t[(MODE == 0 ? 0 : grp * kMaxKB) + kb - t.kb0];
+        const float fB = sx * ws_t[(MODE == 0 ? kMaxKB : grp * kMaxKB) + kb - t.kb0];
+        const uint32_t pb = j & 1u;
+        if (!mbar_wait_t(smem_u32(&bar_pfull[pb]), (j >> 1) & 1u, abort_flag, DEV_TIMEOUT_EPILOGUE, w_pfull)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + pb * PCOLS;
+#pragma unroll
+        for (int c0 = 0; c0 < 64; c0 += 32) {
+          float g[32], u[32];
+          tmem_ld32x2_wait(taddr + colA + c0, taddr + colB + c0, g, u);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            accA[c0 + i] = fmaf(g[i], fA, accA[c0 + i]);
+            accB[c0 + i] = fmaf(u[i], fB, accB[c0 + i]);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_pempty[pb]));
+      }
+      if (!ok) break;
+      const long long tail_t0 = clock64();
+
+      if (MODE == 0) {
+        // 64 activations of this token; the other 64 of its quantisation group live in the
+        // same lane of the other promotion group
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          float av = act_mul<__nv_bfloat16>(accA[i], accB[i], w_on_input, gam, false, a.activation);
+          av = (a.dtype == B200MOE_DTYPE_BF16) ? __bfloat162float(__float2bfloat16_rn(av))
+                                               : __half2float(__float2half_rn(av));
+          accA[i] = av;
+          amax = fmaxf(amax, fabsf(av));
+        }
+        float* red = s_red + buf * 2 * 128;
+        red[grp * 128 + lrow] = amax;
+        named_bar_sync(2, 256);
+        amax = fmaxf(red[lrow], red[128 + lrow]);
+        const float sc = __fdiv_rn(fmaxf(amax, 1e-10f), 448.0f);
+        const float inv = __fdiv_rn(1.0f, sc);
+        const int r = t.row0 + lrow;
+        if (grp == 0) a.out_scale[static_cast<size_t>(t.n0 / 128) * a.ld_xscale + r] = sc;
+        uint32_t pk[16];
+#pragma unroll
+        for (int q = 0; q < 16; ++q) {
+          uint32_t w = 0;
+#pragma unroll
+          for (int b = 0; b < 4; ++b)
+            w |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(accA[4 * q + b] * inv, __NV_SATFINITE, __NV_E4M3)) << (8 * b);
+          pk[q] = w;
+        }
+        uint4* dst = reinterpret_cast<uint4*>(a.out_q + static_cast<size_t>(r) * a.ld_out + t.n0 + 64 * grp);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) dst[q] = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+      } else if (orow >= 0) {
+        const float scale = w_on_input ? 1.0f : gam;
+        float* out = reinterpret_cast<float*>(a.out) + static_cast<size_t>(orow) * a.ld_out + t.n0 + 128 * grp;
+        if (t.n0 + 128 * grp < a.N) {
+#pragma unroll
+          for (int q = 0; q < 16; ++q) {
+            asm volatile("red.global.v4.f32.add [%0], {%1, %2, %3, %4};" ::"l"(out + 4 * q), "f"(accA[4 * q] * scale),
+                         "f"(accA[4 * q + 1] * scale), "f"(accA[4 * q + 2] * scale), "f"(accA[4 * q + 3] * scale)
+                         : "memory");
+            asm volatile("red.global.v4.f32.add [%0], {%1, %2, %3, %4};" ::"l"(out + 64 + 4 * q),
+                         "f"(accB[4 * q] * scale), "f"(accB[4 * q + 1] * scale), "f"(accB[4 * q + 2] * scale),
+                         "f"(accB[4 * q + 3] * scale)
+                         : "memory");
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_sempty[buf]));
+      t_tail += static_cast<unsigned long long>(clock64() - tail_t0);
+    }
+    if (threadIdx.x == 2 * 32) {
+      STALL_ADD8(5, w_pfull);
+      STALL_ADD8(6, w_sfull);
+      STALL_ADD8(7, t_tail);
+      STALL_ADD8(11, static_cast<unsigned long long>(clock64() - role_t0));
+    }
+  }
+
+  // ---- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512u);
+  }
+  if (threadIdx.x == 0 && *abort_flag != 0) atomicCAS(a.status, 0, *abort_flag);
+}
+
+size_t fp8_tokm_ctrl_bytes(const GemmArgs& a) {
+  return 2 * static_cast<size_t>(kMaxKB) * 128 * 4 + 2 * 2 * kMaxKB * 4 + 512 + 2 * 128 * 8 + 2 * 2 * 128 * 4 +
+         static_cast<size_t>(a.E + 1) * 4 + 64;
+}
+
+template <int MODE>
+int launch_fp8_tokm(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmArgs& a, int num_sms,
+                    cudaStream_t stream) {
+  const size_t smem = 1024 + static_cast<size_t>(a.stages) * (3 * kTileBytes) + fp8_tokm_ctrl_bytes(a);
+  if (smem > kSmemLimit) return B200MOE_ERR_TOO_LARGE;
+  if (cudaFuncSetAttribute(moe_gemm_fp8_tokm_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(smem)) != cudaSuccess)
+    return B200MOE_ERR_CUDA;
+  cudaError_t err = launch_kernel(moe_gemm_fp8_tokm_kernel<MODE>, dim3(num_sms), dim3(kThreadsFp8TokM), smem, stream,
+                                  a.pdl != 0, tm_w, tm_x, a);
+  return err == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
+}
+
 size_t fp8_stage_bytes(const GemmArgs& a) {
   return 2 * static_cast<size_t>(kTileBytes) + static_cast<size_t>(a.BT) * kStageKBytes;
 }
@@ -354,8 +700,19 @@ int launch_fp8(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmArgs&
 
 }  // namespace
 
+#ifdef B200MOE_STALL_STATS
+extern "C" int b200moe_debug_stalls_fp8(unsigned long long* out16, int reset) {
+  if (cudaMemcpyFromSymbol(out16, g_stall_fp8, sizeof(unsigned long long) * 16) != cudaSuccess) return -1;
+  if (reset) {
+    unsigned long long z[16] = {0};
+    cudaMemcpyToSymbol(g_stall_fp8, z, sizeof(z));
+  }
+  return 0;
+}
+#endif
+
 void gemm_plan_fp8(GemmArgs* a) {
-  a->orient = 0;
+  if (a->BT != 128) a->orient = 0;
   const int tile_n = (a->mode == 0) ? kTileRows : 2 * kTileRows;
   a->num_nt = (a->N + tile_n - 1) / tile_n;
   a->kblocks = (a->K + 127) / 128;
@@ -366,6 +723,10 @@ void gemm_plan_fp8(GemmArgs* a) {
   a->tmem_cols = tc;
   a->acc_stages = 2;
   int st = static_cast<int>((kSmemLimit - 1024 - fp8_ctrl_bytes(*a)) / fp8_stage_bytes(*a));
+  if (a->orient == 1) {   // tokens on M, 128-token blocks
+    a->tmem_cols = 512;
+    st = static_cast<int>((kSmemLimit - 1024 - fp8_tokm_ctrl_bytes(*a)) / (3 * kTileBytes));
+  }
   if (st > 10) st = 10;
   if (st < 2) st = 2;
   a->stages = st;
@@ -376,6 +737,9 @@ int launch_gemm_fp8(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const Gemm
                     cudaStream_t stream) {
   if (a.wmode != B200MOE_W_FP8_BLOCK) return B200MOE_ERR_BAD_ARG;
   if (a.K % 128 != 0 || a.N % 128 != 0 || a.K / 128 > kMaxKB) return B200MOE_ERR_UNSUPPORTED;
+  if (a.orient == 1 && a.BT == 128)
+    return a.mode == 0 ? launch_fp8_tokm<0>(tm_w, tm_x, a, num_sms, stream)
+                       : launch_fp8_tokm<1>(tm_w, tm_x, a, num_sms, stream);
 #define B200MOE_FP8_CASE(bt, ng)                                                          \
   case bt:                                                                                \
     return a.mode == 0 ? launch_fp8<0, bt, ng>(tm_w, tm_x, a, num_sms, stream)            \
