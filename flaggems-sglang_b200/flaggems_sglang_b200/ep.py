@@ -15,6 +15,15 @@ tokens with routing over the *global* expert ids.  One call does
   combine    the per-(token, rank) partial sums travel back with the inverse
              all_to_all and the owner adds at most R of them in rank order.
 
+With top-8 routing over at most 8 ranks nearly every token visits nearly every rank, and
+the all-to-all above degenerates: every peer gets the same rows.  `mode="allgather"` (the
+default when the ranks do not outnumber the experts per token) therefore dispatches with
+an all-gather of the token rows and of the packed (ids, weights), lets each rank mask the
+foreign experts through its `expert_map`, and combines with a reduce-scatter, which sums
+the per-rank partial rows inside NCCL (in the NVSwitch where NVLS is active) instead of
+moving all of them to the owner first.  `mode="alltoall"` keeps the slot-per-(peer, token)
+exchange.
+
 The reference has no counterpart: it rejects `expert_map`
 (src/flaggems_sglang/ops/fused_moe.py:160-162) and contains no communication.
 """
@@ -41,6 +50,32 @@ def dispatch_tables(topk_ids: torch.Tensor, topk_weights: torch.Tensor, n_local_
     return out_ids.contiguous(), out_w.contiguous()
 
 
+_expert_maps: dict = {}
+
+
+def local_expert_map(n_global: int, n_local: int, rank: int, device) -> torch.Tensor:
+    """int32 [n_global]: local index of the experts this rank holds, -1 elsewhere."""
+    key = (n_global, n_local, rank, str(device))
+    m = _expert_maps.get(key)
+    if m is None:
+        m = torch.full((n_global,), -1, dtype=torch.int32, device=device)
+        m[rank * n_local:(rank + 1) * n_local] = torch.arange(n_local, dtype=torch.int32, device=device)
+        _expert_maps[key] = m
+    return m
+
+
+def _reduce_scatter_rows(partial: torch.Tensor, m: int, group) -> torch.Tensor:
+    out = torch.empty(m, partial.shape[1], dtype=partial.dtype, device=partial.device)
+    try:
+        dist.reduce_scatter_tensor(out, partial, op=dist.ReduceOp.SUM, group=group)
+    except (RuntimeError, NotImplementedError):     # back ends without reduce-scatter (gloo)
+        full = partial.clone()
+        dist.all_reduce(full, op=dist.ReduceOp.SUM, group=group)
+        r = dist.get_rank(group)
+        out.copy_(full[r * m:(r + 1) * m])
+    return out
+
+
 def ep_fused_experts(
     hidden_states: torch.Tensor,
     w13_local: torch.Tensor,
@@ -49,6 +84,7 @@ def ep_fused_experts(
     topk_ids: torch.Tensor,
     group: Optional[dist.ProcessGroup] = None,
     local_fn: Optional[Callable] = None,
+    mode: Optional[str] = None,
     **kwargs,
 ) -> torch.Tensor:
     """Expert-parallel fused MoE for this rank's tokens ``hidden_states [m, H]``.
@@ -65,6 +101,22 @@ def ep_fused_experts(
     e_loc = w13_local.shape[0]
     if world == 1:
         return local_fn(hidden_states, w13_local, w2_local, topk_weights, topk_ids.to(torch.int32), **kwargs)
+    if mode is None:
+        mode = "allgather" if world <= max(k, 2) else "alltoall"
+    if mode == "allgather":
+        rank = dist.get_rank(group)
+        x = hidden_states.contiguous()
+        xg = torch.empty(world * m, h, dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(xg, x, group=group)
+        meta = torch.cat([topk_ids.to(torch.int32), topk_weights.to(torch.float32).view(torch.int32)], dim=1).contiguous()
+        mg = torch.empty(world * m, 2 * k, dtype=torch.int32, device=x.device)
+        dist.all_gather_into_tensor(mg, meta, group=group)
+        ids_all = mg[:, :k].contiguous()
+        w_all = mg[:, k:].contiguous().view(torch.float32)
+        emap = local_expert_map(e_loc * world, e_loc, rank, x.device)
+        partial = local_fn(xg, w13_local, w2_local, w_all, ids_all, expert_map=emap, **kwargs)
+        return _reduce_scatter_rows(partial.contiguous(), m, group)
+    assert mode == "alltoall", f"unknown expert-parallel mode {mode!r}"
 
     ids_t, w_t = dispatch_tables(topk_ids, topk_weights, e_loc, world)
     send_x = hidden_states.unsqueeze(0).expand(world, m, h).contiguous()

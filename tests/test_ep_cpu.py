@@ -19,9 +19,12 @@ def _free_port():
     return p
 
 
-def _oracle_local(x, w13, w2, tw, ids, **kw):
+def _oracle_local(x, w13, w2, tw, ids, expert_map=None, **kw):
     from oracle import moe as OM
-    return OM.fused_experts(x, w13, w2, tw, ids.to(torch.int64), mimic_rounding=False)
+    ids = ids.to(torch.int64)
+    if expert_map is not None:
+        ids = expert_map.to(torch.int64)[ids]
+    return OM.fused_experts(x, w13, w2, tw, ids, mimic_rounding=False)
 
 
 def _worker(rank, world, port, ret):
@@ -41,11 +44,14 @@ def _worker(rank, world, port, ret):
         e_loc = e // world
         w13, w2 = make_weights(h, i, e, dtype=torch.float32, seed=0, scale=0.1)
         xs, tws, idss = zip(*[make_tokens(m, h, e, k, dtype=torch.float32, seed=10 + r) for r in range(world)])
-        out = ep_fused_experts(xs[rank], w13[rank * e_loc:(rank + 1) * e_loc].contiguous(),
-                               w2[rank * e_loc:(rank + 1) * e_loc].contiguous(), tws[rank], idss[rank],
-                               local_fn=_oracle_local)
         ref = OM.fused_experts(xs[rank], w13, w2, tws[rank], idss[rank], mimic_rounding=False)
-        ret[rank] = float((out - ref).abs().max())
+        err = 0.0
+        for mode in ("alltoall", "allgather"):
+            out = ep_fused_experts(xs[rank], w13[rank * e_loc:(rank + 1) * e_loc].contiguous(),
+                                   w2[rank * e_loc:(rank + 1) * e_loc].contiguous(), tws[rank], idss[rank],
+                                   local_fn=_oracle_local, mode=mode)
+            err = max(err, float((out - ref).abs().max()))
+        ret[rank] = err
     finally:
         dist.destroy_process_group()
 

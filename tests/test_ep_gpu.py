@@ -20,7 +20,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, fp8, ret):
+def _worker(rank, world, port, fp8, mode, ret):
     import sys
     from pathlib import Path
     root = Path(__file__).resolve().parent.parent
@@ -46,12 +46,12 @@ def _worker(rank, world, port, fp8, ret):
             w13q, s13 = quantize_fp8_block(w13)
             w2q, s2 = quantize_fp8_block(w2)
             out = ep_fused_experts(x.to(dev), w13q[lo:hi].contiguous().to(dev), w2q[lo:hi].contiguous().to(dev),
-                                   tw.to(dev), ids.to(dev), use_fp8_w8a8=True,
+                                   tw.to(dev), ids.to(dev), mode=mode, use_fp8_w8a8=True,
                                    w13_scale=s13[lo:hi].contiguous().to(dev), w2_scale=s2[lo:hi].contiguous().to(dev))
             ref = OM.fused_experts_fp8(x, w13q, w2q, s13, s2, tw, ids).float()
         else:
             out = ep_fused_experts(x.to(dev), w13[lo:hi].contiguous().to(dev), w2[lo:hi].contiguous().to(dev),
-                                   tw.to(dev), ids.to(dev), mimic_reference_rounding=False)
+                                   tw.to(dev), ids.to(dev), mode=mode, mimic_reference_rounding=False)
             ref = OM.fused_experts(x, w13, w2, tw, ids, mimic_rounding=False).float()
         torch.cuda.synchronize()
         F.check_status()
@@ -62,15 +62,16 @@ def _worker(rank, world, port, fp8, ret):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("mode", ["alltoall", "allgather"])
 @pytest.mark.parametrize("fp8", [False, True], ids=["bf16", "fp8"])
-def test_ep_two_gpus(fp8):
+def test_ep_two_gpus(fp8, mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     world = 2
     port = _free_port()
     with mp.Manager() as mgr:
         ret = mgr.dict()
-        mp.spawn(_worker, args=(world, port, fp8, ret), nprocs=world, join=True)
+        mp.spawn(_worker, args=(world, port, fp8, mode, ret), nprocs=world, join=True)
         assert len(ret) == world
         for r in range(world):
             max_err, scale, frac = ret[r]
