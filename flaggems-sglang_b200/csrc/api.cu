@@ -91,6 +91,7 @@ void prof_mark(int slot, int mark, cudaStream_t st) {
 
 struct Layout {
   int BT, cap, P;
+  int out_rows;   // rows of the fp32 output buffer: tokens, or pairs when nothing is combined
   int orient;     // GEMM tile orientation that goes with BT
   int act_bytes;  // bytes per activation element fed to the GEMMs
   size_t meta, blk_off, sorted_ids, expert_ids, num_post, row_gamma, xs, xs_scale, a2, a2_scale, out32,
@@ -118,7 +119,10 @@ int check_cfg(const b200moe_cfg* c) {
   if (c == nullptr || c->struct_bytes != static_cast<int32_t>(sizeof(b200moe_cfg))) return B200MOE_ERR_BAD_ARG;
   if (c->M < 0 || c->H <= 0 || c->I <= 0 || c->E <= 0 || c->topk <= 0) return B200MOE_ERR_BAD_ARG;
   if (c->dtype != B200MOE_DTYPE_BF16 && c->dtype != B200MOE_DTYPE_FP16) return B200MOE_ERR_BAD_ARG;
-  if (c->activation != B200MOE_ACT_SILU && c->activation != B200MOE_ACT_GELU) return B200MOE_ERR_BAD_ARG;
+  if (c->activation != B200MOE_ACT_SILU && c->activation != B200MOE_ACT_GELU &&
+      c->activation != B200MOE_ACT_SWIGLU_OAI)
+    return B200MOE_ERR_BAD_ARG;
+  if (c->activation == B200MOE_ACT_SWIGLU_OAI && c->wmode != B200MOE_W_16BIT) return B200MOE_ERR_UNSUPPORTED;
   if (c->block_tokens != 0 && (c->block_tokens < 16 || c->block_tokens > 256 || c->block_tokens % 16))
     return B200MOE_ERR_BAD_ARG;
   if (static_cast<long long>(c->M) * c->topk > (1LL << 24)) return B200MOE_ERR_TOO_LARGE;
@@ -173,7 +177,8 @@ int make_layout(const b200moe_cfg* c, Layout* L) {
   L->xs_scale = take(fp8 ? static_cast<size_t>(cap) * (c->H / 128) * 4 : 0);
   L->a2 = take(static_cast<size_t>(cap) * c->I * L->act_bytes);
   L->a2_scale = take(fp8 ? static_cast<size_t>(cap) * (c->I / 128) * 4 : 0);
-  L->out32 = take(static_cast<size_t>(c->M > 0 ? c->M : 1) * c->H * 4);
+  L->out_rows = (c->flags & B200MOE_FLAG_NO_COMBINE) ? L->P : c->M;   // one fp32 row per pair when nothing is summed
+  L->out32 = take(static_cast<size_t>(L->out_rows > 0 ? L->out_rows : 1) * c->H * 4);
   L->total = off;
   return B200MOE_OK;
 }
@@ -244,11 +249,11 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
   if (fp8) {
     if (quant == nullptr || quant->w1_scale == nullptr || quant->w2_scale == nullptr) return B200MOE_ERR_BAD_ARG;
     rc = launch_group_quant_fp8(x, c->dtype, xs, reinterpret_cast<float*>(ws + L.xs_scale), sorted_ids, meta,
-                                L.P, c->topk, L.cap, c->H, 1, L.cap, out32, static_cast<size_t>(c->M) * c->H * 4,
+                                L.P, c->topk, L.cap, c->H, 1, L.cap, out32, static_cast<size_t>(L.out_rows) * c->H * 4,
                                 sms, st, pdl);
   } else {
     rc = launch_gather_rows(x, xs, sorted_ids, meta, L.P, c->topk, c->H * 2, L.cap, out32,
-                            static_cast<size_t>(c->M) * c->H * 4, sms, st, pdl);
+                            static_cast<size_t>(L.out_rows) * c->H * 4, sms, st, pdl);
   }
   if (rc != B200MOE_OK) return rc;
 
@@ -274,6 +279,12 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
   g1.ld_out = c->I;
   g1.status = status;
   g1.pdl = pdl ? 1 : 0;
+  g1.act_alpha = 1.0f;
+  if (quant != nullptr && !fp8 && !w4) {
+    g1.bias = quant->b1;
+    g1.act_alpha = quant->swiglu_alpha;
+    g1.act_limit = quant->swiglu_limit;
+  }
   if (fp8) {
     g1.w_scale = quant->w1_scale;
     g1.w_scale_rows = (2 * c->I + 127) / 128;
@@ -298,6 +309,8 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
   g2.out = out32;
   g2.ld_out = c->H;
   g2.max_split = 0;
+  if (c->flags & B200MOE_FLAG_NO_COMBINE) g2.topk = 1;   // output row = pair slot instead of token
+  g2.bias = (quant != nullptr && !fp8 && !w4) ? quant->b2 : nullptr;
   if (w4) {
     g2.w_sz = quant->w2_sz;
     g2.w_rows = c->H;
@@ -352,7 +365,8 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
     prof_mark(slot, 4, st);
     if (rc != B200MOE_OK) return rc;
   }
-  rc = launch_finalize(out32, out, c->dtype, static_cast<size_t>(c->M) * c->H, c->routed_scaling, sms, st, pdl);
+  rc = launch_finalize(out32, out, c->dtype, static_cast<size_t>(L.out_rows) * c->H,
+                       (c->flags & B200MOE_FLAG_NO_COMBINE) ? 1.0f : c->routed_scaling, sms, st, pdl);
   prof_mark(slot, 5, st);
   return rc;
 }

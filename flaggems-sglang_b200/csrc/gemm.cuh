@@ -40,6 +40,9 @@ struct GemmArgs {
   const float* x_scale;   // [K/128][ld_xscale] group-major activation scales
   int ld_xscale;
   int w_scale_rows;       // scale rows per expert
+  const float* bias;      // optional per-expert bias of this GEMM's output rows: [E, rows] fp32 (mode 0: gate rows then up rows)
+  float act_alpha;        // B200MOE_ACT_SWIGLU_OAI: s = g * sigmoid(alpha * g)
+  float act_limit;        // B200MOE_ACT_SWIGLU_OAI: clamp gate to <= limit and linear to [-limit, limit]; <= 0: none
   const void* w_sz;       // int4: per (expert, group of 128 k, weight row) fp16 scale | fp16 (1024 + zero)
   int w_rows;             // int4: weight rows per expert (2I for mode 0, H for mode 1)
   uint8_t* out_q;         // mode 0 FP8: quantised activations [cap, N]

@@ -280,7 +280,7 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         float* red = s_red + (buf * 2 + grp) * 4 * 64;
 #pragma unroll
         for (int i = 0; i < CPT; ++i) {
-          float av = act_mul<__nv_bfloat16>(acc0[i], acc1[i], w_on_input, col_gam[i], false, a.activation);
+          float av = act_mul<__nv_bfloat16>(acc0[i], acc1[i], w_on_input, col_gam[i], false, act_params(a));
           av = (a.dtype == B200MOE_DTYPE_BF16) ? __bfloat162float(__float2bfloat16_rn(av))
                                                : __half2float(__float2half_rn(av));
           acc0[i] = av;
@@ -594,7 +594,7 @@ moe_gemm_fp8_tokm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
         float amax = 0.f;
 #pragma unroll
         for (int i = 0; i < 64; ++i) {
-          float av = act_mul<__nv_bfloat16>(accA[i], accB[i], w_on_input, gam, false, a.activation);
+          float av = act_mul<__nv_bfloat16>(accA[i], accB[i], w_on_input, gam, false, act_params(a));
           av = (a.dtype == B200MOE_DTYPE_BF16) ? __bfloat162float(__float2bfloat16_rn(av))
                                                : __half2float(__float2half_rn(av));
           accA[i] = av;

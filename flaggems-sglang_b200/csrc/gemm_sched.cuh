@@ -69,11 +69,32 @@ __device__ __forceinline__ TileCoord decode_tile(int id, const Ctrl& c, const in
 }
 
 
-// Fused tail of the gate/up projection: optional routing weight, optional rounding of the
-// two projections to the 16-bit type (as the reference stores them), activation, product.
-template <typename T>
+// Fused tail of the gate/up projection.
+//   SiLU / GELU (the reference's plain op, fused_moe.py:198-206): optional routing weight on the
+//   two projections, optional rounding of both to the 16-bit type (as the reference stores
+//   them), activation(gate) * up.
+//   B200MOE_ACT_SWIGLU_OAI (the reference's bias variant fuses its dependency's swiglu into
+//   GEMM-1, fused_moe.py:258-298): gate clamped from above, linear clamped to [-limit, limit],
+//   s = g / (1 + exp(-alpha * g)), result s * (linear + 1); the routing weight, if it goes on
+//   the input side, multiplies the result.
+struct ActParams {
+  int activation;
+  float alpha, limit;
+};
+// EXT = false compiles the SiLU / GELU tail only: the epilogues are bound by their instruction
+// count, so the plain kernels must not carry the extra tests.
+template <typename T, bool EXT = false>
 __device__ __forceinline__ float act_mul(float g, float u, bool w_on_input, float gam, bool mimic,
-                                         int activation) {
+                                         const ActParams& p) {
+  if (EXT && p.activation == B200MOE_ACT_SWIGLU_OAI) {
+    if (p.limit > 0.f) {
+      g = fminf(g, p.limit);
+      u = fminf(fmaxf(u, -p.limit), p.limit);
+    }
+    const float s = __fdividef(g, 1.0f + __expf(-p.alpha * g));
+    const float r = fmaf(s, u, s);
+    return w_on_input ? r * gam : r;
+  }
   if (w_on_input) {
     g *= gam;
     u *= gam;
@@ -82,8 +103,15 @@ __device__ __forceinline__ float act_mul(float g, float u, bool w_on_input, floa
     g = to_f32<T>(from_f32<T>(g));
     u = to_f32<T>(from_f32<T>(u));
   }
-  const float s = (activation == B200MOE_ACT_SILU) ? __fdividef(g, 1.0f + __expf(-g)) : gelu_f32(g);
+  const float s = (p.activation == B200MOE_ACT_SILU) ? __fdividef(g, 1.0f + __expf(-g)) : gelu_f32(g);
   return s * u;
+}
+__device__ __forceinline__ ActParams act_params(const GemmArgs& a) {
+  ActParams p;
+  p.activation = a.activation;
+  p.alpha = a.act_alpha;
+  p.limit = a.act_limit;
+  return p;
 }
 
 // Work decomposition for one launch; identical in every thread of every CTA.

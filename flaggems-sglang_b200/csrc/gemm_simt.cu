@@ -1,7 +1,7 @@
 // Plain CUDA-core versions of the two grouped GEMMs, one CTA per padded row.
 // Slow; they exist to validate the routing tables and the fused tails separately
 // from the tensor-core pipeline (B200MOE_FLAG_SIMT).  16-bit weights, layer layout.
-#include "gemm.cuh"
+#include "gemm_sched.cuh"
 
 namespace b200moe {
 
@@ -38,12 +38,14 @@ moe_gemm_simt_kernel(const T* __restrict__ w, const T* __restrict__ x, const Gem
       if (MODE == 0) u += xv * to_f32<T>(wu[k]);
     }
     if (MODE == 0) {
-      if (w_on_input) { g *= gam; u *= gam; }
-      if (mimic) { g = to_f32<T>(from_f32<T>(g)); u = to_f32<T>(from_f32<T>(u)); }
-      const float av = (a.activation == B200MOE_ACT_SILU ? silu_f32(g) : gelu_f32(g)) * u;
+      if (a.bias != nullptr) {
+        g += a.bias[static_cast<size_t>(e) * 2 * a.N + n];
+        u += a.bias[static_cast<size_t>(e) * 2 * a.N + a.N + n];
+      }
+      const float av = act_mul<T, true>(g, u, w_on_input, gam, mimic, act_params(a));
       reinterpret_cast<T*>(a.out)[static_cast<size_t>(r) * a.ld_out + n] = from_f32<T>(av);
     } else if (valid) {
-      float y = g;
+      float y = g + (a.bias != nullptr ? a.bias[static_cast<size_t>(e) * a.N + n] : 0.f);
       if (!w_on_input) y *= gam;
       if (mimic) y = to_f32<T>(from_f32<T>(y));
       atomicAdd(reinterpret_cast<float*>(a.out) + static_cast<size_t>(slot / a.topk) * a.ld_out + n, y);

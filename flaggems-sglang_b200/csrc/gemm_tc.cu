@@ -75,7 +75,9 @@ constexpr int kThreadsW4 = kThreads + 32 * kDequantWarps;
 
 // W4: the weight operand is int4 (AWQ, group 128, pre-packed): TMA stages the packed rows,
 // eight extra warps dequantise them into the swizzled fp16 operand tile the MMA reads.
-template <int MODE, typename T, int ORIENT, bool W4>
+// EXT: per-expert bias and the clamped swiglu in the epilogues (separate instantiations, so
+// that the plain kernels keep their shorter epilogue loops).
+template <int MODE, typename T, int ORIENT, bool W4, bool EXT>
 __global__ void __launch_bounds__(W4 ? kThreadsW4 : kThreads, 1)
 moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                    const GemmArgs a) {
@@ -296,6 +298,8 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     const bool w_on_input = (a.flags & B200MOE_FLAG_WEIGHT_ON_INPUT) != 0;
     const bool mimic = (a.flags & B200MOE_FLAG_MIMIC_ROUNDING) != 0;
     const bool round_pair = mimic && c.split == 1;
+    const ActParams ap = act_params(a);
+    const bool has_bias = EXT && a.bias != nullptr;
     int acc = 0, iter = 0;
     uint32_t acc_phase = 0;
     for (int tile = blockIdx.x; tile < c.total; tile += c.grid_eff, ++iter) {
@@ -319,11 +323,21 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
           for (int c0 = 0; c0 < 128; c0 += 16) {
             float g[16], u[16];
             tmem_ld16x2_wait(taddr + c0, taddr + 128 + c0, g, u);
+            if (has_bias) {
+              // gate rows first, then the up / linear rows of the same expert
+              const float* bg = a.bias + static_cast<size_t>(t.e) * 2 * a.N + t.n0 + c0;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const bool in = t.n0 + c0 + j < a.N;
+                g[j] += in ? __ldg(bg + j) : 0.f;
+                u[j] += in ? __ldg(bg + a.N + j) : 0.f;
+              }
+            }
             uint32_t pk[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              const float lo = act_mul<T>(g[2 * j], u[2 * j], w_on_input, gam, mimic, a.activation);
-              const float hi = act_mul<T>(g[2 * j + 1], u[2 * j + 1], w_on_input, gam, mimic, a.activation);
+              const float lo = act_mul<T, EXT>(g[2 * j], u[2 * j], w_on_input, gam, mimic, ap);
+              const float hi = act_mul<T, EXT>(g[2 * j + 1], u[2 * j + 1], w_on_input, gam, mimic, ap);
               pk[j] = pack2<T>(lo, hi);
             }
             if (in_block && t.n0 + c0 + 8 <= a.N)
@@ -340,6 +354,11 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             float v[16];
             tmem_ld16_wait(taddr + c0, v);
             if (valid) {
+              if (has_bias && t.kb0 == 0) {   // the first reduction split carries the bias
+                const float* bo = a.bias + static_cast<size_t>(t.e) * a.N + t.n0 + c0;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] += (t.n0 + c0 + j < a.N) ? __ldg(bo + j) : 0.f;
+              }
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
                 v[j] *= scale;
@@ -370,18 +389,24 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         const bool n_ok = n < a.N;
         if (MODE == 0) {
           T* out = reinterpret_cast<T*>(a.out) + static_cast<size_t>(t.row0) * a.ld_out + n;
+          float bgate = 0.f, bup = 0.f;
+          if (has_bias && n_ok) {
+            bgate = __ldg(a.bias + static_cast<size_t>(t.e) * 2 * a.N + n);
+            bup = __ldg(a.bias + static_cast<size_t>(t.e) * 2 * a.N + a.N + n);
+          }
 #pragma unroll 1
           for (int c0 = 0; c0 < BT; c0 += 16) {
             float g[16], u[16];
             tmem_ld16x2_wait(taddr + c0, taddr + BT + c0, g, u);
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              const float av = act_mul<T>(g[j], u[j], w_on_input, col_gam[c0 + j], mimic, a.activation);
+              const float av = act_mul<T, EXT>(g[j] + bgate, u[j] + bup, w_on_input, col_gam[c0 + j], mimic, ap);
               if (n_ok) out[static_cast<size_t>(c0 + j) * a.ld_out] = from_f32<T>(av);
             }
           }
         } else {
           float* out = reinterpret_cast<float*>(a.out) + n;
+          const float bout = (has_bias && n_ok && t.kb0 == 0) ? __ldg(a.bias + static_cast<size_t>(t.e) * a.N + n) : 0.f;
 #pragma unroll 1
           for (int c0 = 0; c0 < BT; c0 += 16) {
             float v[16];
@@ -390,7 +415,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             for (int j = 0; j < 16; ++j) {
               const int orow = col_row[c0 + j];
               if (orow >= 0 && n_ok) {
-                float y = v[j];
+                float y = v[j] + bout;
                 if (!w_on_input) y *= col_gam[c0 + j];
                 if (round_pair) y = to_f32<T>(from_f32<T>(y));
                 atomicAdd(out + static_cast<size_t>(orow) * a.ld_out, y);
@@ -457,28 +482,28 @@ size_t gemm_smem_bytes(const GemmArgs& a) {
   return 1024 + static_cast<size_t>(a.stages) * stage_bytes_of(a) + ctrl_bytes_of(a);
 }
 
-template <int MODE, typename T, int ORIENT, bool W4 = false>
+template <int MODE, typename T, int ORIENT, bool W4 = false, bool EXT = false>
 static int launch_one(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmArgs& a, int num_sms,
                       cudaStream_t stream) {
   const size_t smem = gemm_smem_bytes(a);
   if (smem > kSmemLimit) return B200MOE_ERR_TOO_LARGE;
-  cudaError_t err = cudaFuncSetAttribute(moe_gemm_tc_kernel<MODE, T, ORIENT, W4>,
+  cudaError_t err = cudaFuncSetAttribute(moe_gemm_tc_kernel<MODE, T, ORIENT, W4, EXT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem));
   if (err != cudaSuccess) return B200MOE_ERR_CUDA;
-  err = launch_kernel(moe_gemm_tc_kernel<MODE, T, ORIENT, W4>, dim3(num_sms), dim3(W4 ? kThreadsW4 : kThreads), smem,
+  err = launch_kernel(moe_gemm_tc_kernel<MODE, T, ORIENT, W4, EXT>, dim3(num_sms), dim3(W4 ? kThreadsW4 : kThreads), smem,
                       stream, a.pdl != 0, tm_w, tm_x, a);
   return err == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
 }
 
-template <typename T>
+template <typename T, bool EXT>
 static int launch_typed(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmArgs& a, int num_sms,
                         cudaStream_t stream) {
   if (a.orient == 1)
-    return a.mode == 0 ? launch_one<0, T, 1>(tm_w, tm_x, a, num_sms, stream)
-                       : launch_one<1, T, 1>(tm_w, tm_x, a, num_sms, stream);
-  return a.mode == 0 ? launch_one<0, T, 0>(tm_w, tm_x, a, num_sms, stream)
-                     : launch_one<1, T, 0>(tm_w, tm_x, a, num_sms, stream);
+    return a.mode == 0 ? launch_one<0, T, 1, false, EXT>(tm_w, tm_x, a, num_sms, stream)
+                       : launch_one<1, T, 1, false, EXT>(tm_w, tm_x, a, num_sms, stream);
+  return a.mode == 0 ? launch_one<0, T, 0, false, EXT>(tm_w, tm_x, a, num_sms, stream)
+                     : launch_one<1, T, 0, false, EXT>(tm_w, tm_x, a, num_sms, stream);
 }
 
 int launch_gemm_tc(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmArgs& a, int num_sms,
@@ -494,8 +519,12 @@ int launch_gemm_tc(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmA
                        : launch_one<1, __half, 0, true>(tm_w, tm_x, a, num_sms, stream);
   }
   if (a.wmode != B200MOE_W_16BIT) return B200MOE_ERR_UNSUPPORTED;
-  if (a.dtype == B200MOE_DTYPE_BF16) return launch_typed<__nv_bfloat16>(tm_w, tm_x, a, num_sms, stream);
-  return launch_typed<__half>(tm_w, tm_x, a, num_sms, stream);
+  const bool ext = a.bias != nullptr || a.activation == B200MOE_ACT_SWIGLU_OAI;
+  if (a.dtype == B200MOE_DTYPE_BF16)
+    return ext ? launch_typed<__nv_bfloat16, true>(tm_w, tm_x, a, num_sms, stream)
+               : launch_typed<__nv_bfloat16, false>(tm_w, tm_x, a, num_sms, stream);
+  return ext ? launch_typed<__half, true>(tm_w, tm_x, a, num_sms, stream)
+             : launch_typed<__half, false>(tm_w, tm_x, a, num_sms, stream);
 }
 
 }  // namespace b200moe

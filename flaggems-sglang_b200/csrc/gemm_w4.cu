@@ -389,7 +389,7 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         const bool n_ok = n < a.N;
 #pragma unroll
         for (int i = 0; i < BT; ++i) {
-          const float av = act_mul<__half>(acc0[i], acc1[i], w_on_input, col_gam[i], mimic, a.activation);
+          const float av = act_mul<__half>(acc0[i], acc1[i], w_on_input, col_gam[i], mimic, act_params(a));
           if (n_ok) out[static_cast<size_t>(i) * a.ld_out] = __float2half_rn(av);
         }
       } else {

@@ -15,10 +15,10 @@ ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_T
 DTYPE_BF16, DTYPE_FP16 = 0, 1
 W_16BIT, W_FP8_BLOCK, W_INT4_AWQ = 0, 1, 2
 LAYOUT_LAYER, LAYOUT_OP = 0, 1
-ACT_SILU, ACT_GELU = 0, 1
+ACT_SILU, ACT_GELU, ACT_SWIGLU_OAI = 0, 1, 2
 NOALLOC_SCRATCH_BYTES = 16 * 1024 * 1024
 FLAG_WEIGHT_ON_INPUT, FLAG_MIMIC_ROUNDING, FLAG_SIMT, FLAG_IDS_I64, FLAG_NO_SPLIT_K, \
-    FLAG_NO_GRID_BALANCE, FLAG_NO_PDL, FLAG_W4_SMEM_OPERANDS = 1, 2, 4, 8, 16, 32, 64, 128
+    FLAG_NO_GRID_BALANCE, FLAG_NO_PDL, FLAG_W4_SMEM_OPERANDS, FLAG_NO_COMBINE = 1, 2, 4, 8, 16, 32, 64, 128, 256
 
 
 class Cfg(C.Structure):
@@ -31,7 +31,8 @@ class Cfg(C.Structure):
 
 
 class Quant(C.Structure):
-    _fields_ = [("w1_scale", C.c_void_p), ("w2_scale", C.c_void_p), ("w1_sz", C.c_void_p), ("w2_sz", C.c_void_p)]
+    _fields_ = [("w1_scale", C.c_void_p), ("w2_scale", C.c_void_p), ("w1_sz", C.c_void_p), ("w2_sz", C.c_void_p),
+                ("b1", C.c_void_p), ("b2", C.c_void_p), ("swiglu_alpha", C.c_float), ("swiglu_limit", C.c_float)]
 
 
 # name -> (restype, argtypes); every symbol include/b200moe.h declares

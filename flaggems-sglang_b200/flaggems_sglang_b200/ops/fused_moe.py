@@ -24,7 +24,7 @@ logger = logging.getLogger(__name__)
 _UNSUPPORTED_FEATURE_MSG = "{name} is not supported"
 
 _DTYPES = {torch.bfloat16: _lib.DTYPE_BF16, torch.float16: _lib.DTYPE_FP16}
-_ACTS = {"silu": _lib.ACT_SILU, "gelu": _lib.ACT_GELU}
+_ACTS = {"silu": _lib.ACT_SILU, "gelu": _lib.ACT_GELU, "swiglu_oai": _lib.ACT_SWIGLU_OAI}
 
 # ---------------------------------------------------------------------------- state
 _workspaces: dict = {}     # (device index, stream handle) -> uint8 tensor
@@ -132,8 +132,22 @@ def fused_experts(
     use_int4_w4a16: bool = False,
     w13_sz: Optional[torch.Tensor] = None,
     w2_sz: Optional[torch.Tensor] = None,
+    b13: Optional[torch.Tensor] = None,
+    b2: Optional[torch.Tensor] = None,
+    swiglu_alpha: float = 1.0,
+    swiglu_limit: Optional[float] = None,
+    no_combine: bool = False,
 ) -> torch.Tensor:
     """Fused experts on layer-layout weights ``w13 [E, 2I, H]``, ``w2 [E, H, I]``.
+
+    ``no_combine``: return ``[M, topk, H]``, one weighted expert output per (token, choice)
+    pair instead of their sum; ``routed_scaling_factor`` is not applied (the reference's
+    adapter skips it too, src/flaggems_sglang/ops/fused_moe.py:399-404).
+
+    ``b13 [E, 2I]`` / ``b2 [E, H]`` (16-bit weights only): per-expert biases added to
+    the two projections.  ``activation="swiglu_oai"``: ``s = g * sigmoid(alpha * g)``,
+    ``out = s * (linear + 1)`` with the gate clamped from above and the linear half
+    clamped to ``[-limit, limit]`` when ``swiglu_limit`` is given.
 
     ``use_int4_w4a16``: ``w13`` / ``w2`` are the packed int4 rows ``[E, 2I, H/8]`` /
     ``[E, H, I/8]`` int32 and ``w13_sz`` / ``w2_sz`` the scale/zero tables from
@@ -184,6 +198,20 @@ def fused_experts(
         quant = _lib.Quant(None, None, z1.data_ptr(), z2.data_ptr())
     else:
         assert w13.dtype == x.dtype and w2.dtype == x.dtype, "weights must have the activation dtype"
+        if b13 is not None or b2 is not None or activation == "swiglu_oai":
+            bias1 = b13.to(torch.float32).contiguous() if b13 is not None else None
+            bias2 = b2.to(torch.float32).contiguous() if b2 is not None else None
+            if bias1 is not None:
+                assert bias1.shape == (e, 2 * i), "b13 must be [E, 2I]"
+            if bias2 is not None:
+                assert bias2.shape == (e, h), "b2 must be [E, H]"
+            quant = _lib.Quant(None, None, None, None,
+                               bias1.data_ptr() if bias1 is not None else None,
+                               bias2.data_ptr() if bias2 is not None else None,
+                               float(swiglu_alpha), float(swiglu_limit) if swiglu_limit else 0.0)
+    if quant is None or wmode != _lib.W_16BIT:
+        assert b13 is None and b2 is None and activation != "swiglu_oai", \
+            "biases and the clamped swiglu are available with 16-bit weights only"
 
     lib = _lib.lib()
     if routing is None:
@@ -200,9 +228,11 @@ def fused_experts(
         topk_indx = topk_indx.to(torch.int32).contiguous()
         gate_scal = gate_scal.to(torch.float32).contiguous()
 
+    if no_combine:
+        flags |= _lib.FLAG_NO_COMBINE
     cfg = _make_cfg(m, h, i, e, k, dtype, wmode, _ACTS[activation], flags,
                     block_tokens or _block_tokens_env(), float(routed_scaling_factor))
-    out = torch.empty((m, h), dtype=x.dtype, device=dev)
+    out = torch.empty((m, k, h) if no_combine else (m, h), dtype=x.dtype, device=dev)
     if m == 0:
         return out
     nbytes = lib.b200moe_workspace_bytes(C.byref(cfg))
@@ -318,6 +348,21 @@ def triton_kernel_fused_experts(
     return out.view(hidden_states.shape[0], hidden_states.shape[1])
 
 
+def _deinterleaved(w1: torch.Tensor, b1: torch.Tensor, layer_layout: bool = False):
+    """The bias variant stores gate and linear outputs interleaved (even = gate, odd =
+    linear; the dependency's swiglu splits them that way).  The kernels want the gate rows
+    first and the linear rows after them: re-laid out once per weight tensor object.
+    ``w1`` is ``[E, H, 2I]`` (op level) or, with ``layer_layout``, ``[E, 2I, H]``."""
+    ent = _relayout.get(w1)
+    if ent is None or ent[0] != w1._version or ent[1] != w1.data_ptr() or ent[2] != b1._version:
+        rows = w1 if layer_layout else w1.transpose(1, 2)                                   # [E, 2I, H]
+        w13 = torch.cat([rows[:, 0::2, :], rows[:, 1::2, :]], dim=1).contiguous()
+        b13 = torch.cat([b1[:, 0::2], b1[:, 1::2]], dim=1).to(torch.float32).contiguous()   # [E, 2I]
+        ent = (w1._version, w1.data_ptr(), b1._version, (w13, b13))
+        _relayout[w1] = ent
+    return ent[3]
+
+
 def triton_kernel_fused_experts_with_bias(
     hidden_states: torch.Tensor,
     w1: torch.Tensor,
@@ -336,15 +381,28 @@ def triton_kernel_fused_experts_with_bias(
     gemm1_alpha: Optional[float] = None,
     gemm1_clamp_limit: Optional[float] = None,
 ) -> torch.Tensor:
-    """Signature of the reference's bias variant
-    (src/flaggems_sglang/ops/fused_moe.py:219-309).  Not built yet: the variant
-    is untested upstream and sits outside the measured path."""
+    """Bias variant of the op, same signature as the reference's
+    (src/flaggems_sglang/ops/fused_moe.py:219-309): ``w1 [E, H, 2I]`` with gate and linear
+    columns interleaved, ``b1 [E, 2I]`` likewise, ``w2 [E, I, H]``, ``b2 [E, H]``.
+    GEMM-1 adds ``b1`` and applies ``s = g * sigmoid(alpha * g)``, ``s * (linear + 1)``
+    (gate clamped to ``<= limit``, linear to ``[-limit, limit]``) in its epilogue; GEMM-2 adds
+    ``b2`` before the routing weight.  ``w1_pcg`` / ``w2_pcg`` (the dependency's precision
+    configs) must be None or plain bf16 configs: they carry nothing this path uses."""
     logger.debug("FLAGGEMS_SGLANG FUSED_MOE_WITH_BIAS")
     assert inplace is False, "Inplace is not supported"
     assert hidden_states.dtype == torch.bfloat16, "hidden_states must be bfloat16"
     if activation != "silu":
         raise ValueError(f"Unsupported FusedMoe activation: {activation}")
-    raise NotImplementedError("per-expert bias / interleaved swiglu variant is not implemented")
+    assert w1.dtype == torch.bfloat16 and w2.dtype == torch.bfloat16, "weights must be bfloat16"
+    assert hidden_states.shape[-1] == w1.shape[-2], "hidden size mismatch"
+    assert w2.shape[-1] == w1.shape[1], "intermediate size mismatch"
+    w13, b13 = _deinterleaved(w1, b1)
+    routing = (routing_data.expt_hist, gather_indx.src_indx, routing_data.gate_scal, routing_data.n_expts_act)
+    out = fused_experts(hidden_states, w13, _layer_layout(w2), routing=routing, activation="swiglu_oai",
+                        apply_router_weight_on_input=apply_router_weight_on_input, b13=b13, b2=b2,
+                        swiglu_alpha=1.0 if gemm1_alpha is None else float(gemm1_alpha),
+                        swiglu_limit=gemm1_clamp_limit)
+    return out.view(hidden_states.shape[0], hidden_states.shape[1])
 
 
 def fused_moe_flagos(obj, layer: torch.nn.Module, dispatch_output):
@@ -358,22 +416,33 @@ def fused_moe_flagos(obj, layer: torch.nn.Module, dispatch_output):
     cfg = obj.runner.config
     hidden_states = dispatch_output.hidden_states
     topk_output = dispatch_output.topk_output
-    if getattr(cfg, "no_combine", False):
-        raise NotImplementedError("no_combine is not implemented")
-    if getattr(layer, "w13_weight_bias", None) is not None or getattr(layer, "w2_weight_bias", None) is not None:
-        raise NotImplementedError("per-expert bias is not implemented")
+    no_combine = bool(getattr(cfg, "no_combine", False))
+    b13 = getattr(layer, "w13_weight_bias", None)
+    b2 = getattr(layer, "w2_weight_bias", None)
+    has_bias = b13 is not None or b2 is not None
+    if has_bias:
+        assert b13 is not None and b2 is not None, "Bias execution requires both w13_bias and w2_bias"
     scale = getattr(cfg, "routed_scaling_factor", None)
     scale = 1.0 if scale is None else float(scale)
     common = dict(activation=cfg.activation,
                   apply_router_weight_on_input=bool(getattr(cfg, "apply_router_weight_on_input", False)),
-                  routed_scaling_factor=scale)
+                  routed_scaling_factor=scale, no_combine=no_combine)
+    w13 = layer.w13_weight
+    if has_bias:
+        if cfg.activation != "silu":
+            raise ValueError(f"Unsupported FusedMoe activation: {cfg.activation}")
+        # biased layers keep gate and linear rows interleaved: split them once per weight object
+        w13, b13 = _deinterleaved(layer.w13_weight, b13, layer_layout=True)
+        alpha = getattr(cfg, "gemm1_alpha", None)
+        common.update(activation="swiglu_oai", b13=b13, b2=b2, swiglu_alpha=1.0 if alpha is None else float(alpha),
+                      swiglu_limit=getattr(cfg, "gemm1_clamp_limit", None))
     if hasattr(topk_output, "topk_weights"):
-        out = fused_experts(hidden_states, layer.w13_weight, layer.w2_weight,
+        out = fused_experts(hidden_states, w13, layer.w2_weight,
                             topk_output.topk_weights, topk_output.topk_ids, **common)
     else:
         routing_data, gather_indx, _ = topk_output
         routing = (routing_data.expt_hist, gather_indx.src_indx, routing_data.gate_scal, routing_data.n_expts_act)
-        out = fused_experts(hidden_states, layer.w13_weight, layer.w2_weight, routing=routing, **common)
+        out = fused_experts(hidden_states, w13, layer.w2_weight, routing=routing, **common)
     try:
         from sglang.srt.layers.moe.token_dispatcher.standard import StandardCombineInput
         return StandardCombineInput(hidden_states=out)

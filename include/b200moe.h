@@ -47,6 +47,7 @@ extern "C" {
 
 #define B200MOE_ACT_SILU 0
 #define B200MOE_ACT_GELU 1
+#define B200MOE_ACT_SWIGLU_OAI 2 /* s = g*sigmoid(alpha*g) with clamps; out = s*(linear + 1): the bias variant's activation */
 
 /* cfg.flags */
 #define B200MOE_FLAG_WEIGHT_ON_INPUT 1  /* router weight scales GEMM-1's output, not GEMM-2's */
@@ -57,6 +58,9 @@ extern "C" {
 #define B200MOE_FLAG_NO_GRID_BALANCE 32 /* tuning aid: every CTA takes tiles round-robin       */
 #define B200MOE_FLAG_NO_PDL 64          /* launch every kernel fully serialised                */
 #define B200MOE_FLAG_W4_SMEM_OPERANDS 128 /* int4: always stage fp16 operands in shared memory (tuning aid) */
+#define B200MOE_FLAG_NO_COMBINE 256     /* out is [M*topk, H]: row t*topk+j holds pair j of token t,
+                                           routing weight applied, nothing summed, routed_scaling ignored
+                                           (the adapter's no_combine, fused_moe.py:392-397)               */
 
 typedef struct b200moe_cfg {
   int32_t struct_bytes;   /* sizeof(b200moe_cfg), checked                      */
@@ -75,7 +79,8 @@ typedef struct b200moe_cfg {
   int32_t num_sms;        /* 0 = query the current device                       */
 } b200moe_cfg;
 
-/* scales / zero points for the quantised weight modes (NULL members unused) */
+/* scales / zero points for the quantised weight modes and the optional per-expert biases
+ * (NULL members unused) */
 typedef struct b200moe_quant {
   const float *w1_scale;  /* FP8: [E, ceil(2I/128), ceil(H/128)]                 */
   const float *w2_scale;  /* FP8: [E, ceil(H/128), ceil(I/128)]                  */
@@ -85,6 +90,14 @@ typedef struct b200moe_quant {
    * flaggems_sglang_b200.quant.repack_awq_for_kernel builds both from AWQ checkpoint tensors. */
   const void *w1_sz;
   const void *w2_sz;
+  /* 16-bit weights only: per-expert biases, fp32.  b1 [E, 2I] (gate rows, then up / linear
+   * rows, matching w1's row order), b2 [E, H]; added to the GEMM outputs before activation /
+   * routing weight, as triton_kernel_fused_experts_with_bias does
+   * (src/flaggems_sglang/ops/fused_moe.py:285-308). */
+  const float *b1;
+  const float *b2;
+  float swiglu_alpha;     /* B200MOE_ACT_SWIGLU_OAI */
+  float swiglu_limit;     /* B200MOE_ACT_SWIGLU_OAI: <= 0 disables the clamps */
 } b200moe_quant;
 
 int b200moe_version(void);

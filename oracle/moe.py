@@ -72,6 +72,20 @@ def gelu_mul(y1: torch.Tensor) -> torch.Tensor:
     return torch.nn.functional.gelu(g) * u
 
 
+def swiglu_oai(y1: torch.Tensor, alpha: float = 1.0, limit=None) -> torch.Tensor:
+    """Activation the reference's bias variant fuses into GEMM-1 (its dependency's swiglu:
+    triton_kernels/swiglu_details/_swiglu.py, compute_swiglu): on [gate | linear] halves,
+    gate clamped from above, linear to [-limit, limit], s = g / (1 + exp(-alpha g)),
+    result s * linear + s."""
+    i = y1.shape[-1] // 2
+    g, u = y1[..., :i].float(), y1[..., i:].float()
+    if limit is not None and limit > 0:
+        g = torch.minimum(g, torch.tensor(float(limit)))
+        u = u.clamp(-float(limit), float(limit))
+    s = g / (1.0 + torch.exp(-alpha * g))
+    return s * u + s
+
+
 def _n_local(w1) -> int:
     return w1.shape[0] if hasattr(w1, "shape") else w1.n_experts
 
@@ -95,6 +109,10 @@ def fused_experts(
     act_quant=None,
     expert_lo: int = 0,
     no_combine: bool = False,
+    b1=None,
+    b2=None,
+    swiglu_alpha: float = 1.0,
+    swiglu_limit=None,
 ) -> torch.Tensor:
     """x [M, H]; w1 [E, 2I, H] / w2 [E, H, I] tensors (any float dtype), or
     callables ``e -> fp32 matrix`` for lazily dequantised weights.
@@ -113,7 +131,8 @@ def fused_experts(
     n_local = w1.shape[0] if hasattr(w1, "shape") else w1.n_experts
     get1 = (lambda e: w1[e].float()) if hasattr(w1, "shape") else w1
     get2 = (lambda e: w2[e].float()) if hasattr(w2, "shape") else w2
-    act = {"silu": silu_mul, "gelu": gelu_mul}
+    act = {"silu": silu_mul, "gelu": gelu_mul,
+           "swiglu_oai": lambda y: swiglu_oai(y, swiglu_alpha, swiglu_limit)}
     if activation not in act:
         raise ValueError(f"Unsupported FusedMoe activation: {activation}")
 
@@ -136,13 +155,25 @@ def fused_experts(
         tok = slots // k
         gam = gate_scal[lo:hi, None]
         y1 = xf[tok] @ get1(e).t()
-        if apply_router_weight_on_input:
-            y1 = y1 * gam
-        y1 = _round(y1, out_dtype, mimic_rounding)
-        a = act[activation](y1).to(out_dtype).float()          # point 2 is inherent
+        if b1 is not None:
+            y1 = y1 + b1[e].float()
+        if activation == "swiglu_oai":
+            # bias variant (fused_moe.py:285-298): activation fused into GEMM-1, routing weight after it,
+            # a single rounding of the activated rows
+            a = act[activation](y1)
+            if apply_router_weight_on_input:
+                a = a * gam
+            a = a.to(out_dtype).float()
+        else:
+            if apply_router_weight_on_input:
+                y1 = y1 * gam
+            y1 = _round(y1, out_dtype, mimic_rounding)
+            a = act[activation](y1).to(out_dtype).float()      # point 2 is inherent
         if act_quant is not None:
             a = act_quant(a)
         y2 = a @ get2(e).t()
+        if b2 is not None:
+            y2 = y2 + b2[e].float()
         if not apply_router_weight_on_input:
             y2 = y2 * gam
         y2 = _round(y2, out_dtype, round_y2)
@@ -151,7 +182,13 @@ def fused_experts(
         else:
             out.index_add_(0, tok, y2)
     if no_combine:
-        return pairs.to(out_dtype).view(m, k, h)
+        # The routing tables number a token's pairs in ascending expert order (the converter sorts
+        # each row first); hand them back in the order of the caller's topk_ids columns.
+        order = torch.from_numpy(np.argsort(ids.numpy(), axis=1, kind="stable"))
+        by_sorted = pairs.to(out_dtype).view(m, k, h)
+        res = torch.empty_like(by_sorted)
+        res.scatter_(1, order[:, :, None].expand(m, k, h), by_sorted)
+        return res
     return out.to(out_dtype)
 
 

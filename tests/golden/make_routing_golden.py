@@ -2,13 +2,13 @@
 routing conversion (src/flaggems_sglang/ops/fused_moe.py:103-130,
 `_standard_topk_to_triton_kernels`) on CPU.
 
-Runs only where the reference tree is mounted (pass its path, default
-/root/reference) and where the dependency it imports (`triton_kernels`) can be
+Runs only where the reference tree is available (pass its path as the first
+argument, or set REFERENCE_ROOT) and where the dependency it imports (`triton_kernels`) can be
 found inside the installed vllm wheel.  The inputs follow the recipe of the
 reference's test (tests/test_fused_moe.py:15-27, 50-58): seed M+K+N+E+topk,
 logits randn(M, E), softmax, top-k, renormalise.
 
-    python tests/golden/make_routing_golden.py [/path/to/reference]
+    python tests/golden/make_routing_golden.py /path/to/reference
 """
 import importlib
 import os
@@ -18,7 +18,7 @@ from pathlib import Path
 
 import numpy as np
 
-ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ["REFERENCE_ROOT"]
 os.environ["DNN_VENDOR"] = "nvidia"
 sys.path.insert(0, os.path.join(ref_root, "src"))
 import vllm.third_party.triton_kernels as tk  # noqa: E402

@@ -185,3 +185,129 @@ def test_linearity_at_full_size(cuda_device):
     F.check_status()
     _assert_close(b, a.float().cpu() * 0.5, rtol=2e-2, atol=2e-3, what="linearity")
     assert torch.isfinite(a.float()).all()
+
+
+def _bias_inputs(M, K, N, E, topk, seed):
+    from flaggems_sglang_b200.testing import route
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w1 = (torch.randn(E, K, 2 * N, generator=g) * 0.05).to(torch.bfloat16)     # interleaved gate / linear columns
+    w2 = (torch.randn(E, N, K, generator=g) * 0.05).to(torch.bfloat16)
+    b1 = (torch.randn(E, 2 * N, generator=g) * 0.5).to(torch.bfloat16)
+    b2 = (torch.randn(E, K, generator=g) * 0.5).to(torch.bfloat16)
+    tw, ids = route(torch.randn(M, E, generator=g), topk)
+    return x, w1, w2, b1, b2, tw, ids
+
+
+@pytest.mark.parametrize("shape", [(7, 128, 256, 8, 2), (33, 256, 512, 16, 4), (300, 512, 384, 8, 2)],
+                         ids=lambda s: "M%d_K%d_N%d_E%d_topk%d" % s)
+@pytest.mark.parametrize("alpha,limit", [(1.702, 7.0), (None, None)])
+def test_fused_moe_with_bias(cuda_device, shape, alpha, limit):
+    """Bias variant (reference signature, fused_moe.py:219-236): interleaved gate/linear columns,
+    per-expert biases, clamped swiglu.  Untested upstream; parity against the oracle only."""
+    import flaggems_sglang
+    M, K, N, E, topk = shape
+    x, w1, w2, b1, b2, tw, ids = _bias_inputs(*shape, seed=M + K)
+    d = cuda_device
+    rd, gi, si = flaggems_sglang.topk_to_routing(tw.to(d), ids.to(d), E)
+    out = flaggems_sglang.triton_kernel_fused_experts_with_bias(
+        x.to(d), w1.to(d), None, b1.to(d), w2.to(d), None, b2.to(d), rd, gi, si,
+        gemm1_alpha=alpha, gemm1_clamp_limit=limit)
+    flaggems_sglang.check_status()
+    w13 = torch.cat([w1[:, :, 0::2], w1[:, :, 1::2]], dim=2).transpose(1, 2)
+    b13 = torch.cat([b1[:, 0::2], b1[:, 1::2]], dim=1)
+    ref = OM.fused_experts(x, w13, w2.transpose(1, 2), tw, ids, activation="swiglu_oai", b1=b13, b2=b2,
+                           swiglu_alpha=1.0 if alpha is None else alpha, swiglu_limit=limit)
+    _assert_close(out, ref, what=f"with_bias {shape}")
+    with pytest.raises(ValueError):
+        flaggems_sglang.triton_kernel_fused_experts_with_bias(
+            x.to(d), w1.to(d), None, b1.to(d), w2.to(d), None, b2.to(d), rd, gi, si, activation="gelu")
+
+
+def _adapter_objects(x, w13, w2, tw, ids, device, E, b13=None, b2=None, **cfg):
+    from types import SimpleNamespace as NS
+    config = dict(num_experts=E, activation="silu", no_combine=False, apply_router_weight_on_input=False,
+                  routed_scaling_factor=None, gemm1_alpha=None, gemm1_clamp_limit=None)
+    config.update(cfg)
+    layer = NS(w13_weight=w13.to(device).contiguous(), w2_weight=w2.to(device).contiguous())
+    if b13 is not None:
+        layer.w13_weight_bias, layer.w2_weight_bias = b13.to(device), b2.to(device)
+    obj = NS(runner=NS(config=NS(**config)))
+    disp = NS(hidden_states=x.to(device), topk_output=NS(topk_weights=tw.to(device), topk_ids=ids.to(device)))
+    return obj, layer, disp
+
+
+def test_adapter_layer_weights_scaling_and_no_combine(cuda_device):
+    """The serving adapter (reference: fused_moe.py:312-406) on duck-typed layer objects:
+    layer-layout weights used in place, routed scaling folded in, per-pair output."""
+    import flaggems_sglang
+    M, K, N, E, topk = 45, 256, 384, 16, 4
+    x, w1, w2, tw, ids = _ref_inputs(M, K, N, E, topk, cuda_device)
+    w13, w2l = w1.transpose(1, 2).contiguous(), w2.transpose(1, 2).contiguous()
+    obj, layer, disp = _adapter_objects(x, w13, w2l, tw, ids, cuda_device, E, routed_scaling_factor=2.5)
+    out = flaggems_sglang.fused_moe_flagos(obj, layer, disp).hidden_states
+    flaggems_sglang.check_status()
+    ref = OM.fused_experts(x, w13, w2l, tw, ids)
+    _assert_close(out, (ref.float() * 2.5).to(torch.bfloat16), what="adapter scaled")
+
+    obj, layer, disp = _adapter_objects(x, w13, w2l, tw, ids, cuda_device, E, no_combine=True,
+                                        routed_scaling_factor=2.5)
+    pairs = flaggems_sglang.fused_moe_flagos(obj, layer, disp).hidden_states
+    flaggems_sglang.check_status()
+    assert pairs.shape == (M, topk, K)
+    refp = OM.fused_experts(x, w13, w2l, tw, ids, no_combine=True)
+    _assert_close(pairs, refp, what="adapter no_combine")
+    # the pairs of a token sum to its combined row
+    _assert_close(pairs.float().sum(1).to(torch.bfloat16), ref, rtol=2e-2, atol=2e-2, what="pairs sum")
+
+
+def test_adapter_biased_layer(cuda_device):
+    import flaggems_sglang
+    shape = (21, 256, 256, 8, 2)
+    x, w1, w2, b1, b2, tw, ids = _bias_inputs(*shape, seed=5)
+    E = shape[3]
+    w13_inter, w2l = w1.transpose(1, 2).contiguous(), w2.transpose(1, 2).contiguous()     # rows interleaved
+    obj, layer, disp = _adapter_objects(x, w13_inter, w2l, tw, ids, cuda_device, E, b13=b1, b2=b2,
+                                        gemm1_alpha=1.702, gemm1_clamp_limit=7.0)
+    out = flaggems_sglang.fused_moe_flagos(obj, layer, disp).hidden_states
+    flaggems_sglang.check_status()
+    w13 = torch.cat([w13_inter[:, 0::2], w13_inter[:, 1::2]], dim=1)
+    b13 = torch.cat([b1[:, 0::2], b1[:, 1::2]], dim=1)
+    ref = OM.fused_experts(x, w13, w2l, tw, ids, activation="swiglu_oai", b1=b13, b2=b2, swiglu_alpha=1.702,
+                           swiglu_limit=7.0)
+    _assert_close(out, ref, what="adapter bias")
+    obj.runner.config.activation = "gelu"
+    with pytest.raises(ValueError):
+        flaggems_sglang.fused_moe_flagos(obj, layer, disp)
+
+
+@pytest.mark.parametrize("mode", ["fp8", "int4"])
+def test_no_combine_quantised(cuda_device, mode):
+    from flaggems_sglang_b200 import quant as Q
+    from flaggems_sglang_b200.ops.fused_moe import fused_experts
+    from flaggems_sglang_b200.testing import route
+    M, H, I, E, topk = 19, 256, 256, 8, 2
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(M, H, generator=g).to(torch.bfloat16)
+    w13 = torch.randn(E, 2 * I, H, generator=g) * 0.05
+    w2 = torch.randn(E, H, I, generator=g) * 0.05
+    tw, ids = route(torch.randn(M, E, generator=g), topk)
+    d = cuda_device
+    if mode == "fp8":
+        q13, s13 = Q.quantize_fp8_block(w13)
+        q2, s2 = Q.quantize_fp8_block(w2)
+        pairs = fused_experts(x.to(d), q13.to(d), q2.to(d), tw.to(d), ids.to(d), use_fp8_w8a8=True,
+                              w13_scale=s13.to(d), w2_scale=s2.to(d), no_combine=True)
+        whole = fused_experts(x.to(d), q13.to(d), q2.to(d), tw.to(d), ids.to(d), use_fp8_w8a8=True,
+                              w13_scale=s13.to(d), w2_scale=s2.to(d))
+    else:
+        a13 = Q.quantize_awq(w13.transpose(1, 2).contiguous())
+        a2 = Q.quantize_awq(w2.transpose(1, 2).contiguous())
+        k13, z13 = Q.repack_awq_for_kernel(*[t.to(d) for t in a13])
+        k2, z2 = Q.repack_awq_for_kernel(*[t.to(d) for t in a2])
+        x = x.to(torch.float16)
+        pairs = fused_experts(x.to(d), k13, k2, tw.to(d), ids.to(d), use_int4_w4a16=True, w13_sz=z13, w2_sz=z2,
+                              no_combine=True)
+        whole = fused_experts(x.to(d), k13, k2, tw.to(d), ids.to(d), use_int4_w4a16=True, w13_sz=z13, w2_sz=z2)
+    assert pairs.shape == (M, topk, H)
+    _assert_close(pairs.float().sum(1).to(whole.dtype), whole, rtol=2e-2, atol=2e-2, what=f"no_combine {mode}")
