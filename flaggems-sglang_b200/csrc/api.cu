@@ -5,6 +5,7 @@
 #include "align.cuh"
 #include "gemm.cuh"
 #include "prep.cuh"
+#include "router.cuh"
 
 using namespace b200moe;
 
@@ -95,7 +96,7 @@ struct Layout {
   int orient;     // GEMM tile orientation that goes with BT
   int act_bytes;  // bytes per activation element fed to the GEMMs
   size_t meta, blk_off, sorted_ids, expert_ids, num_post, row_gamma, xs, xs_scale, a2, a2_scale, out32,
-      total;
+      route_w, route_ids, total;
 };
 
 int pick_bt(const b200moe_cfg* c) {
@@ -179,6 +180,8 @@ int make_layout(const b200moe_cfg* c, Layout* L) {
   L->a2_scale = take(fp8 ? static_cast<size_t>(cap) * (c->I / 128) * 4 : 0);
   L->out_rows = (c->flags & B200MOE_FLAG_NO_COMBINE) ? L->P : c->M;   // one fp32 row per pair when nothing is summed
   L->out32 = take(static_cast<size_t>(L->out_rows > 0 ? L->out_rows : 1) * c->H * 4);
+  L->route_w = take(static_cast<size_t>(L->P > 0 ? L->P : 1) * 4);    // router output when the call starts from logits
+  L->route_ids = take(static_cast<size_t>(L->P > 0 ? L->P : 1) * 4);
   L->total = off;
   return B200MOE_OK;
 }
@@ -216,7 +219,7 @@ bool reference_rounds_pairs(int P, int E, int n, int k, int sms) {
 }
 
 int query_sms(const b200moe_cfg* c) {
-  if (c->num_sms > 0) return c->num_sms;
+  if (c != nullptr && c->num_sms > 0) return c->num_sms;
   static int cached[64] = {0};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
@@ -470,6 +473,41 @@ int b200moe_forward_topk(const b200moe_cfg* cfg, const void* x, const void* w1, 
   prof_mark(slot, 0, st);
   rc = launch_align_block(topk_ids, (cfg->flags & B200MOE_FLAG_IDS_I64) ? 1 : 0, expert_map, topk_weights, L.P,
                           cfg->E, L.BT, L.cap, reinterpret_cast<int*>(ws + L.sorted_ids),
+                          reinterpret_cast<int*>(ws + L.expert_ids), reinterpret_cast<int*>(ws + L.num_post),
+                          reinterpret_cast<float*>(ws + L.row_gamma), reinterpret_cast<int*>(ws + L.blk_off),
+                          reinterpret_cast<int*>(ws + L.meta), st);
+  if (rc != B200MOE_OK) return rc;
+  return run_experts(cfg, L, x, w1, w2, quant, ws, out, status, st, slot);
+}
+
+int b200moe_route_topk(const b200moe_router* router, const void* logits, int n_tokens, int n_experts, int topk,
+                       float* topk_weights, int32_t* topk_ids, void* stream) {
+  if (n_tokens < 0) return B200MOE_ERR_BAD_ARG;
+  return launch_route_topk(router, logits, n_tokens, n_experts, topk, topk_weights, topk_ids, query_sms(nullptr),
+                           static_cast<cudaStream_t>(stream));
+}
+
+int b200moe_forward_logits(const b200moe_cfg* cfg, const b200moe_router* router, const void* x, const void* w1,
+                           const void* w2, const b200moe_quant* quant, const void* logits,
+                           const int32_t* expert_map, void* workspace, size_t workspace_bytes, void* out,
+                           int32_t* status, void* stream) {
+  Layout L;
+  int rc = forward_common(cfg, x, w1, w2, workspace, workspace_bytes, out, status, &L);
+  if (rc != B200MOE_OK) return rc;
+  rc = check_router(router, cfg->E, cfg->topk);
+  if (rc != B200MOE_OK) return rc;
+  if (cfg->flags & B200MOE_FLAG_IDS_I64) return B200MOE_ERR_BAD_ARG;   // the router writes int32 ids
+  if (cfg->M == 0) return B200MOE_OK;
+  if (!logits) return B200MOE_ERR_BAD_ARG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+  float* tw = reinterpret_cast<float*>(ws + L.route_w);
+  int* ids = reinterpret_cast<int*>(ws + L.route_ids);
+  const int slot = prof_slot();
+  prof_mark(slot, 0, st);
+  rc = launch_route_topk(router, logits, cfg->M, cfg->E, cfg->topk, tw, ids, query_sms(cfg), st);
+  if (rc != B200MOE_OK) return rc;
+  rc = launch_align_block(ids, 0, expert_map, tw, L.P, cfg->E, L.BT, L.cap, reinterpret_cast<int*>(ws + L.sorted_ids),
                           reinterpret_cast<int*>(ws + L.expert_ids), reinterpret_cast<int*>(ws + L.num_post),
                           reinterpret_cast<float*>(ws + L.row_gamma), reinterpret_cast<int*>(ws + L.blk_off),
                           reinterpret_cast<int*>(ws + L.meta), st);

@@ -3,8 +3,11 @@ fused-MoE entry points (src/flaggems_sglang/__init__.py:7-10 in the reference)."
 from .ops import (
     check_status,
     fused_experts,
+    fused_moe,
     fused_moe_flagos,
+    grouped_topk,
     moe_align_block_size,
+    topk_softmax,
     topk_to_routing,
     triton_kernel_fused_experts,
     triton_kernel_fused_experts_with_bias,
@@ -18,7 +21,10 @@ vendor_name = "nvidia"
 __all__ = [
     "check_status",
     "fused_experts",
+    "fused_moe",
     "fused_moe_flagos",
+    "grouped_topk",
+    "topk_softmax",
     "moe_align_block_size",
     "topk_to_routing",
     "triton_kernel_fused_experts",

@@ -12,7 +12,9 @@ VERSION = 1
 OK = 0
 ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_TOO_LARGE = -1, -2, -3, -4, -5, -6
 
-DTYPE_BF16, DTYPE_FP16 = 0, 1
+DTYPE_BF16, DTYPE_FP16, DTYPE_FP32 = 0, 1, 2
+SCORE_SOFTMAX, SCORE_SIGMOID = 0, 1
+ROUTER_MAX_EXPERTS, ROUTER_MAX_TOPK = 1024, 32
 W_16BIT, W_FP8_BLOCK, W_INT4_AWQ = 0, 1, 2
 LAYOUT_LAYER, LAYOUT_OP = 0, 1
 ACT_SILU, ACT_GELU, ACT_SWIGLU_OAI = 0, 1, 2
@@ -33,6 +35,12 @@ class Cfg(C.Structure):
 class Quant(C.Structure):
     _fields_ = [("w1_scale", C.c_void_p), ("w2_scale", C.c_void_p), ("w1_sz", C.c_void_p), ("w2_sz", C.c_void_p),
                 ("b1", C.c_void_p), ("b2", C.c_void_p), ("swiglu_alpha", C.c_float), ("swiglu_limit", C.c_float)]
+
+
+class Router(C.Structure):
+    _fields_ = [("struct_bytes", C.c_int32), ("scoring", C.c_int32), ("renormalize", C.c_int32),
+                ("n_group", C.c_int32), ("topk_group", C.c_int32), ("logits_dtype", C.c_int32),
+                ("scale", C.c_float), ("reserved", C.c_int32), ("bias", C.c_void_p)]
 
 
 # name -> (restype, argtypes); every symbol include/b200moe.h declares
@@ -56,6 +64,11 @@ SYMBOLS = {
                                                C.c_void_p, C.c_void_p, C.c_void_p]),
     "b200moe_forward_routed": (C.c_int, [C.POINTER(Cfg), C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(Quant),
                                          C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
+                                         C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b200moe_route_topk": (C.c_int, [C.POINTER(Router), C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p,
+                                     C.c_void_p, C.c_void_p]),
+    "b200moe_forward_logits": (C.c_int, [C.POINTER(Cfg), C.POINTER(Router), C.c_void_p, C.c_void_p, C.c_void_p,
+                                         C.POINTER(Quant), C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
                                          C.c_void_p, C.c_void_p, C.c_void_p]),
     "b200moe_profile_begin": (C.c_int, [C.c_int]),
     "b200moe_profile_end": (C.c_int, [C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double),

@@ -137,8 +137,12 @@ def fused_experts(
     swiglu_alpha: float = 1.0,
     swiglu_limit: Optional[float] = None,
     no_combine: bool = False,
+    router=None,
 ) -> torch.Tensor:
     """Fused experts on layer-layout weights ``w13 [E, 2I, H]``, ``w2 [E, H, I]``.
+
+    ``router``: ``(make_router(...) result, topk)``; the call then starts from the gating
+    logits and runs the router kernel in front (see ``fused_moe``).
 
     ``no_combine``: return ``[M, topk, H]``, one weighted expert output per (token, choice)
     pair instead of their sum; ``routed_scaling_factor`` is not applied (the reference's
@@ -214,7 +218,11 @@ def fused_experts(
             "biases and the clamped swiglu are available with 16-bit weights only"
 
     lib = _lib.lib()
-    if routing is None:
+    if router is not None:
+        assert routing is None and topk_weights is None and topk_ids is None, "router excludes other routing inputs"
+        (rt, logits, _bias_keepalive), k = router
+        assert logits.shape == (m, e), "gating_output must be [tokens, experts]"
+    elif routing is None:
         assert topk_weights is not None and topk_ids is not None, "routing or (topk_weights, topk_ids) required"
         k = topk_ids.shape[1]
         ids = topk_ids.contiguous()
@@ -246,7 +254,15 @@ def fused_experts(
     stream = torch.cuda.current_stream(dev).cuda_stream
     qref = C.byref(quant) if quant is not None else None
     with torch.cuda.device(dev):
-        if routing is None:
+        if router is not None:
+            emap = None
+            if expert_map is not None:
+                emap = expert_map.to(device=dev, dtype=torch.int32).contiguous()
+            rc = lib.b200moe_forward_logits(
+                C.byref(cfg), C.byref(rt), x.data_ptr(), w13.data_ptr(), w2.data_ptr(), qref, logits.data_ptr(),
+                emap.data_ptr() if emap is not None else None, base, avail, out.data_ptr(),
+                status.data_ptr(), stream)
+        elif routing is None:
             emap = None
             if expert_map is not None:
                 emap = expert_map.to(device=dev, dtype=torch.int32).contiguous()
@@ -263,6 +279,30 @@ def fused_experts(
     if os.environ.get("B200MOE_CHECK_STATUS", "0") == "1":
         check_status(dev)
     return out
+
+
+def fused_moe(
+    hidden_states: torch.Tensor,
+    w13: torch.Tensor,
+    w2: torch.Tensor,
+    gating_output: torch.Tensor,
+    topk: int,
+    renormalize: bool = True,
+    *,
+    num_expert_group: int = 0,
+    topk_group: int = 0,
+    scoring_func: str = "softmax",
+    correction_bias: Optional[torch.Tensor] = None,
+    **kwargs,
+) -> torch.Tensor:
+    """Whole MoE layer from the gating logits ``[M, E]``: router (softmax or sigmoid scores,
+    optional expert groups and selection bias, see ``ops.router``), alignment, both grouped
+    GEMMs and the combine in one C call with no host read in between.  Remaining keyword
+    arguments are those of ``fused_experts``."""
+    from .router import make_router
+    rt = make_router(gating_output, topk, renormalize, num_expert_group=num_expert_group, topk_group=topk_group,
+                     scoring_func=scoring_func, correction_bias=correction_bias)
+    return fused_experts(hidden_states, w13, w2, router=(rt, topk), **kwargs)
 
 
 # ---------------------------------------------------------------------------- reference-compatible entry points

@@ -35,6 +35,7 @@ extern "C" {
 /* activation / output element type */
 #define B200MOE_DTYPE_BF16 0
 #define B200MOE_DTYPE_FP16 1
+#define B200MOE_DTYPE_FP32 2 /* router logits only */
 
 /* weight storage */
 #define B200MOE_W_16BIT 0     /* same 16-bit type as the activations               */
@@ -200,6 +201,48 @@ int b200moe_forward_routed(const b200moe_cfg *cfg, const void *x, const void *w1
                            const float *gate_scal, void *workspace,
                            size_t workspace_bytes, void *out, int32_t *status,
                            void *stream);
+
+/*
+ * Router front-end: gating logits -> top-k routing weights and expert ids, the
+ * step in front of the alignment.  The reference leaves it to the caller
+ * (recipe at tests/test_fused_moe.py:21-27: softmax, top-k, divide by the sum);
+ * grouped selection with an optional selection bias is the DeepSeek-V2 / -V3
+ * rule (named `grouped_topk` in
+ * src/flaggems_sglang/runtime/backend/_iluvatar/op_black_list.yaml:6-11).
+ * Ties go to the lower expert id.
+ */
+#define B200MOE_SCORE_SOFTMAX 0
+#define B200MOE_SCORE_SIGMOID 1
+#define B200MOE_ROUTER_MAX_EXPERTS 1024
+#define B200MOE_ROUTER_MAX_TOPK 32
+
+typedef struct b200moe_router {
+  int32_t struct_bytes;  /* sizeof(b200moe_router), checked                                   */
+  int32_t scoring;       /* B200MOE_SCORE_*                                                   */
+  int32_t renormalize;   /* 1: divide the k weights by their sum                              */
+  int32_t n_group;       /* contiguous expert groups (<= 32, divides E); 0 or 1: no grouping  */
+  int32_t topk_group;    /* groups that stay eligible                                         */
+  int32_t logits_dtype;  /* B200MOE_DTYPE_BF16 / FP16 / FP32                                  */
+  float scale;           /* multiplies the final weights; 0 is read as 1                      */
+  int32_t reserved;
+  const float *bias;     /* [E] added to the scores for selection only, or NULL; with groups,
+                            a group's score becomes the sum of its two best biased scores    */
+} b200moe_router;
+
+/* logits [M, E]; topk_weights [M, topk] fp32 and topk_ids [M, topk] int32 on the device. */
+int b200moe_route_topk(const b200moe_router *router, const void *logits, int n_tokens,
+                       int n_experts, int topk, float *topk_weights, int32_t *topk_ids,
+                       void *stream);
+
+/*
+ * Whole layer from gating logits: router, alignment, both grouped GEMMs and the
+ * combine, one call, no host read in between.  Arguments as b200moe_forward_topk
+ * with `logits [M, E]` in place of the top-k tensors.
+ */
+int b200moe_forward_logits(const b200moe_cfg *cfg, const b200moe_router *router, const void *x,
+                           const void *w1, const void *w2, const b200moe_quant *quant,
+                           const void *logits, const int32_t *expert_map, void *workspace,
+                           size_t workspace_bytes, void *out, int32_t *status, void *stream);
 
 /*
  * Dynamic per-token-group FP8 quantisation (1 x 128 groups): the step in front
