@@ -92,11 +92,12 @@ void prof_mark(int slot, int mark, cudaStream_t st) {
 
 struct Layout {
   int BT, cap, P;
+  bool w4p;       // int4 decode path: integer MMAs on three-plane int8 activations
   int out_rows;   // rows of the fp32 output buffer: tokens, or pairs when nothing is combined
   int orient;     // GEMM tile orientation that goes with BT
   int act_bytes;  // bytes per activation element fed to the GEMMs
-  size_t meta, blk_off, sorted_ids, expert_ids, num_post, row_gamma, xs, xs_scale, a2, a2_scale, out32,
-      route_w, route_ids, total;
+  size_t meta, blk_off, sorted_ids, expert_ids, num_post, row_gamma, xs, xs_scale, xs_sum, a2, a2_scale,
+      a2_sum, out32, route_w, route_ids, total;
 };
 
 int pick_bt(const b200moe_cfg* c) {
@@ -161,7 +162,12 @@ int make_layout(const b200moe_cfg* c, Layout* L) {
   cap = static_cast<int>(align_up(static_cast<size_t>(cap > 0 ? cap : 1), L->BT));
   L->cap = cap;
   const bool fp8 = c->wmode == B200MOE_W_FP8_BLOCK;
-  L->act_bytes = fp8 ? 1 : 2;
+  // decode-sized int4: nibbles converted straight into tensor memory, integer MMAs, group scales
+  // applied to the partial sums
+  L->w4p = c->wmode == B200MOE_W_INT4_AWQ && L->BT <= 32 && !(c->flags & B200MOE_FLAG_W4_SMEM_OPERANDS) &&
+           gemm_w4_planes_ok(c->H, L->BT) && gemm_w4_planes_ok(c->I, L->BT);
+  L->act_bytes = fp8 ? 1 : (L->w4p ? 3 : 2);
+  const bool tables = fp8 || L->w4p;   // per (128-k group, row) tables beside the activations
   size_t off = 0;
   auto take = [&](size_t bytes) {
     size_t o = off;
@@ -175,9 +181,11 @@ int make_layout(const b200moe_cfg* c, Layout* L) {
   L->num_post = take(16);
   L->row_gamma = take(static_cast<size_t>(cap) * 4);
   L->xs = take(static_cast<size_t>(cap) * c->H * L->act_bytes);
-  L->xs_scale = take(fp8 ? static_cast<size_t>(cap) * (c->H / 128) * 4 : 0);
+  L->xs_scale = take(tables ? static_cast<size_t>(cap) * (c->H / 128) * 4 : 0);
+  L->xs_sum = take(L->w4p ? static_cast<size_t>(cap) * (c->H / 128) * 4 : 0);
   L->a2 = take(static_cast<size_t>(cap) * c->I * L->act_bytes);
-  L->a2_scale = take(fp8 ? static_cast<size_t>(cap) * (c->I / 128) * 4 : 0);
+  L->a2_scale = take(tables ? static_cast<size_t>(cap) * (c->I / 128) * 4 : 0);
+  L->a2_sum = take(L->w4p ? static_cast<size_t>(cap) * (c->I / 128) * 4 : 0);
   L->out_rows = (c->flags & B200MOE_FLAG_NO_COMBINE) ? L->P : c->M;   // one fp32 row per pair when nothing is summed
   L->out32 = take(static_cast<size_t>(L->out_rows > 0 ? L->out_rows : 1) * c->H * 4);
   L->route_w = take(static_cast<size_t>(L->P > 0 ? L->P : 1) * 4);    // router output when the call starts from logits
@@ -254,6 +262,10 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
     rc = launch_group_quant_fp8(x, c->dtype, xs, reinterpret_cast<float*>(ws + L.xs_scale), sorted_ids, meta,
                                 L.P, c->topk, L.cap, c->H, 1, L.cap, out32, static_cast<size_t>(L.out_rows) * c->H * 4,
                                 sms, st, pdl);
+  } else if (L.w4p) {
+    rc = launch_group_split_i8(x, reinterpret_cast<uint8_t*>(xs), reinterpret_cast<float*>(ws + L.xs_scale),
+                               reinterpret_cast<int*>(ws + L.xs_sum), sorted_ids, meta, L.P, c->topk, L.cap, c->H,
+                               L.BT, L.cap, out32, static_cast<size_t>(L.out_rows) * c->H * 4, sms, st, pdl);
   } else {
     rc = launch_gather_rows(x, xs, sorted_ids, meta, L.P, c->topk, c->H * 2, L.cap, out32,
                             static_cast<size_t>(L.out_rows) * c->H * 4, sms, st, pdl);
@@ -300,8 +312,15 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
     g1.w_sz = quant->w1_sz;
     g1.w_rows = 2 * c->I;
   }
-  // decode-sized int4: operands dequantised into tensor memory, group scales applied to partial sums
-  const bool w4p = w4 && L.BT <= 32 && !(c->flags & B200MOE_FLAG_W4_SMEM_OPERANDS);
+  const bool w4p = L.w4p;
+  if (w4p) {
+    g1.x_scale = reinterpret_cast<float*>(ws + L.xs_scale);
+    g1.x_sum = reinterpret_cast<int*>(ws + L.xs_sum);
+    g1.ld_xscale = L.cap;
+    g1.out_q = reinterpret_cast<uint8_t*>(a2);
+    g1.out_scale = reinterpret_cast<float*>(ws + L.a2_scale);
+    g1.out_sum = reinterpret_cast<int*>(ws + L.a2_sum);
+  }
   if (fp8) gemm_plan_fp8(&g1); else if (w4p) gemm_plan_w4(&g1); else gemm_plan(&g1);
 
   GemmArgs g2 = g1;
@@ -330,6 +349,13 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
     g2.out_scale = nullptr;
     g2.flags &= ~B200MOE_FLAG_MIMIC_ROUNDING;
   }
+  if (w4p) {
+    g2.x_scale = reinterpret_cast<float*>(ws + L.a2_scale);
+    g2.x_sum = reinterpret_cast<int*>(ws + L.a2_sum);
+    g2.out_q = nullptr;
+    g2.out_scale = nullptr;
+    g2.out_sum = nullptr;
+  }
   if (fp8) gemm_plan_fp8(&g2); else if (w4p) gemm_plan_w4(&g2); else gemm_plan(&g2);
 
   if (c->flags & B200MOE_FLAG_SIMT) {
@@ -338,25 +364,32 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
     rc = launch_gemm_simt(w2, a2, g2, st, L.cap);
     if (rc != B200MOE_OK) return rc;
   } else {
-    const int eb = L.act_bytes;
+    const int eb = w4p ? 1 : L.act_bytes;
     const CUtensorMapDataType dt = tmap_dtype(c->dtype, eb);
     const uint32_t kbox = 128 / eb;
     CUtensorMap tm_w1, tm_x, tm_w2, tm_a2;
     if (w4) {
-      // packed int4 rows: K/2 bytes per row, 32 bytes (64 k) per stage, plain row-major staging
-      if ((rc = make_tmap_3d(&tm_w1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w1, c->H / 2, 2ull * c->I, c->E, 32, 128,
-                             CU_TENSOR_MAP_SWIZZLE_NONE)) != B200MOE_OK)
+      // packed int4 rows, K/2 bytes per row.  Shared-memory-operand kernels: 32 bytes (64 k) per
+      // stage, plain row-major staging; integer decode kernels: 64 bytes (one group) per stage with
+      // the 64-byte swizzle, so that threads reading whole rows do not collide on banks
+      const uint32_t pbox = w4p ? 64 : 32;
+      const CUtensorMapSwizzle psw = w4p ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE;
+      if ((rc = make_tmap_3d(&tm_w1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w1, c->H / 2, 2ull * c->I, c->E, pbox, 128,
+                             psw)) != B200MOE_OK)
         return rc;
-      if ((rc = make_tmap_3d(&tm_w2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w2, c->I / 2, c->H, c->E, 32, 128,
-                             CU_TENSOR_MAP_SWIZZLE_NONE)) != B200MOE_OK)
+      if ((rc = make_tmap_3d(&tm_w2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w2, c->I / 2, c->H, c->E, pbox, 128,
+                             psw)) != B200MOE_OK)
         return rc;
     } else {
       if ((rc = make_tmap_3d(&tm_w1, dt, eb, w1, c->H, 2ull * c->I, c->E, kbox, 128)) != B200MOE_OK) return rc;
       if ((rc = make_tmap_3d(&tm_w2, dt, eb, w2, c->I, c->H, c->E, kbox, (L.orient == 1 && !fp8) ? 256 : 128)) != B200MOE_OK)
         return rc;
     }
-    if ((rc = make_tmap_2d(&tm_x, dt, eb, xs, c->H, L.cap, kbox, L.BT)) != B200MOE_OK) return rc;
-    if ((rc = make_tmap_2d(&tm_a2, dt, eb, a2, c->I, L.cap, kbox, L.BT)) != B200MOE_OK) return rc;
+    // int4 decode: a token block is 3 * BT consecutive rows (its three byte planes)
+    const uint64_t xrows = w4p ? 3ull * L.cap : static_cast<uint64_t>(L.cap);
+    const uint32_t xbox = w4p ? 3u * L.BT : static_cast<uint32_t>(L.BT);
+    if ((rc = make_tmap_2d(&tm_x, dt, eb, xs, c->H, xrows, kbox, xbox)) != B200MOE_OK) return rc;
+    if ((rc = make_tmap_2d(&tm_a2, dt, eb, a2, c->I, xrows, kbox, xbox)) != B200MOE_OK) return rc;
     prof_mark(slot, 1, st);
     rc = fp8 ? launch_gemm_fp8(tm_w1, tm_x, g1, sms, st)
              : (w4p ? launch_gemm_w4(tm_w1, tm_x, g1, sms, st) : launch_gemm_tc(tm_w1, tm_x, g1, sms, st));

@@ -185,6 +185,17 @@ __device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, 
       "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Integer form: A (tensor memory, four consecutive k per 32-bit column, lowest byte first) and
+// B (shared memory) hold 8-bit integers, the accumulator is int32.
+__device__ __forceinline__ void tc_mma_i8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Each thread of the warp writes 32 consecutive 32-bit columns of its own TMEM lane and waits
 // until the store has landed.
 __device__ __forceinline__ void tmem_st32_wait(uint32_t taddr, const uint32_t (&r)[32]) {
@@ -230,6 +241,28 @@ __device__ __forceinline__ void tmem_ld16_wait(uint32_t taddr, float (&v)[16]) {
 }
 
 // Two loads (e.g. gate and up accumulators) in flight before the single wait.
+// Three 16-column reads of raw 32-bit accumulators (integer MMAs), one wait.
+__device__ __forceinline__ void tmem_ld16x3_wait_b32(uint32_t taddr0, uint32_t taddr1, uint32_t taddr2,
+                                                     int (&v0)[16], int (&v1)[16], int (&v2)[16]) {
+  uint32_t r[48];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, "
+      "%13, %14, %15}, [%48];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, "
+      "%27, %28, %29, %30, %31}, [%49];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, "
+      "%43, %44, %45, %46, %47}, [%50];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : B200MOE_R16(r, 0), B200MOE_R16(r, 16), B200MOE_R16(r, 32)
+      : "r"(taddr0), "r"(taddr1), "r"(taddr2)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    v0[i] = static_cast<int>(r[i]);
+    v1[i] = static_cast<int>(r[16 + i]);
+    v2[i] = static_cast<int>(r[32 + i]);
+  }
+}
 __device__ __forceinline__ void tmem_ld16x2_wait(uint32_t taddr0, uint32_t taddr1, float (&v0)[16],
                                                  float (&v1)[16]) {
   uint32_t r[32];
@@ -304,6 +337,18 @@ __host__ __device__ __forceinline__ uint32_t make_idesc(uint32_t fmt, uint32_t m
   d |= 1u << 4;           // accumulator format fp32
   d |= (fmt & 7u) << 7;   // A format
   d |= (fmt & 7u) << 10;  // B format
+  d |= (n >> 3) << 17;
+  d |= (m >> 4) << 24;
+  return d;
+}
+
+// Integer instruction descriptor (kind::i8): int32 accumulate, A unsigned or signed 8-bit, B
+// unsigned or signed 8-bit, both with the reduction dim contiguous.
+__host__ __device__ __forceinline__ uint32_t make_idesc_i8(bool a_signed, bool b_signed, uint32_t m, uint32_t n) {
+  uint32_t d = 0;
+  d |= 2u << 4;                       // accumulator format s32
+  d |= (a_signed ? 1u : 0u) << 7;     // A format: 0 = u8, 1 = s8
+  d |= (b_signed ? 1u : 0u) << 10;    // B format
   d |= (n >> 3) << 17;
   d |= (m >> 4) << 24;
   return d;

@@ -47,9 +47,15 @@ struct GemmArgs {
   int w_rows;             // int4: weight rows per expert (2I for mode 0, H for mode 1)
   uint8_t* out_q;         // mode 0 FP8: quantised activations [cap, N]
   float* out_scale;       // mode 0 FP8: [N/128][ld_xscale]
+  // int4 decode path (integer MMAs): activations are three int8 planes per token block
+  // ([block][plane][BT rows][K], rows of one block consecutive) + per (128-k group, row) a
+  // power-of-two scale (x_scale / out_scale, [K/128][ld_xscale]) and the sum of the integers
+  const int* x_sum;       // [K/128][ld_xscale]
+  int* out_sum;           // mode 0: [N/128][ld_xscale]; planes go to out_q with row stride ld_out
 };
 
 size_t gemm_smem_bytes(const GemmArgs& a);
+bool gemm_w4_planes_ok(int K, int BT);   // can the integer int4 path take this reduction length / token block?
 void gemm_plan(GemmArgs* a);  // fills stages / acc_stages / tmem_cols / num_nt / kblocks from the rest
 
 int launch_gemm_tc(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmArgs& a, int num_sms,

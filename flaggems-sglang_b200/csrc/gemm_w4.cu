@@ -1,29 +1,41 @@
 // Grouped expert GEMMs for int4 (AWQ, group 128, zero points) weights and fp16 activations,
-// decode-sized token blocks (16 / 32).
+// decode-sized token blocks (16 / 32), on the integer tensor-core path.
 //
-// Weight-only int4 at decode is a dequantisation problem: the packed weights arrive from HBM
-// four times faster than fp16 ones, so the CUDA-core work per weight has to shrink with them.
-// Here the dequant warps only turn each nibble into the exact small integer (q - zero) as
-// fp16 (two instructions per pair) and write it into the swizzled operand tile; the MMA
-// (tcgen05.mma.kind::f16, fp32 accumulate) then sums exact products over one quantisation
-// group of 128 k (two pipeline stages) into a partial accumulator in tensor memory, and the
-// promotion warps multiply that partial by the group's scale -- one scalar per thread, since
-// a thread owns one weight row -- while adding it to accumulators in registers.  The result is
-// also closer to the real-valued product than rounding (q - z) * s to fp16 per weight.
+// Weight-only int4 at decode is bound by how many weights one tcgen05.mma consumes: the
+// instruction walks its 128 operand rows at one row per clock whatever the width of the other
+// operand, so with fp16 operands (16 k per instruction) a CTA takes in 16 weights per clock,
+// a quarter of what the packed weights need to keep HBM busy.  8-bit operands double the k per
+// instruction, and integer ones make the conversion almost free:
 //
-// Tiles are two 128-row weight blocks sharing the token block (gate | up rows for the first
-// GEMM, rows n0.. | n0+128.. for the second), as in the FP8 kernels.
+//   weights      the raw nibbles q (0..15) as unsigned bytes: two logic instructions per eight
+//                weights, written straight into tensor memory (tcgen05.st), never into shared
+//                memory.  The zero point is not subtracted here.
+//   activations  per (token, 128-k group) a power-of-two scale f and the exact integers
+//                v = rint(x / f), |v| < 2^19, split into three signed bytes
+//                v = p0 + 256 p1 + 65536 p2.  The three byte planes of a token block are three
+//                sets of columns of ONE MMA (N = 3 * BT), which costs no extra tensor time.
+//   MMA          kind::i8, int32 accumulate, A from tensor memory: per group the exact sums
+//                S_p = sum_k q_k p_{p,k}.
+//   promotion    exact integer S = S_0 + 256 S_1 + 65536 S_2 - z * X with X = sum_k v_k (from
+//                the activation tables), then acc += (s * f) * float(S): the group scale s and
+//                zero z are one scalar per thread (a thread owns one weight row).
 //
-// The dequantised operand never touches shared memory: staging fp16 tiles there costs four
-// times the bytes that arrive from HBM in shared-memory writes plus the same again in MMA
-// operand reads, and that bandwidth (128 B/clk) caps the kernel well below the HBM rate.
-// Instead each dequant thread owns one weight row = one TMEM lane and writes its 64 k-values
-// of a stage into tensor memory with tcgen05.st; the MMA takes its A operand from there
-// (tcgen05.mma with A in TMEM) and only the small token block as a shared-memory descriptor.
-// Shared memory then holds just a deep ring of small TMA stages (8 KiB packed + token block).
+// Up to the rounding of x / f to 20 bits this is the real-valued product of the dequantised
+// weights with the fp16 activations, accumulated in fp32 once per group: closer to it than
+// rounding (q - z) * s to fp16 per weight.
+//
+// A tile is two 128-row weight blocks sharing the token block (gate | up rows for the first
+// GEMM, rows n0.. | n0+128.. for the second).  The first GEMM's tail applies the activation,
+// rounds to fp16 and re-expresses the block in the same three-plane form for the second GEMM
+// (its 128 output columns are exactly one group of the second GEMM's reduction).
+//
+// Byte order inside each aligned run of eight k: the packed word keeps element 2i in nibble i
+// and element 2i+1 in nibble 4+i, so `w & 0x0F0F0F0F` and `(w >> 4) & 0x0F0F0F0F` are the
+// elements (0, 4, 1, 5) and (2, 6, 3, 7).  The activation planes are stored in that same
+// order; a dot product does not care as long as both sides agree.
 //
 // Warps: 0 TMA producer, 1 MMA issuer, 2-5 promotion + tail, 6 per-tile table loader,
-// 7-14 dequantisation.
+// 7-10 nibble -> byte conversion.
 #include "gemm_sched.cuh"
 
 namespace b200moe {
@@ -37,23 +49,13 @@ __device__ unsigned long long g_stall_w4[16];
 #define STALL_ADD(slot, v) ((void)0)
 #endif
 
-constexpr int kDqWarps = 8;
-constexpr int kOperandStages = 4;   // A-operand stages in tensor memory, 64 columns each
-constexpr int kThreadsW4P = 7 * 32 + 32 * kDqWarps;  // 480
+constexpr int kDqWarps = 4;
+constexpr int kThreadsW4P = 7 * 32 + 32 * kDqWarps;  // 352
+constexpr int kPackedRowBytes = 64;                  // 128 k of one weight row
+constexpr int kMaxGroupsW4 = 128;                    // reduction groups whose tables fit in shared memory
 
-// 32 packed uint4 (16 bytes) -> 16 words of two fp16 values (q - zero) each, k ascending.
-__device__ __forceinline__ void dequant_w4x32_centered(const uint4 packed, const __half2 zero1024, uint32_t* out) {
-  const uint32_t w[4] = {packed.x, packed.y, packed.z, packed.w};
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      uint32_t t = ((w[j] >> (4 * i)) & 0x000F000Fu) | 0x64006400u;  // fp16 pair (1024 + q, 1024 + q')
-      __half2 h = __hsub2(*reinterpret_cast<__half2*>(&t), zero1024);
-      out[4 * j + i] = *reinterpret_cast<uint32_t*>(&h);
-    }
-  }
-}
+// position inside an aligned run of eight k at which element e is stored
+__device__ __forceinline__ int plane_pos(int e) { return ((e & 3) << 1) | ((e >> 2) & 1); }
 
 template <int MODE, int BT>
 __global__ void __launch_bounds__(kThreadsW4P, 1)
@@ -62,17 +64,21 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  constexpr int X_BYTES = BT * kStageKBytes;        // token block: BT rows x 64 k fp16
-  constexpr int PK_BYTES = 2 * kTileRows * 32;      // packed rows: 256 x 32 bytes
-  constexpr int STAGE_BYTES = X_BYTES + PK_BYTES;   // one stage of the TMA ring: [token block | packed rows]
-  constexpr int PCOLS = 2 * BT;
-  constexpr int NO = kOperandStages;
-  const int stages = a.stages;                      // depth of the TMA ring
+  constexpr int NB = 3 * BT;                                   // MMA N: three byte planes of the token block
+  constexpr int X_BYTES = NB * kStageKBytes;                   // [3 planes][BT rows][128 k] int8
+  constexpr int PK_BYTES = 2 * kTileRows * kPackedRowBytes;    // packed rows: 256 x 64 bytes
+  constexpr int STAGE_BYTES = X_BYTES + PK_BYTES;              // one stage = one quantisation group
+  constexpr int PCOLS = 2 * NB;                                // int32 partial sums of both weight blocks
+  constexpr int NO = (BT == 16) ? 4 : 2;                       // A-operand stages in tensor memory
+  constexpr uint32_t A_COL0 = 2 * PCOLS;                       // TMEM: two partial buffers, then the A stages
+  const int stages = a.stages;
+  const int nkb_max = a.kblocks;
 
-  uint8_t* pk_base = smem;                                           // TMA ring
-  constexpr uint32_t A_COL0 = 4 * BT;                                // TMEM: [0, 4*BT) partial sums, then A stages
-  uint8_t* ctrl_base = pk_base + static_cast<size_t>(stages) * STAGE_BYTES;
-  uint64_t* bar_full = reinterpret_cast<uint64_t*>(ctrl_base);
+  uint8_t* ring = smem;
+  uint8_t* ctrl_base = ring + static_cast<size_t>(stages) * STAGE_BYTES;
+  float* s_xf = reinterpret_cast<float*>(ctrl_base);                       // [2][kblocks][BT] activation scales
+  int* s_xsum = reinterpret_cast<int*>(s_xf + 2 * nkb_max * BT);           // [2][kblocks][BT] activation sums
+  uint64_t* bar_full = reinterpret_cast<uint64_t*>(s_xsum + 2 * nkb_max * BT);
   uint64_t* bar_empty = bar_full + stages;
   uint64_t* bar_dq = bar_empty + stages;       // [NO] operand tile written
   uint64_t* bar_oempty = bar_dq + NO;          // [NO] operand tile consumed
@@ -80,11 +86,14 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   uint64_t* bar_pempty = bar_pfull + 2;
   uint64_t* bar_sfull = bar_pempty + 2;
   uint64_t* bar_sempty = bar_sfull + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_sempty + 2);
+  uint64_t* bar_tail = bar_sempty + 2;         // [2][2] tail: maxima complete / sums complete
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tail + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* s_col_row = reinterpret_cast<int*>(tmem_slot + 4);           // [2][32]
   float* s_col_gam = reinterpret_cast<float*>(s_col_row + 2 * 32);  // [2][32]
-  int* s_blk_off = reinterpret_cast<int*>(s_col_gam + 2 * 32);      // [E+1]
+  unsigned int* s_amax = reinterpret_cast<unsigned int*>(s_col_gam + 2 * 32);   // [2][32] tail: group maxima
+  int* s_osum = reinterpret_cast<int*>(s_amax + 2 * 32);            // [2][32] tail: sums of the new integers
+  int* s_blk_off = s_osum + 2 * 32;                                 // [E+1]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -103,6 +112,8 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       mbar_init(smem_u32(&bar_pempty[s]), 4);
       mbar_init(smem_u32(&bar_sfull[s]), 1);
       mbar_init(smem_u32(&bar_sempty[s]), 4);
+      mbar_init(smem_u32(&bar_tail[2 * s]), 4);
+      mbar_init(smem_u32(&bar_tail[2 * s + 1]), 4);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -122,7 +133,7 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // the scheduler's reduction unit is one quantisation group (128 k = two pipeline stages)
+  // the scheduler's reduction unit is one quantisation group (128 k = one pipeline stage)
   const Ctrl c = make_ctrl(a, MODE == 1);
   const bool active = static_cast<int>(blockIdx.x) < c.grid_eff;
   constexpr int kTileN = (MODE == 0) ? kTileRows : 2 * kTileRows;
@@ -138,18 +149,19 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     const long long role_t0 = clock64();
     for (int tile = blockIdx.x; ok && tile < c.total; tile += c.grid_eff) {
       const TileCoord t = decode_tile(tile, c, s_blk_off, a.E, BT, a.num_nt, a.kblocks, kTileN);
-      for (int ks = 2 * t.kb0; ks < 2 * t.kb1; ++ks) {  // ks: 64-wide k step
+      const int xrow0 = (t.row0 / BT) * NB;   // the block's three planes are 3 * BT consecutive rows
+      for (int kb = t.kb0; kb < t.kb1; ++kb) {
         if (!mbar_wait_t(smem_u32(&bar_empty[stage]), phase ^ 1, abort_flag, DEV_TIMEOUT_PRODUCER, w_empty)) {
           ok = false;
           break;
         }
         const uint32_t full = smem_u32(&bar_full[stage]);
-        mbar_arrive_expect_tx(full, static_cast<uint32_t>(PK_BYTES + X_BYTES));
-        const uint32_t sbase = smem_u32(pk_base + static_cast<size_t>(stage) * STAGE_BYTES);
+        mbar_arrive_expect_tx(full, static_cast<uint32_t>(STAGE_BYTES));
+        const uint32_t sbase = smem_u32(ring + static_cast<size_t>(stage) * STAGE_BYTES);
         const uint32_t spk = sbase + X_BYTES;
-        tma_load_3d(spk, &tm_w, full, ks * 32, t.n0, t.e);
-        tma_load_3d(spk + kTileRows * 32, &tm_w, full, ks * 32, second_off + t.n0, t.e);
-        tma_load_2d(sbase, &tm_x, full, ks * 64, t.row0);
+        tma_load_3d(spk, &tm_w, full, kb * kPackedRowBytes, t.n0, t.e);
+        tma_load_3d(spk + kTileRows * kPackedRowBytes, &tm_w, full, kb * kPackedRowBytes, second_off + t.n0, t.e);
+        tma_load_2d(sbase, &tm_x, full, kb * 128, xrow0);
         ++issued;
         if (++stage == stages) {
           stage = 0;
@@ -173,7 +185,7 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     }
   } else if (active && warp == 1 && lane == 0) {
     // =============================== MMA issuer =================================
-    const uint32_t idesc = make_idesc(0u /* fp16 */, kTileRows, static_cast<uint32_t>(BT));
+    const uint32_t idesc = make_idesc_i8(false, true, kTileRows, static_cast<uint32_t>(NB));
     int stage = 0, ost = 0;
     uint32_t phase = 0, ophase = 0, j = 0;  // j counts groups over the whole launch
     bool ok = true;
@@ -181,43 +193,36 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     const long long role_t0 = clock64();
     for (int tile = blockIdx.x; ok && tile < c.total; tile += c.grid_eff) {
       const TileCoord t = decode_tile(tile, c, s_blk_off, a.E, BT, a.num_nt, a.kblocks, kTileN);
-      for (int kb = t.kb0; kb < t.kb1 && ok; ++kb, ++j) {
+      for (int kb = t.kb0; kb < t.kb1; ++kb, ++j) {
         const uint32_t pb = j & 1u;
-        if (!mbar_wait_t(smem_u32(&bar_pempty[pb]), ((j >> 1) & 1u) ^ 1u, abort_flag, DEV_TIMEOUT_MMA, w_pempty)) {
+        // the operand tile is written only after its TMA stage has landed, so the second wait
+        // also covers the token block of that stage
+        if (!mbar_wait_t(smem_u32(&bar_pempty[pb]), ((j >> 1) & 1u) ^ 1u, abort_flag, DEV_TIMEOUT_MMA, w_pempty) ||
+            !mbar_wait_t(smem_u32(&bar_dq[ost]), ophase, abort_flag, DEV_TIMEOUT_MMA, w_dq)) {
           ok = false;
           break;
         }
+        tc_fence_after();
         const uint32_t d0 = tmem_base + pb * PCOLS;
-#pragma unroll 1
-        for (int h = 0; h < 2; ++h) {
-          // the operand tile is written only after its TMA stage has landed, so this wait
-          // also covers the token block of that stage
-          if (!mbar_wait_t(smem_u32(&bar_dq[ost]), ophase, abort_flag, DEV_TIMEOUT_MMA, w_dq)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          // A operand: 64 TMEM columns of this stage (32 per weight block, 8 per 16-wide k slice)
-          const uint32_t a0 = tmem_base + A_COL0 + static_cast<uint32_t>(ost) * 64;
-          const uint64_t dx = smem_desc_k_sw128(smem_u32(pk_base + static_cast<size_t>(stage) * STAGE_BYTES));
+        // A operand: 64 TMEM columns of this stage (32 per weight block, 8 per 32-wide k slice)
+        const uint32_t a0 = tmem_base + A_COL0 + static_cast<uint32_t>(ost) * 64;
+        const uint64_t dx = smem_desc_k_sw128(smem_u32(ring + static_cast<size_t>(stage) * STAGE_BYTES));
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const uint32_t accum = (h > 0 || k > 0) ? 1u : 0u;
-            tc_mma_f16_ts(d0, a0 + 8 * k, dx + 2 * k, idesc, accum);
-            tc_mma_f16_ts(d0 + BT, a0 + 32 + 8 * k, dx + 2 * k, idesc, accum);
-          }
-          tc_commit(smem_u32(&bar_empty[stage]));
-          tc_commit(smem_u32(&bar_oempty[ost]));
-          if (++stage == stages) {
-            stage = 0;
-            phase ^= 1;
-          }
-          if (++ost == NO) {
-            ost = 0;
-            ophase ^= 1;
-          }
+        for (int k = 0; k < 4; ++k) {
+          tc_mma_i8_ts(d0, a0 + 8 * k, dx + 2 * k, idesc, k > 0 ? 1u : 0u);
+          tc_mma_i8_ts(d0 + NB, a0 + 32 + 8 * k, dx + 2 * k, idesc, k > 0 ? 1u : 0u);
         }
-        if (ok) tc_commit(smem_u32(&bar_pfull[pb]));
+        tc_commit(smem_u32(&bar_empty[stage]));
+        tc_commit(smem_u32(&bar_oempty[ost]));
+        tc_commit(smem_u32(&bar_pfull[pb]));
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1;
+        }
+        if (++ost == NO) {
+          ost = 0;
+          ophase ^= 1;
+        }
       }
     }
     STALL_ADD(1, w_pempty);
@@ -236,18 +241,28 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         s_col_row[buf * 32 + lane] = valid ? (MODE == 1 ? slot / a.topk : slot) : -1;
         s_col_gam[buf * 32 + lane] = valid ? a.row_gamma[t.row0 + lane] : 0.f;
       }
+      s_amax[buf * 32 + lane] = 0u;
+      s_osum[buf * 32 + lane] = 0;
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bar_sfull[buf]));
+      const int nkb = t.kb1 - t.kb0;
+      const uint32_t sfull = smem_u32(&bar_sfull[buf]);
+      if (lane == 0) mbar_arrive_expect_tx(sfull, static_cast<uint32_t>(nkb * BT * 8));
+      __syncwarp();
+      for (int i = lane; i < nkb; i += 32) {
+        const size_t src = static_cast<size_t>(t.kb0 + i) * a.ld_xscale + t.row0;
+        bulk_copy_g2s(smem_u32(s_xf + (buf * nkb_max + i) * BT), a.x_scale + src, BT * 4, sfull);
+        bulk_copy_g2s(smem_u32(s_xsum + (buf * nkb_max + i) * BT), a.x_sum + src, BT * 4, sfull);
+      }
     }
   } else if (active && warp >= 7) {
-    // =============================== int4 -> centred fp16 operand ===============
-    // warp w may touch TMEM lanes 32 * (w % 4)..: warps 7-10 convert the first weight block,
-    // warps 11-14 the second, each thread the row that is its own TMEM lane
-    const int wblk = (warp - 7) >> 2;
+    // =============================== nibbles -> unsigned bytes in tensor memory ==
+    // warp w may touch TMEM lanes 32 * (w % 4)..; each thread converts the two rows (one per
+    // weight block) that live in its own lane
     const int quad = warp & 3;
-    const int row = wblk * kTileRows + quad * 32 + lane;  // packed row of the stage
-    const uint32_t* sz = reinterpret_cast<const uint32_t*>(a.w_sz);
-    const int groups = a.kblocks;
+    const int row = quad * 32 + lane;
+    // the packed tile is staged with the 64-byte swizzle: 16-byte chunk c of row r sits at chunk
+    // c ^ ((r >> 1) & 3), which spreads the 64-byte row stride over all banks
+    const int sw = (row >> 1) & 3;
     int stage = 0, ost = 0;
     uint32_t phase = 0, ophase = 0;
     bool ok = true;
@@ -255,52 +270,45 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     const long long role_t0 = clock64();
     for (int tile = blockIdx.x; ok && tile < c.total; tile += c.grid_eff) {
       const TileCoord t = decode_tile(tile, c, s_blk_off, a.E, BT, a.num_nt, a.kblocks, kTileN);
-      const int n = (row < kTileRows) ? t.n0 + row : second_off + t.n0 + (row - kTileRows);
-      const bool n_ok = n < a.w_rows;
-      const uint32_t* szrow = sz + static_cast<size_t>(t.e) * groups * a.w_rows + n;
-      // zero points of this row, fetched three groups ahead of their use (a dependent global
-      // load per group would otherwise sit on the dequantisation's critical path);
-      // 0x6400 = fp16(1024 + 0) for rows past the expert, whose output is never stored
-      auto load_sz = [&](int kb) -> uint32_t {
-        return (n_ok && kb < t.kb1) ? __ldg(szrow + static_cast<size_t>(kb) * a.w_rows) : 0x64000000u;
-      };
-      uint32_t sz_a = load_sz(t.kb0), sz_b = load_sz(t.kb0 + 1), sz_c = load_sz(t.kb0 + 2);
-      for (int kb = t.kb0; kb < t.kb1 && ok; ++kb) {
-        const uint32_t szv = sz_a;
-        sz_a = sz_b;
-        sz_b = sz_c;
-        sz_c = load_sz(kb + 3);
-        const __half2 zp = __half2half2(__ushort_as_half(static_cast<unsigned short>(szv >> 16)));
-#pragma unroll 1
-        for (int h = 0; h < 2; ++h) {
-          if (!mbar_wait_t(smem_u32(&bar_full[stage]), phase, abort_flag, DEV_TIMEOUT_MMA, w_full) ||
-              !mbar_wait_t(smem_u32(&bar_oempty[ost]), ophase ^ 1, abort_flag, DEV_TIMEOUT_MMA, w_oempty)) {
-            ok = false;
-            break;
-          }
-          const uint4* pk = reinterpret_cast<const uint4*>(pk_base + static_cast<size_t>(stage) * STAGE_BYTES +
-                                                           X_BYTES + row * 32);
+      for (int kb = t.kb0; kb < t.kb1; ++kb) {
+        if (!mbar_wait_t(smem_u32(&bar_full[stage]), phase, abort_flag, DEV_TIMEOUT_MMA, w_full) ||
+            !mbar_wait_t(smem_u32(&bar_oempty[ost]), ophase ^ 1, abort_flag, DEV_TIMEOUT_MMA, w_oempty)) {
+          ok = false;
+          break;
+        }
+        const uint8_t* pk = ring + static_cast<size_t>(stage) * STAGE_BYTES + X_BYTES;
+        tc_fence_after();
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+          const uint4* prow = reinterpret_cast<const uint4*>(pk + (b * kTileRows + row) * kPackedRowBytes);
           uint32_t o[32];
-          dequant_w4x32_centered(pk[0], zp, o);
-          dequant_w4x32_centered(pk[1], zp, o + 16);
-          tc_fence_after();
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            const uint4 v = prow[ch ^ sw];
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              o[8 * ch + 2 * q] = w[q] & 0x0F0F0F0Fu;
+              o[8 * ch + 2 * q + 1] = (w[q] >> 4) & 0x0F0F0F0Fu;
+            }
+          }
           tmem_st32_wait(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + A_COL0 +
-                             static_cast<uint32_t>(ost) * 64 + static_cast<uint32_t>(wblk) * 32, o);
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&bar_dq[ost]));
-          if (++stage == stages) {
-            stage = 0;
-            phase ^= 1;
-          }
-          if (++ost == NO) {
-            ost = 0;
-            ophase ^= 1;
-          }
+                             static_cast<uint32_t>(ost) * 64 + static_cast<uint32_t>(b) * 32, o);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_dq[ost]));
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1;
+        }
+        if (++ost == NO) {
+          ost = 0;
+          ophase ^= 1;
         }
       }
     }
-    if (threadIdx.x == 8 * 32) {
+    if (threadIdx.x == 7 * 32) {
       STALL_ADD(3, w_full);
       STALL_ADD(4, w_oempty);
       STALL_ADD(10, static_cast<unsigned long long>(clock64() - role_t0));
@@ -324,18 +332,23 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       const int buf = iter & 1;
       const int* col_row = s_col_row + buf * 32;
       const float* col_gam = s_col_gam + buf * 32;
-      // scales of this thread's two weight rows, one per group
+      // scale (fp16, low half) and 1024 + zero (fp16, high half) of this thread's two weight rows
       const int n = t.n0 + lrow;
       const int n2 = second_off + t.n0 + lrow;
       const bool ok0 = n < a.w_rows, ok1 = n2 < a.w_rows;
       const uint32_t* sz0 = sz + static_cast<size_t>(t.e) * groups * a.w_rows + n;
       const uint32_t* sz1 = sz + static_cast<size_t>(t.e) * groups * a.w_rows + n2;
       auto scale_of = [](uint32_t v) { return __half2float(__ushort_as_half(static_cast<unsigned short>(v & 0xFFFFu))); };
-      float s0 = ok0 ? scale_of(__ldg(sz0 + static_cast<size_t>(t.kb0) * a.w_rows)) : 0.f;
-      float s1 = ok1 ? scale_of(__ldg(sz1 + static_cast<size_t>(t.kb0) * a.w_rows)) : 0.f;
-      float s0n = (ok0 && t.kb0 + 1 < t.kb1) ? scale_of(__ldg(sz0 + static_cast<size_t>(t.kb0 + 1) * a.w_rows)) : 0.f;
-      float s1n = (ok1 && t.kb0 + 1 < t.kb1) ? scale_of(__ldg(sz1 + static_cast<size_t>(t.kb0 + 1) * a.w_rows)) : 0.f;
+      // fp16(1024 + z) has the bit pattern 0x6400 + z; rows past the expert carry word 0 -> scale 0
+      auto zero_of = [](uint32_t v) { return static_cast<int>((v >> 16) & 0x3FFu); };
+      auto load_sz = [&](const uint32_t* p, bool row_ok, int kb) -> uint32_t {
+        return (row_ok && kb < t.kb1) ? __ldg(p + static_cast<size_t>(kb) * a.w_rows) : 0u;
+      };
+      uint32_t c0 = load_sz(sz0, ok0, t.kb0), c1 = load_sz(sz1, ok1, t.kb0);
+      uint32_t n0w = load_sz(sz0, ok0, t.kb0 + 1), n1w = load_sz(sz1, ok1, t.kb0 + 1);
       if (!mbar_wait_t(smem_u32(&bar_sfull[buf]), (iter >> 1) & 1, abort_flag, DEV_TIMEOUT_EPILOGUE, w_sfull)) break;
+      const float* xf_t = s_xf + buf * nkb_max * BT;
+      const int* xs_t = s_xsum + buf * nkb_max * BT;
 
       float acc0[BT], acc1[BT];
 #pragma unroll
@@ -345,11 +358,11 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       }
       for (int kb = t.kb0; kb < t.kb1; ++kb, ++j) {
         // fetch the scales two groups ahead, before waiting for this group's partial sums
-        uint32_t r0 = 0, r1 = 0;
-        if (kb + 2 < t.kb1) {
-          if (ok0) r0 = __ldg(sz0 + static_cast<size_t>(kb + 2) * a.w_rows);
-          if (ok1) r1 = __ldg(sz1 + static_cast<size_t>(kb + 2) * a.w_rows);
-        }
+        const uint32_t r0 = load_sz(sz0, ok0, kb + 2), r1 = load_sz(sz1, ok1, kb + 2);
+        const float s0 = scale_of(c0), s1 = scale_of(c1);
+        const int z0 = zero_of(c0), z1 = zero_of(c1);
+        const float* xf = xf_t + (kb - t.kb0) * BT;
+        const int* xs = xs_t + (kb - t.kb0) * BT;
         const uint32_t pb = j & 1u;
         if (!mbar_wait_t(smem_u32(&bar_pfull[pb]), (j >> 1) & 1u, abort_flag, DEV_TIMEOUT_EPILOGUE, w_pfull)) {
           ok = false;
@@ -357,40 +370,93 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         }
         tc_fence_after();
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + pb * PCOLS;
-        if constexpr (BT == 32) {
-          float g[32], u[32];
-          tmem_ld32x2_wait(taddr, taddr + BT, g, u);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            acc0[i] = fmaf(g[i], s0, acc0[i]);
-            acc1[i] = fmaf(u[i], s1, acc1[i]);
+        for (int cb = 0; cb < BT; cb += 16) {
+          float xfv[16];
+          int xsv[16];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float4 fv = *reinterpret_cast<const float4*>(xf + cb + 4 * q);
+            const int4 sv = *reinterpret_cast<const int4*>(xs + cb + 4 * q);
+            xfv[4 * q] = fv.x; xfv[4 * q + 1] = fv.y; xfv[4 * q + 2] = fv.z; xfv[4 * q + 3] = fv.w;
+            xsv[4 * q] = sv.x; xsv[4 * q + 1] = sv.y; xsv[4 * q + 2] = sv.z; xsv[4 * q + 3] = sv.w;
           }
-        } else {
-          float g[16], u[16];
-          tmem_ld16x2_wait(taddr, taddr + BT, g, u);
+          int p0[16], p1[16], p2[16];
+          tmem_ld16x3_wait_b32(taddr + cb, taddr + BT + cb, taddr + 2 * BT + cb, p0, p1, p2);
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            acc0[i] = fmaf(g[i], s0, acc0[i]);
-            acc1[i] = fmaf(u[i], s1, acc1[i]);
+            const int sum = p0[i] + (p1[i] << 8) + (p2[i] << 16) - z0 * xsv[i];
+            acc0[cb + i] = fmaf(s0 * xfv[i], static_cast<float>(sum), acc0[cb + i]);
+          }
+          tmem_ld16x3_wait_b32(taddr + NB + cb, taddr + NB + BT + cb, taddr + NB + 2 * BT + cb, p0, p1, p2);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int sum = p0[i] + (p1[i] << 8) + (p2[i] << 16) - z1 * xsv[i];
+            acc1[cb + i] = fmaf(s1 * xfv[i], static_cast<float>(sum), acc1[cb + i]);
           }
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bar_pempty[pb]));
-        s0 = s0n;
-        s1 = s1n;
-        s0n = scale_of(r0);   // fp16 bits 0 -> 0.0f when out of range
-        s1n = scale_of(r1);
+        c0 = n0w;
+        c1 = n1w;
+        n0w = r0;
+        n1w = r1;
       }
       if (!ok) break;
 
       if (MODE == 0) {
-        __half* out = reinterpret_cast<__half*>(a.out) + static_cast<size_t>(t.row0) * a.ld_out + n;
+        // activation, rounded to fp16 as the 16-bit path stores it, then re-expressed for the
+        // second GEMM: this tile's 128 columns are one of its reduction groups
         const bool n_ok = n < a.N;
+        unsigned int* amax = s_amax + buf * 32;
+        int* osum = s_osum + buf * 32;
 #pragma unroll
         for (int i = 0; i < BT; ++i) {
-          const float av = act_mul<__half>(acc0[i], acc1[i], w_on_input, col_gam[i], mimic, act_params(a));
-          if (n_ok) out[static_cast<size_t>(i) * a.ld_out] = __float2half_rn(av);
+          float av = act_mul<__half>(acc0[i], acc1[i], w_on_input, col_gam[i], mimic, act_params(a));
+          av = n_ok ? __half2float(__float2half_rn(av)) : 0.f;
+          acc0[i] = av;
+          const unsigned int m = __reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(av)));
+          if (lane == 0) atomicMax(amax + i, m);
+        }
+        // the four warps meet on a barrier with a bounded wait (a plain bar.sync would hang the
+        // CTA if one of them had given up)
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_tail[2 * buf]));
+        if (!mbar_wait(smem_u32(&bar_tail[2 * buf]), (iter >> 1) & 1, abort_flag, DEV_TIMEOUT_EPILOGUE)) break;
+        const int kcol = (n & ~7) | plane_pos(n & 7);
+        const size_t plane_stride = static_cast<size_t>(BT) * a.ld_out;
+        uint8_t* obase = a.out_q + static_cast<size_t>(t.row0 / BT) * 3 * plane_stride + kcol;
+#pragma unroll
+        for (int i = 0; i < BT; ++i) {
+          // group maximum in [2^ex, 2^(ex+1)): integers of magnitude below 2^19
+          const unsigned int mb = amax[i];
+          const int ex = static_cast<int>(mb >> 23) - 127;
+          const float mult = (mb == 0u) ? 0.f : __uint_as_float(static_cast<unsigned int>(127 + 18 - ex) << 23);
+          const int v = __float2int_rn(acc0[i] * mult);
+          const int b0 = (v << 24) >> 24;
+          const int v1 = (v - b0) >> 8;
+          const int b1 = (v1 << 24) >> 24;
+          const int b2 = (v1 - b1) >> 8;
+          if (n_ok) {
+            uint8_t* o = obase + static_cast<size_t>(i) * a.ld_out;
+            o[0] = static_cast<uint8_t>(b0);
+            o[plane_stride] = static_cast<uint8_t>(b1);
+            o[2 * plane_stride] = static_cast<uint8_t>(b2);
+          }
+          const int ws = __reduce_add_sync(0xffffffffu, v);
+          if (lane == 0) atomicAdd(osum + i, ws);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_tail[2 * buf + 1]));
+        if (!mbar_wait(smem_u32(&bar_tail[2 * buf + 1]), (iter >> 1) & 1, abort_flag, DEV_TIMEOUT_EPILOGUE)) break;
+        if (lrow < BT && t.n0 < a.N) {
+          const unsigned int mb = amax[lrow];
+          const int ex = static_cast<int>(mb >> 23) - 127;
+          const float f = (mb == 0u) ? 1.0f : __uint_as_float(static_cast<unsigned int>(127 + ex - 18) << 23);
+          const size_t dst = static_cast<size_t>(t.n0 / 128) * a.ld_xscale + t.row0 + lrow;
+          a.out_scale[dst] = f;
+          a.out_sum[dst] = osum[lrow];
         }
       } else {
         float* out = reinterpret_cast<float*>(a.out) + n;
@@ -431,11 +497,12 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   if (threadIdx.x == 0 && *abort_flag != 0) atomicCAS(a.status, 0, *abort_flag);
 }
 
-size_t w4_stage_bytes(const GemmArgs& a) {   // one stage of the TMA ring
-  return static_cast<size_t>(a.BT) * kStageKBytes + 2 * kTileRows * 32;
+size_t w4_stage_bytes(const GemmArgs& a) {   // one stage of the TMA ring: three activation planes + packed rows
+  return static_cast<size_t>(3 * a.BT) * kStageKBytes + 2 * kTileRows * kPackedRowBytes;
 }
-size_t w4_ctrl_bytes(const GemmArgs& a) {    // barriers + tables
-  return 1024 + 2 * 32 * 8 + static_cast<size_t>(a.E + 1) * 4 + 64;
+size_t w4_ctrl_bytes(const GemmArgs& a) {    // activation tables, barriers, per-tile tables
+  return static_cast<size_t>(2) * 2 * a.kblocks * a.BT * 4 + 1024 + 4 * 8 + 4 * 2 * 32 * 4 +
+         static_cast<size_t>(a.E + 1) * 4 + 64;
 }
 
 template <int MODE, int BT>
@@ -463,17 +530,19 @@ extern "C" int b200moe_debug_stalls_w4(unsigned long long* out16, int reset) {
 }
 #endif
 
+bool gemm_w4_planes_ok(int K, int BT) {
+  return (BT == 16 || BT == 32) && K % 128 == 0 && K / 128 <= kMaxGroupsW4;
+}
+
 void gemm_plan_w4(GemmArgs* a) {
   a->orient = 0;
   const int tile_n = (a->mode == 0) ? kTileRows : 2 * kTileRows;
   a->num_nt = (a->N + tile_n - 1) / tile_n;
   a->kblocks = (a->K + 127) / 128;  // reduction unit = one quantisation group
-  int tc = 32;
-  while (tc < 4 * a->BT + 64 * kOperandStages) tc <<= 1;   // partial sums + A-operand stages
-  a->tmem_cols = tc;
+  a->tmem_cols = 512;               // two partial buffers of 6 * BT int32 columns + the A-operand stages
   a->acc_stages = 2;
   int st = static_cast<int>((kSmemLimit - 1024 - w4_ctrl_bytes(*a)) / w4_stage_bytes(*a));
-  if (st > 16) st = 16;
+  if (st > 8) st = 8;
   if (st < 2) st = 2;
   a->stages = st;
   if (a->max_split <= 0) a->max_split = 16;
@@ -482,12 +551,11 @@ void gemm_plan_w4(GemmArgs* a) {
 int launch_gemm_w4(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmArgs& a, int num_sms,
                    cudaStream_t stream) {
   if (a.wmode != B200MOE_W_INT4_AWQ || a.dtype != B200MOE_DTYPE_FP16 || a.w_sz == nullptr) return B200MOE_ERR_BAD_ARG;
-  if (a.K % 128 != 0) return B200MOE_ERR_UNSUPPORTED;
+  if (!gemm_w4_planes_ok(a.K, a.BT) || a.x_scale == nullptr || a.x_sum == nullptr) return B200MOE_ERR_UNSUPPORTED;
+  if (a.mode == 0 && (a.out_q == nullptr || a.out_scale == nullptr || a.out_sum == nullptr)) return B200MOE_ERR_BAD_ARG;
   if (a.BT == 16)
     return a.mode == 0 ? launch_w4<0, 16>(tm_w, tm_x, a, num_sms, stream) : launch_w4<1, 16>(tm_w, tm_x, a, num_sms, stream);
-  if (a.BT == 32)
-    return a.mode == 0 ? launch_w4<0, 32>(tm_w, tm_x, a, num_sms, stream) : launch_w4<1, 32>(tm_w, tm_x, a, num_sms, stream);
-  return B200MOE_ERR_BAD_ARG;
+  return a.mode == 0 ? launch_w4<0, 32>(tm_w, tm_x, a, num_sms, stream) : launch_w4<1, 32>(tm_w, tm_x, a, num_sms, stream);
 }
 
 }  // namespace b200moe

@@ -102,6 +102,67 @@ group_quant_fp8_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* 
   }
 }
 
+// One warp per (padded row, 128-wide group): see launch_group_split_i8.
+__global__ void __launch_bounds__(256)
+group_split_i8_kernel(const __half* __restrict__ x, uint8_t* __restrict__ planes, float* __restrict__ scales,
+                      int* __restrict__ sums, const int* __restrict__ sorted_ids, const int* __restrict__ meta,
+                      int P, int topk, int cap, int K, int BT, int ld, uint4* __restrict__ zero,
+                      long long zero_chunks) {
+  griddep_wait();
+  griddep_launch_dependents();
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < zero_chunks;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    zero[i] = make_uint4(0, 0, 0, 0);
+  const int groups = K >> 7;
+  const int lane = threadIdx.x & 31;
+  const int rows = min(meta[1], cap);
+  const long long total = static_cast<long long>(rows) * groups;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const size_t plane_stride = static_cast<size_t>(BT) * K;
+  for (long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; w < total; w += warps) {
+    const int r = static_cast<int>(w / groups), g = static_cast<int>(w - static_cast<long long>(r) * groups);
+    const int slot = sorted_ids[r];
+    const bool pad = (slot < 0 || slot >= P);
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (!pad) load4<__half>(x + static_cast<size_t>(slot / topk) * K + g * 128 + lane * 4, v);
+    const float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    const unsigned int mb = __reduce_max_sync(0xffffffffu, __float_as_uint(amax));
+    // group maximum in [2^ex, 2^(ex+1)): x * 2^(18-ex) has magnitude below 2^19
+    const int ex = static_cast<int>(mb >> 23) - 127;
+    const float mult = (mb == 0u) ? 0.f : __uint_as_float(static_cast<unsigned int>(127 + 18 - ex) << 23);
+    const float f = (mb == 0u) ? 1.0f : __uint_as_float(static_cast<unsigned int>(127 + ex - 18) << 23);
+    uint32_t pk[3] = {0u, 0u, 0u};
+    int part = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int q = __float2int_rn(v[i] * mult);
+      const int b0 = (q << 24) >> 24;
+      const int q1 = (q - b0) >> 8;
+      const int b1 = (q1 << 24) >> 24;
+      const int b2 = (q1 - b1) >> 8;
+      pk[0] |= static_cast<uint32_t>(b0 & 0xFF) << (8 * i);
+      pk[1] |= static_cast<uint32_t>(b1 & 0xFF) << (8 * i);
+      pk[2] |= static_cast<uint32_t>(b2 & 0xFF) << (8 * i);
+      part += q;
+    }
+    const int xsum = __reduce_add_sync(0xffffffffu, part);
+    // an even lane holds elements 0..3 of its run of eight, the odd neighbour 4..7; stored
+    // order is (0, 4, 1, 5 | 2, 6, 3, 7)
+    uint8_t* dst = planes + (static_cast<size_t>(r / BT) * 3) * plane_stride + static_cast<size_t>(r % BT) * K +
+                   g * 128 + lane * 4;
+#pragma unroll
+    for (int p = 0; p < 3; ++p) {
+      const uint32_t other = __shfl_xor_sync(0xffffffffu, pk[p], 1);
+      const uint32_t word = (lane & 1) ? __byte_perm(pk[p], other, 0x3726) : __byte_perm(pk[p], other, 0x5140);
+      *reinterpret_cast<uint32_t*>(dst + p * plane_stride) = word;
+    }
+    if (lane == 0) {
+      scales[static_cast<size_t>(g) * ld + r] = f;
+      sums[static_cast<size_t>(g) * ld + r] = xsum;
+    }
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 finalize_kernel(const float4* __restrict__ acc, T* __restrict__ out, size_t n4, float scale) {
@@ -151,6 +212,21 @@ int launch_group_quant_fp8(const void* x, int dtype, void* q, float* scales, con
     err = launch_kernel(group_quant_fp8_kernel<__half>, dim3(static_cast<unsigned>(ctas)), dim3(256), 0, stream, pdl,
                         reinterpret_cast<const __half*>(x), reinterpret_cast<uint8_t*>(q), scales, sorted_ids, meta, P,
                         topk, rows, K, scale_t, ld_scale, reinterpret_cast<uint4*>(zero), zc);
+  return err == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
+}
+
+int launch_group_split_i8(const void* x, uint8_t* planes, float* scales, int* sums, const int* sorted_ids,
+                          const int* meta, int P, int topk, int cap, int K, int BT, int ld, void* zero,
+                          size_t zero_bytes, int num_sms, cudaStream_t stream, bool pdl) {
+  if (K % 128 != 0 || zero_bytes % 16 != 0 || BT <= 0 || cap % BT != 0) return B200MOE_ERR_UNSUPPORTED;
+  long long warps = static_cast<long long>(cap) * (K / 128);
+  long long ctas = (warps + 7) / 8;
+  if (ctas > num_sms * 16) ctas = num_sms * 16;
+  if (ctas < 1) ctas = 1;
+  cudaError_t err = launch_kernel(group_split_i8_kernel, dim3(static_cast<unsigned>(ctas)), dim3(256), 0, stream, pdl,
+                                  reinterpret_cast<const __half*>(x), planes, scales, sums, sorted_ids, meta, P, topk,
+                                  cap, K, BT, ld, reinterpret_cast<uint4*>(zero),
+                                  static_cast<long long>(zero_bytes / 16));
   return err == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
 }
 

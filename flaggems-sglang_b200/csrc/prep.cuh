@@ -16,6 +16,15 @@ int launch_group_quant_fp8(const void* x, int dtype, void* q, float* scales, con
                            const int* meta, int P, int topk, int rows, int K, int scale_t, int ld_scale,
                            void* zero, size_t zero_bytes, int num_sms, cudaStream_t stream, bool pdl);
 
+// fp16 token rows -> the integer form the int4 decode kernels read: per (row, 128-k group) a
+// power-of-two scale f (2^(e-18) for a group maximum in [2^e, 2^(e+1))), the exact integers
+// v = rint(x / f) split into three signed byte planes (v = p0 + 256 p1 + 65536 p2) and their sum.
+// planes: [block][plane][BT rows][K] int8, inside each aligned run of eight k the order
+// (0, 4, 1, 5, 2, 6, 3, 7); scales / sums: [K/128][ld].  Rows are gathered through sorted_ids.
+int launch_group_split_i8(const void* x, uint8_t* planes, float* scales, int* sums, const int* sorted_ids,
+                          const int* meta, int P, int topk, int cap, int K, int BT, int ld, void* zero,
+                          size_t zero_bytes, int num_sms, cudaStream_t stream, bool pdl);
+
 // out[i] = cast(acc[i] * scale)
 int launch_finalize(const float* acc, void* out, int dtype, size_t n, float scale, int num_sms,
                     cudaStream_t stream, bool pdl);
