@@ -241,6 +241,27 @@ __device__ __forceinline__ void tmem_ld16_wait(uint32_t taddr, float (&v)[16]) {
 }
 
 // Two loads (e.g. gate and up accumulators) in flight before the single wait.
+// Six 8-column reads of raw 32-bit accumulators, one wait.
+#define B200MOE_R8(r, o)                                                                             \
+  "=r"(r[o + 0]), "=r"(r[o + 1]), "=r"(r[o + 2]), "=r"(r[o + 3]), "=r"(r[o + 4]), "=r"(r[o + 5]),   \
+      "=r"(r[o + 6]), "=r"(r[o + 7])
+__device__ __forceinline__ void tmem_ld8x6_wait_b32(uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t a4,
+                                                    uint32_t a5, int (&v)[48]) {
+  uint32_t r[48];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%48];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%8, %9, %10, %11, %12, %13, %14, %15}, [%49];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%16, %17, %18, %19, %20, %21, %22, %23}, [%50];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%24, %25, %26, %27, %28, %29, %30, %31}, [%51];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%32, %33, %34, %35, %36, %37, %38, %39}, [%52];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%40, %41, %42, %43, %44, %45, %46, %47}, [%53];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : B200MOE_R8(r, 0), B200MOE_R8(r, 8), B200MOE_R8(r, 16), B200MOE_R8(r, 24), B200MOE_R8(r, 32), B200MOE_R8(r, 40)
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(a4), "r"(a5)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 48; ++i) v[i] = static_cast<int>(r[i]);
+}
 // Three 16-column reads of raw 32-bit accumulators (integer MMAs), one wait.
 __device__ __forceinline__ void tmem_ld16x3_wait_b32(uint32_t taddr0, uint32_t taddr1, uint32_t taddr2,
                                                      int (&v0)[16], int (&v1)[16], int (&v2)[16]) {

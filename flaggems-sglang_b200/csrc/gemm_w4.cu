@@ -34,8 +34,10 @@
 // elements (0, 4, 1, 5) and (2, 6, 3, 7).  The activation planes are stored in that same
 // order; a dot product does not care as long as both sides agree.
 //
-// Warps: 0 TMA producer, 1 MMA issuer, 2-5 promotion + tail, 6 per-tile table loader,
-// 7-10 nibble -> byte conversion.
+// Warps: 0 TMA producer, 1 MMA issuer, 6 per-tile table loader, 7-10 nibble -> byte conversion,
+// 2-5 and 11-14 promotion + tail: a thread owns one weight row (its TMEM lane) and half of the
+// token block, so that two promotion warps share each scheduler and hide each other's
+// tensor-memory load latency (with one set of warps the promotion, not the MMA, set the pace).
 #include "gemm_sched.cuh"
 
 namespace b200moe {
@@ -50,9 +52,11 @@ __device__ unsigned long long g_stall_w4[16];
 #endif
 
 constexpr int kDqWarps = 4;
-constexpr int kThreadsW4P = 7 * 32 + 32 * kDqWarps;  // 352
+constexpr int kPromoWarps = 8;
+constexpr int kThreadsW4P = 3 * 32 + 32 * kDqWarps + 32 * kPromoWarps;  // 480
 constexpr int kPackedRowBytes = 64;                  // 128 k of one weight row
-constexpr int kMaxGroupsW4 = 128;                    // reduction groups whose tables fit in shared memory
+constexpr int kMaxGroupsW4 = 128;
+constexpr int kSzSlots = 16;                         // ring of per-group scale / zero words (1 KiB each)                    // reduction groups whose tables fit in shared memory
 
 // position inside an aligned run of eight k at which element e is stored
 __device__ __forceinline__ int plane_pos(int e) { return ((e & 3) << 1) | ((e >> 2) & 1); }
@@ -78,7 +82,8 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   uint8_t* ctrl_base = ring + static_cast<size_t>(stages) * STAGE_BYTES;
   float* s_xf = reinterpret_cast<float*>(ctrl_base);                       // [2][kblocks][BT] activation scales
   int* s_xsum = reinterpret_cast<int*>(s_xf + 2 * nkb_max * BT);           // [2][kblocks][BT] activation sums
-  uint64_t* bar_full = reinterpret_cast<uint64_t*>(s_xsum + 2 * nkb_max * BT);
+  uint32_t* s_sz = reinterpret_cast<uint32_t*>(s_xsum + 2 * nkb_max * BT);  // [kSzSlots][2 blocks][128 rows]
+  uint64_t* bar_full = reinterpret_cast<uint64_t*>(s_sz + kSzSlots * 256);
   uint64_t* bar_empty = bar_full + stages;
   uint64_t* bar_dq = bar_empty + stages;       // [NO] operand tile written
   uint64_t* bar_oempty = bar_dq + NO;          // [NO] operand tile consumed
@@ -87,7 +92,9 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   uint64_t* bar_sfull = bar_pempty + 2;
   uint64_t* bar_sempty = bar_sfull + 2;
   uint64_t* bar_tail = bar_sempty + 2;         // [2][2] tail: maxima complete / sums complete
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tail + 4);
+  uint64_t* bar_zfull = bar_tail + 4;          // [kSzSlots] scale words landed
+  uint64_t* bar_zempty = bar_zfull + kSzSlots; // [kSzSlots] scale words read by every promotion warp
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_zempty + kSzSlots);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* s_col_row = reinterpret_cast<int*>(tmem_slot + 4);           // [2][32]
   float* s_col_gam = reinterpret_cast<float*>(s_col_row + 2 * 32);  // [2][32]
@@ -109,11 +116,15 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(smem_u32(&bar_pfull[s]), 1);
-      mbar_init(smem_u32(&bar_pempty[s]), 4);
+      mbar_init(smem_u32(&bar_pempty[s]), kPromoWarps);
       mbar_init(smem_u32(&bar_sfull[s]), 1);
-      mbar_init(smem_u32(&bar_sempty[s]), 4);
-      mbar_init(smem_u32(&bar_tail[2 * s]), 4);
-      mbar_init(smem_u32(&bar_tail[2 * s + 1]), 4);
+      mbar_init(smem_u32(&bar_sempty[s]), kPromoWarps);
+      mbar_init(smem_u32(&bar_tail[2 * s]), kPromoWarps);
+      mbar_init(smem_u32(&bar_tail[2 * s + 1]), kPromoWarps);
+    }
+    for (int s = 0; s < kSzSlots; ++s) {
+      mbar_init(smem_u32(&bar_zfull[s]), 1);
+      mbar_init(smem_u32(&bar_zempty[s]), kPromoWarps);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -144,16 +155,33 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     int stage = 0;
     uint32_t phase = 0;
     long long issued = 0;
+    uint32_t jz = 0;   // groups issued over the whole launch (index into the scale ring)
     bool ok = true;
     unsigned long long w_empty = 0;
     const long long role_t0 = clock64();
+    const uint32_t* szg = reinterpret_cast<const uint32_t*>(a.w_sz);
     for (int tile = blockIdx.x; ok && tile < c.total; tile += c.grid_eff) {
       const TileCoord t = decode_tile(tile, c, s_blk_off, a.E, BT, a.num_nt, a.kblocks, kTileN);
       const int xrow0 = (t.row0 / BT) * NB;   // the block's three planes are 3 * BT consecutive rows
-      for (int kb = t.kb0; kb < t.kb1; ++kb) {
-        if (!mbar_wait_t(smem_u32(&bar_empty[stage]), phase ^ 1, abort_flag, DEV_TIMEOUT_PRODUCER, w_empty)) {
+      // whole 128-row blocks only (weight rows per expert are a multiple of 128); the second
+      // block of the last tile may lie past the expert
+      const bool second_in = second_off + t.n0 < a.w_rows;
+      for (int kb = t.kb0; kb < t.kb1; ++kb, ++jz) {
+        const uint32_t zs = jz % kSzSlots;
+        if (!mbar_wait_t(smem_u32(&bar_empty[stage]), phase ^ 1, abort_flag, DEV_TIMEOUT_PRODUCER, w_empty) ||
+            !mbar_wait_t(smem_u32(&bar_zempty[zs]), ((jz / kSzSlots) & 1u) ^ 1u, abort_flag, DEV_TIMEOUT_PRODUCER,
+                         w_empty)) {
           ok = false;
           break;
+        }
+        // scale / zero words of the group's two row blocks: the promotion warps read them from
+        // shared memory, so no global load sits on their critical path
+        {
+          const uint32_t zfull = smem_u32(&bar_zfull[zs]);
+          mbar_arrive_expect_tx(zfull, second_in ? 1024u : 512u);
+          const uint32_t* src = szg + (static_cast<size_t>(t.e) * a.kblocks + kb) * a.w_rows;
+          bulk_copy_g2s(smem_u32(s_sz + zs * 256), src + t.n0, 512, zfull);
+          if (second_in) bulk_copy_g2s(smem_u32(s_sz + zs * 256 + 128), src + second_off + t.n0, 512, zfull);
         }
         const uint32_t full = smem_u32(&bar_full[stage]);
         mbar_arrive_expect_tx(full, static_cast<uint32_t>(STAGE_BYTES));
@@ -254,7 +282,7 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         bulk_copy_g2s(smem_u32(s_xsum + (buf * nkb_max + i) * BT), a.x_sum + src, BT * 4, sfull);
       }
     }
-  } else if (active && warp >= 7) {
+  } else if (active && warp >= 7 && warp < 7 + kDqWarps) {
     // =============================== nibbles -> unsigned bytes in tensor memory ==
     // warp w may touch TMEM lanes 32 * (w % 4)..; each thread converts the two rows (one per
     // weight block) that live in its own lane
@@ -313,95 +341,100 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       STALL_ADD(4, w_oempty);
       STALL_ADD(10, static_cast<unsigned long long>(clock64() - role_t0));
     }
-  } else if (active && warp >= 2 && warp < 6) {
+  } else if (active && ((warp >= 2 && warp < 6) || warp >= 7 + kDqWarps)) {
     // =============================== promotion + tail ===========================
+    constexpr int HT = BT / 2;                  // tokens per thread
     unsigned long long w_pfull = 0, w_sfull = 0;
     const long long role_t0 = clock64();
     const int quad = warp & 3;
     const int lrow = quad * 32 + lane;
+    const int tk0 = (warp < 6) ? 0 : HT;        // first token of this thread's half
     const bool w_on_input = (a.flags & B200MOE_FLAG_WEIGHT_ON_INPUT) != 0;
     const bool mimic = (a.flags & B200MOE_FLAG_MIMIC_ROUNDING) != 0;
     const bool round_pair = mimic && c.split == 1;
-    const uint32_t* sz = reinterpret_cast<const uint32_t*>(a.w_sz);
-    const int groups = a.kblocks;
     uint32_t j = 0;
     int iter = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < c.total; tile += c.grid_eff, ++iter) {
       const TileCoord t = decode_tile(tile, c, s_blk_off, a.E, BT, a.num_nt, a.kblocks, kTileN);
       const int buf = iter & 1;
-      const int* col_row = s_col_row + buf * 32;
-      const float* col_gam = s_col_gam + buf * 32;
+      const int* col_row = s_col_row + buf * 32 + tk0;
+      const float* col_gam = s_col_gam + buf * 32 + tk0;
       // scale (fp16, low half) and 1024 + zero (fp16, high half) of this thread's two weight rows
       const int n = t.n0 + lrow;
       const int n2 = second_off + t.n0 + lrow;
       const bool ok0 = n < a.w_rows, ok1 = n2 < a.w_rows;
-      const uint32_t* sz0 = sz + static_cast<size_t>(t.e) * groups * a.w_rows + n;
-      const uint32_t* sz1 = sz + static_cast<size_t>(t.e) * groups * a.w_rows + n2;
       auto scale_of = [](uint32_t v) { return __half2float(__ushort_as_half(static_cast<unsigned short>(v & 0xFFFFu))); };
       // fp16(1024 + z) has the bit pattern 0x6400 + z; rows past the expert carry word 0 -> scale 0
       auto zero_of = [](uint32_t v) { return static_cast<int>((v >> 16) & 0x3FFu); };
-      auto load_sz = [&](const uint32_t* p, bool row_ok, int kb) -> uint32_t {
-        return (row_ok && kb < t.kb1) ? __ldg(p + static_cast<size_t>(kb) * a.w_rows) : 0u;
-      };
-      uint32_t c0 = load_sz(sz0, ok0, t.kb0), c1 = load_sz(sz1, ok1, t.kb0);
-      uint32_t n0w = load_sz(sz0, ok0, t.kb0 + 1), n1w = load_sz(sz1, ok1, t.kb0 + 1);
       if (!mbar_wait_t(smem_u32(&bar_sfull[buf]), (iter >> 1) & 1, abort_flag, DEV_TIMEOUT_EPILOGUE, w_sfull)) break;
-      const float* xf_t = s_xf + buf * nkb_max * BT;
-      const int* xs_t = s_xsum + buf * nkb_max * BT;
+      const float* xf_t = s_xf + buf * nkb_max * BT + tk0;
+      const int* xs_t = s_xsum + buf * nkb_max * BT + tk0;
 
-      float acc0[BT], acc1[BT];
+      float acc0[HT], acc1[HT];
 #pragma unroll
-      for (int i = 0; i < BT; ++i) {
+      for (int i = 0; i < HT; ++i) {
         acc0[i] = 0.f;
         acc1[i] = 0.f;
       }
       for (int kb = t.kb0; kb < t.kb1; ++kb, ++j) {
-        // fetch the scales two groups ahead, before waiting for this group's partial sums
-        const uint32_t r0 = load_sz(sz0, ok0, kb + 2), r1 = load_sz(sz1, ok1, kb + 2);
+        // everything that does not depend on the MMA first: the group's scale words (staged in
+        // shared memory by the producer) and its activation tables
+        const uint32_t zs = j % kSzSlots;
+        if (!mbar_wait_t(smem_u32(&bar_zfull[zs]), (j / kSzSlots) & 1u, abort_flag, DEV_TIMEOUT_EPILOGUE, w_sfull)) {
+          ok = false;
+          break;
+        }
+        const uint32_t c0 = ok0 ? s_sz[zs * 256 + lrow] : 0u;
+        const uint32_t c1 = ok1 ? s_sz[zs * 256 + 128 + lrow] : 0u;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_zempty[zs]));
         const float s0 = scale_of(c0), s1 = scale_of(c1);
         const int z0 = zero_of(c0), z1 = zero_of(c1);
-        const float* xf = xf_t + (kb - t.kb0) * BT;
-        const int* xs = xs_t + (kb - t.kb0) * BT;
+        float xfv[HT];
+        int xsv[HT];
+#pragma unroll
+        for (int q = 0; q < HT / 4; ++q) {
+          const float4 fv = *reinterpret_cast<const float4*>(xf_t + (kb - t.kb0) * BT + 4 * q);
+          const int4 sv = *reinterpret_cast<const int4*>(xs_t + (kb - t.kb0) * BT + 4 * q);
+          xfv[4 * q] = fv.x; xfv[4 * q + 1] = fv.y; xfv[4 * q + 2] = fv.z; xfv[4 * q + 3] = fv.w;
+          xsv[4 * q] = sv.x; xsv[4 * q + 1] = sv.y; xsv[4 * q + 2] = sv.z; xsv[4 * q + 3] = sv.w;
+        }
         const uint32_t pb = j & 1u;
         if (!mbar_wait_t(smem_u32(&bar_pfull[pb]), (j >> 1) & 1u, abort_flag, DEV_TIMEOUT_EPILOGUE, w_pfull)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + pb * PCOLS;
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + pb * PCOLS + tk0;
+        if constexpr (HT == 8) {
+          int p[48];   // [block][plane][8 tokens]
+          tmem_ld8x6_wait_b32(taddr, taddr + BT, taddr + 2 * BT, taddr + NB, taddr + NB + BT, taddr + NB + 2 * BT, p);
 #pragma unroll
-        for (int cb = 0; cb < BT; cb += 16) {
-          float xfv[16];
-          int xsv[16];
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const float4 fv = *reinterpret_cast<const float4*>(xf + cb + 4 * q);
-            const int4 sv = *reinterpret_cast<const int4*>(xs + cb + 4 * q);
-            xfv[4 * q] = fv.x; xfv[4 * q + 1] = fv.y; xfv[4 * q + 2] = fv.z; xfv[4 * q + 3] = fv.w;
-            xsv[4 * q] = sv.x; xsv[4 * q + 1] = sv.y; xsv[4 * q + 2] = sv.z; xsv[4 * q + 3] = sv.w;
+          for (int i = 0; i < 8; ++i) {
+            const int sum0 = p[i] + (p[8 + i] << 8) + (p[16 + i] << 16) - z0 * xsv[i];
+            const int sum1 = p[24 + i] + (p[32 + i] << 8) + (p[40 + i] << 16) - z1 * xsv[i];
+            acc0[i] = fmaf(s0 * xfv[i], static_cast<float>(sum0), acc0[i]);
+            acc1[i] = fmaf(s1 * xfv[i], static_cast<float>(sum1), acc1[i]);
           }
+        } else {
           int p0[16], p1[16], p2[16];
-          tmem_ld16x3_wait_b32(taddr + cb, taddr + BT + cb, taddr + 2 * BT + cb, p0, p1, p2);
+          tmem_ld16x3_wait_b32(taddr, taddr + BT, taddr + 2 * BT, p0, p1, p2);
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const int sum = p0[i] + (p1[i] << 8) + (p2[i] << 16) - z0 * xsv[i];
-            acc0[cb + i] = fmaf(s0 * xfv[i], static_cast<float>(sum), acc0[cb + i]);
+            acc0[i] = fmaf(s0 * xfv[i], static_cast<float>(sum), acc0[i]);
           }
-          tmem_ld16x3_wait_b32(taddr + NB + cb, taddr + NB + BT + cb, taddr + NB + 2 * BT + cb, p0, p1, p2);
+          tmem_ld16x3_wait_b32(taddr + NB, taddr + NB + BT, taddr + NB + 2 * BT, p0, p1, p2);
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const int sum = p0[i] + (p1[i] << 8) + (p2[i] << 16) - z1 * xsv[i];
-            acc1[cb + i] = fmaf(s1 * xfv[i], static_cast<float>(sum), acc1[cb + i]);
+            acc1[i] = fmaf(s1 * xfv[i], static_cast<float>(sum), acc1[i]);
           }
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bar_pempty[pb]));
-        c0 = n0w;
-        c1 = n1w;
-        n0w = r0;
-        n1w = r1;
       }
       if (!ok) break;
 
@@ -409,26 +442,27 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         // activation, rounded to fp16 as the 16-bit path stores it, then re-expressed for the
         // second GEMM: this tile's 128 columns are one of its reduction groups
         const bool n_ok = n < a.N;
-        unsigned int* amax = s_amax + buf * 32;
-        int* osum = s_osum + buf * 32;
+        unsigned int* amax = s_amax + buf * 32 + tk0;
+        int* osum = s_osum + buf * 32 + tk0;
 #pragma unroll
-        for (int i = 0; i < BT; ++i) {
+        for (int i = 0; i < HT; ++i) {
           float av = act_mul<__half>(acc0[i], acc1[i], w_on_input, col_gam[i], mimic, act_params(a));
           av = n_ok ? __half2float(__float2half_rn(av)) : 0.f;
           acc0[i] = av;
           const unsigned int m = __reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(av)));
           if (lane == 0) atomicMax(amax + i, m);
         }
-        // the four warps meet on a barrier with a bounded wait (a plain bar.sync would hang the
+        // the eight warps meet on a barrier with a bounded wait (a plain bar.sync would hang the
         // CTA if one of them had given up)
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bar_tail[2 * buf]));
         if (!mbar_wait(smem_u32(&bar_tail[2 * buf]), (iter >> 1) & 1, abort_flag, DEV_TIMEOUT_EPILOGUE)) break;
         const int kcol = (n & ~7) | plane_pos(n & 7);
         const size_t plane_stride = static_cast<size_t>(BT) * a.ld_out;
-        uint8_t* obase = a.out_q + static_cast<size_t>(t.row0 / BT) * 3 * plane_stride + kcol;
+        uint8_t* obase = a.out_q + static_cast<size_t>(t.row0 / BT) * 3 * plane_stride +
+                         static_cast<size_t>(tk0) * a.ld_out + kcol;
 #pragma unroll
-        for (int i = 0; i < BT; ++i) {
+        for (int i = 0; i < HT; ++i) {
           // group maximum in [2^ex, 2^(ex+1)): integers of magnitude below 2^19
           const unsigned int mb = amax[i];
           const int ex = static_cast<int>(mb >> 23) - 127;
@@ -450,19 +484,19 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bar_tail[2 * buf + 1]));
         if (!mbar_wait(smem_u32(&bar_tail[2 * buf + 1]), (iter >> 1) & 1, abort_flag, DEV_TIMEOUT_EPILOGUE)) break;
-        if (lrow < BT && t.n0 < a.N) {
-          const unsigned int mb = amax[lrow];
+        if (warp < 6 && lrow < BT && t.n0 < a.N) {
+          const unsigned int mb = s_amax[buf * 32 + lrow];
           const int ex = static_cast<int>(mb >> 23) - 127;
           const float f = (mb == 0u) ? 1.0f : __uint_as_float(static_cast<unsigned int>(127 + ex - 18) << 23);
           const size_t dst = static_cast<size_t>(t.n0 / 128) * a.ld_xscale + t.row0 + lrow;
           a.out_scale[dst] = f;
-          a.out_sum[dst] = osum[lrow];
+          a.out_sum[dst] = s_osum[buf * 32 + lrow];
         }
       } else {
         float* out = reinterpret_cast<float*>(a.out) + n;
         const bool first = n < a.N, second = n + kTileRows < a.N;
 #pragma unroll
-        for (int i = 0; i < BT; ++i) {
+        for (int i = 0; i < HT; ++i) {
           const int orow = col_row[i];
           if (orow >= 0) {
             const float gam = w_on_input ? 1.0f : col_gam[i];
@@ -501,7 +535,8 @@ size_t w4_stage_bytes(const GemmArgs& a) {   // one stage of the TMA ring: three
   return static_cast<size_t>(3 * a.BT) * kStageKBytes + 2 * kTileRows * kPackedRowBytes;
 }
 size_t w4_ctrl_bytes(const GemmArgs& a) {    // activation tables, barriers, per-tile tables
-  return static_cast<size_t>(2) * 2 * a.kblocks * a.BT * 4 + 1024 + 4 * 8 + 4 * 2 * 32 * 4 +
+  return static_cast<size_t>(2) * 2 * a.kblocks * a.BT * 4 + kSzSlots * 1024 + 1024 + 4 * 8 + 2 * kSzSlots * 8 +
+         4 * 2 * 32 * 4 +
          static_cast<size_t>(a.E + 1) * 4 + 64;
 }
 
