@@ -90,7 +90,8 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   const int BT = a.BT;
   const int x_bytes = BT * kStageKBytes;
   constexpr int PK_BYTES = W4 ? W_BYTES / 4 : 0;  // packed int4 rows: 32 bytes per row and stage
-  const int stage_bytes = W_BYTES + x_bytes + PK_BYTES;
+  constexpr int SZ_BYTES = W4 ? 1024 : 0;         // scale / zero word of every packed row for the stage's group
+  const int stage_bytes = W_BYTES + x_bytes + PK_BYTES + SZ_BYTES;
   const int stages = a.stages;
 
   uint8_t* ctrl_base = smem + static_cast<size_t>(stages) * stage_bytes;
@@ -159,12 +160,22 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         const uint32_t sw = smem_u32(smem + static_cast<size_t>(stage) * stage_bytes);
         const int k0 = kb * (kStageKBytes / static_cast<int>(sizeof(T)));
         if (W4) {
-          // packed rows: 64 k = 32 bytes per row, 128 rows per box, no swizzle
-          mbar_arrive_expect_tx(full, static_cast<uint32_t>(PK_BYTES + x_bytes));
+          // packed rows: 64 k = 32 bytes per row, 128 rows per box, no swizzle; beside them the
+          // scale / zero words of the rows for this stage's group (whole 128-row blocks: weight
+          // rows per expert are a multiple of 128), so that the conversion never waits on a
+          // global load
+          const int second0 = (MODE == 0) ? a.up_row_off + t.n0 : t.n0 + kTileRows;
+          const bool has_second = (MODE == 0 || ORIENT == 1);
+          const bool first_in = t.n0 < a.w_rows, second_in = has_second && second0 < a.w_rows;
+          mbar_arrive_expect_tx(full, static_cast<uint32_t>(PK_BYTES + x_bytes) + (first_in ? 512u : 0u) +
+                                          (second_in ? 512u : 0u));
           const uint32_t spk = sw + W_BYTES + x_bytes;
           tma_load_3d(spk, &tm_w, full, kb * 32, t.n0, t.e);
-          if (MODE == 0) tma_load_3d(spk + kTileRows * 32, &tm_w, full, kb * 32, a.up_row_off + t.n0, t.e);
-          else if (ORIENT == 1) tma_load_3d(spk + kTileRows * 32, &tm_w, full, kb * 32, t.n0 + kTileRows, t.e);
+          if (has_second) tma_load_3d(spk + kTileRows * 32, &tm_w, full, kb * 32, second0, t.e);
+          const uint32_t* szg = reinterpret_cast<const uint32_t*>(a.w_sz) +
+                                (static_cast<size_t>(t.e) * ((a.K + 127) / 128) + (kb >> 1)) * a.w_rows;
+          if (first_in) bulk_copy_g2s(spk + PK_BYTES, szg + t.n0, 512, full);
+          if (second_in) bulk_copy_g2s(spk + PK_BYTES + 512, szg + second0, 512, full);
         } else {
           mbar_arrive_expect_tx(full, static_cast<uint32_t>(stage_bytes));
           tma_load_3d(sw, &tm_w, full, k0, t.n0, t.e);
@@ -247,8 +258,6 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     const int dt = threadIdx.x - 6 * 32;                          // 0..255
     const int row = (UNITS_PER_THREAD == 2) ? dt : (dt >> 1);     // packed row this thread converts
     const int half0 = (UNITS_PER_THREAD == 2) ? 0 : (dt & 1);
-    const uint32_t* sz = reinterpret_cast<const uint32_t*>(a.w_sz);
-    const int groups = (a.K + 127) / 128;
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
@@ -257,14 +266,15 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       // output row of this packed row inside the expert (gate rows first, then the up rows)
       const int n = (row < kTileRows || MODE == 1) ? t.n0 + row : a.up_row_off + t.n0 + (row - kTileRows);
       const bool n_ok = n < a.w_rows;
-      const uint32_t* szrow = sz + static_cast<size_t>(t.e) * groups * a.w_rows + n;
       for (int kb = t.kb0; kb < t.kb1; ++kb) {
-        uint32_t szv = 0;
-        if (n_ok) szv = __ldg(szrow + static_cast<size_t>(kb >> 1) * a.w_rows);
         if (!mbar_wait(smem_u32(&bar_full[stage]), phase, abort_flag, DEV_TIMEOUT_MMA)) {
           ok = false;
           break;
         }
+        // scale (low half) and 1024 + zero (high half), staged beside the packed rows
+        const uint32_t szv = n_ok ? *reinterpret_cast<const uint32_t*>(smem + static_cast<size_t>(stage) * stage_bytes +
+                                                                         W_BYTES + x_bytes + PK_BYTES + row * 4)
+                                  : 0u;
         const __half2 sc = __half2half2(__ushort_as_half(static_cast<unsigned short>(szv & 0xFFFFu)));
         const __half2 zp = __half2half2(__ushort_as_half(static_cast<unsigned short>(szv >> 16)));
         uint8_t* sbase = smem + static_cast<size_t>(stage) * stage_bytes;
@@ -449,7 +459,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 
 static size_t stage_bytes_of(const GemmArgs& a) {
   const size_t w = (a.orient == 1) ? 2 * kTileBytes : static_cast<size_t>(a.mode == 0 ? 2 : 1) * kTileBytes;
-  const size_t packed = (a.wmode == B200MOE_W_INT4_AWQ) ? w / 4 : 0;
+  const size_t packed = (a.wmode == B200MOE_W_INT4_AWQ) ? w / 4 + 1024 : 0;   // + scale words of the stage
   return w + packed + static_cast<size_t>(a.BT) * kStageKBytes;
 }
 
