@@ -240,8 +240,8 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
           tc_mma_i8_ts(d0, a0 + 8 * k, dx + 2 * k, idesc, k > 0 ? 1u : 0u);
           tc_mma_i8_ts(d0 + NB, a0 + 32 + 8 * k, dx + 2 * k, idesc, k > 0 ? 1u : 0u);
         }
-        tc_commit(smem_u32(&bar_empty[stage]));
-        tc_commit(smem_u32(&bar_oempty[ost]));
+        // one commit per group: the first promotion warp passes the news on to the producer
+        // (ring stage free) and to the conversion warps (operand stage free)
         tc_commit(smem_u32(&bar_pfull[pb]));
         if (++stage == stages) {
           stage = 0;
@@ -406,6 +406,10 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
           break;
         }
         tc_fence_after();
+        if (warp == 2 && lane == 0) {
+          mbar_arrive(smem_u32(&bar_empty[j % static_cast<uint32_t>(stages)]));
+          mbar_arrive(smem_u32(&bar_oempty[j % NO]));
+        }
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + pb * PCOLS + tk0;
         if constexpr (HT == 8) {
           int p[48];   // [block][plane][8 tokens]
