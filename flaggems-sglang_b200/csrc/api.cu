@@ -92,12 +92,14 @@ void prof_mark(int slot, int mark, cudaStream_t st) {
 
 struct Layout {
   int BT, cap, P;
+  bool quant_once; // FP8: quantise each token once, then gather the quantised rows (many pairs per token)
+  bool pair_rows; // the down projection stores one 16-bit row per pair, the output conversion sums them
   bool w4p;       // int4 decode path: integer MMAs on three-plane int8 activations
   int out_rows;   // rows of the fp32 output buffer: tokens, or pairs when nothing is combined
   int orient;     // GEMM tile orientation that goes with BT
   int act_bytes;  // bytes per activation element fed to the GEMMs
   size_t meta, blk_off, sorted_ids, expert_ids, num_post, row_gamma, xs, xs_scale, xs_sum, a2, a2_scale,
-      a2_sum, out32, route_w, route_ids, total;
+      a2_sum, out32, pairs, pair_valid, xq_tok, xq_scale, route_w, route_ids, total;
 };
 
 int pick_bt(const b200moe_cfg* c) {
@@ -147,6 +149,8 @@ int check_cfg(const b200moe_cfg* c) {
   return B200MOE_OK;
 }
 
+int query_sms(const b200moe_cfg* c);
+
 int make_layout(const b200moe_cfg* c, Layout* L) {
   L->BT = pick_bt(c);
   // a block of 128 tokens sits on the M side of the MMA; smaller (and 256-token) blocks on the N side
@@ -187,7 +191,19 @@ int make_layout(const b200moe_cfg* c, Layout* L) {
   L->a2_scale = take(tables ? static_cast<size_t>(cap) * (c->I / 128) * 4 : 0);
   L->a2_sum = take(L->w4p ? static_cast<size_t>(cap) * (c->I / 128) * 4 : 0);
   L->out_rows = (c->flags & B200MOE_FLAG_NO_COMBINE) ? L->P : c->M;   // one fp32 row per pair when nothing is summed
-  L->out32 = take(static_cast<size_t>(L->out_rows > 0 ? L->out_rows : 1) * c->H * 4);
+  // Many pairs (FP8, 128-token blocks): fp32 atomics into the combine buffer would bound the down
+  // projection's tail, and its tiles fill the GPU without splitting the reduction; store 16-bit pair
+  // rows instead.  The combine buffer shrinks to the pairs' validity bytes.
+  L->pair_rows = fp8 && L->BT == 128 && !(c->flags & B200MOE_FLAG_NO_COMBINE) &&
+                 (static_cast<long long>(L->P) / L->BT) * ((c->H + 255) / 256) >= 2LL * query_sms(c);
+  L->out32 = take(L->pair_rows ? 16 : static_cast<size_t>(L->out_rows > 0 ? L->out_rows : 1) * c->H * 4);
+  // Quantising inside the gather repeats the work topk times; beyond a few thousand pairs it pays to
+  // quantise the M token rows once and gather bytes.
+  L->quant_once = fp8 && L->P >= 2048 && c->topk > 1;
+  L->xq_tok = take(L->quant_once ? static_cast<size_t>(c->M) * c->H : 0);
+  L->xq_scale = take(L->quant_once ? static_cast<size_t>(c->M) * (c->H / 128) * 4 : 0);
+  L->pairs = take(L->pair_rows ? static_cast<size_t>(L->P) * c->H * 2 : 0);
+  L->pair_valid = take(L->pair_rows ? align_up(static_cast<size_t>(L->P), 16) : 0);
   L->route_w = take(static_cast<size_t>(L->P > 0 ? L->P : 1) * 4);    // router output when the call starts from logits
   L->route_ids = take(static_cast<size_t>(L->P > 0 ? L->P : 1) * 4);
   L->total = off;
@@ -259,9 +275,21 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
 
   if (fp8) {
     if (quant == nullptr || quant->w1_scale == nullptr || quant->w2_scale == nullptr) return B200MOE_ERR_BAD_ARG;
-    rc = launch_group_quant_fp8(x, c->dtype, xs, reinterpret_cast<float*>(ws + L.xs_scale), sorted_ids, meta,
-                                L.P, c->topk, L.cap, c->H, 1, L.cap, out32, static_cast<size_t>(L.out_rows) * c->H * 4,
-                                sms, st, pdl);
+    // cleared alongside: the fp32 combine buffer, or the pairs' validity bytes when rows are stored per pair
+    void* zero = L.pair_rows ? static_cast<void*>(ws + L.pair_valid) : static_cast<void*>(out32);
+    const size_t zero_bytes = L.pair_rows ? align_up(static_cast<size_t>(L.P), 16)
+                                          : static_cast<size_t>(L.out_rows) * c->H * 4;
+    if (L.quant_once) {
+      float* tok_scale = reinterpret_cast<float*>(ws + L.xq_scale);
+      rc = launch_group_quant_fp8(x, c->dtype, ws + L.xq_tok, tok_scale, nullptr, nullptr, L.P, c->topk, c->M, c->H, 0,
+                                  0, zero, zero_bytes, sms, st, pdl);
+      if (rc != B200MOE_OK) return rc;
+      rc = launch_gather_rows(ws + L.xq_tok, xs, sorted_ids, meta, L.P, c->topk, c->H, L.cap, zero, 0, sms, st, pdl,
+                              tok_scale, reinterpret_cast<float*>(ws + L.xs_scale), c->H / 128, L.cap);
+    } else {
+      rc = launch_group_quant_fp8(x, c->dtype, xs, reinterpret_cast<float*>(ws + L.xs_scale), sorted_ids, meta,
+                                  L.P, c->topk, L.cap, c->H, 1, L.cap, zero, zero_bytes, sms, st, pdl);
+    }
   } else if (L.w4p) {
     rc = launch_group_split_i8(x, reinterpret_cast<uint8_t*>(xs), reinterpret_cast<float*>(ws + L.xs_scale),
                                reinterpret_cast<int*>(ws + L.xs_sum), sorted_ids, meta, L.P, c->topk, L.cap, c->H,
@@ -348,6 +376,11 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
     g2.out_q = nullptr;
     g2.out_scale = nullptr;
     g2.flags &= ~B200MOE_FLAG_MIMIC_ROUNDING;
+    if (L.pair_rows) {
+      g2.out_pairs = ws + L.pairs;
+      g2.pair_valid = ws + L.pair_valid;
+      g2.flags |= B200MOE_FLAG_NO_SPLIT_K;
+    }
   }
   if (w4p) {
     g2.x_scale = reinterpret_cast<float*>(ws + L.a2_scale);
@@ -401,8 +434,12 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
     prof_mark(slot, 4, st);
     if (rc != B200MOE_OK) return rc;
   }
-  rc = launch_finalize(out32, out, c->dtype, static_cast<size_t>(L.out_rows) * c->H,
-                       (c->flags & B200MOE_FLAG_NO_COMBINE) ? 1.0f : c->routed_scaling, sms, st, pdl);
+  if (L.pair_rows)
+    rc = launch_finalize_pairs(ws + L.pairs, ws + L.pair_valid, out, c->dtype, c->M, c->topk, c->H,
+                               c->routed_scaling, sms, st, pdl);
+  else
+    rc = launch_finalize(out32, out, c->dtype, static_cast<size_t>(L.out_rows) * c->H,
+                         (c->flags & B200MOE_FLAG_NO_COMBINE) ? 1.0f : c->routed_scaling, sms, st, pdl);
   prof_mark(slot, 5, st);
   return rc;
 }

@@ -50,6 +50,12 @@ struct GemmArgs {
   // int4 decode path (integer MMAs): activations are three int8 planes per token block
   // ([block][plane][BT rows][K], rows of one block consecutive) + per (128-k group, row) a
   // power-of-two scale (x_scale / out_scale, [K/128][ld_xscale]) and the sum of the integers
+  // mode 1, optional: instead of adding into the fp32 combine buffer, store each (token, choice)
+  // pair's weighted row in the 16-bit type at out_pairs[slot][N] and mark pair_valid[slot]; the
+  // output conversion then sums a token's rows.  Plain 16-byte stores instead of fp32 atomics,
+  // which bound the tail once M * topk * N is large.  Requires an unsplit reduction.
+  void* out_pairs;
+  uint8_t* pair_valid;
   const int* x_sum;       // [K/128][ld_xscale]
   int* out_sum;           // mode 0: [N/128][ld_xscale]; planes go to out_q with row stride ld_out
 };

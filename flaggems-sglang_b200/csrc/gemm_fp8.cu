@@ -509,7 +509,8 @@ moe_gemm_fp8_tokm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
       for (int cidx = lane; cidx < BT; cidx += 32) {
         const int slot = a.sorted_ids[t.row0 + cidx];
         const bool valid = slot >= 0 && slot < a.P;
-        s_col_row[buf * 128 + cidx] = valid ? (MODE == 1 ? slot / a.topk : slot) : -1;
+        // mode 1: output row = token, or the pair's own slot when rows are stored per pair
+        s_col_row[buf * 128 + cidx] = valid ? ((MODE == 1 && a.out_pairs == nullptr) ? slot / a.topk : slot) : -1;
         s_col_gam[buf * 128 + cidx] = valid ? a.row_gamma[t.row0 + cidx] : 0.f;
       }
       const int nb0 = t.n0 / 128, nb1 = (second_off + t.n0) / 128;
@@ -620,6 +621,31 @@ moe_gemm_fp8_tokm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
         uint4* dst = reinterpret_cast<uint4*>(a.out_q + static_cast<size_t>(r) * a.ld_out + t.n0 + 64 * grp);
 #pragma unroll
         for (int q = 0; q < 4; ++q) dst[q] = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+      } else if (orow >= 0 && a.out_pairs != nullptr) {
+        // the pair's row, weighted and rounded to the 16-bit type: 128 contiguous columns per thread
+        const float scale = w_on_input ? 1.0f : gam;
+        if (t.n0 + 128 * grp < a.N) {
+          uint16_t* prow = reinterpret_cast<uint16_t*>(a.out_pairs) + static_cast<size_t>(orow) * a.N + t.n0 + 128 * grp;
+          const bool bf = a.dtype == B200MOE_DTYPE_BF16;
+#pragma unroll
+          for (int q = 0; q < 16; ++q) {
+            const float* src = (q < 8) ? accA + 8 * q : accB + 8 * (q - 8);
+            uint32_t w[4];
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+              const float lo = src[2 * b] * scale, hi = src[2 * b + 1] * scale;
+              if (bf) {
+                __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+                w[b] = *reinterpret_cast<uint32_t*>(&v);
+              } else {
+                __half2 v = __floats2half2_rn(lo, hi);
+                w[b] = *reinterpret_cast<uint32_t*>(&v);
+              }
+            }
+            *reinterpret_cast<uint4*>(prow + 8 * q) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+        if (t.n0 == 0 && grp == 0) a.pair_valid[orow] = 1;
       } else if (orow >= 0) {
         const float scale = w_on_input ? 1.0f : gam;
         float* out = reinterpret_cast<float*>(a.out) + static_cast<size_t>(orow) * a.ld_out + t.n0 + 128 * grp;

@@ -10,16 +10,29 @@ namespace {
 // One thread per 16-byte chunk of a padded row (grid-stride), so that a handful of rows at
 // decode sizes still spreads over many threads.  Rows beyond meta[1] are left alone, padding
 // rows are zero-filled.  The same launch clears the fp32 combine buffer (`zero`, `zero_chunks`).
+// With sc_src: the rows are already quantised (one byte per element) and each has G group scales
+// [tokens][G]; they are re-laid group-major for the GEMMs, sc_dst [G][ld].
 __global__ void __launch_bounds__(256)
 gather_rows_kernel(const uint4* __restrict__ x, uint4* __restrict__ xs, const int* __restrict__ sorted_ids,
                    const int* __restrict__ meta, int P, int topk, int chunks_per_row, int cap,
-                   uint4* __restrict__ zero, long long zero_chunks) {
+                   uint4* __restrict__ zero, long long zero_chunks, const float* __restrict__ sc_src,
+                   float* __restrict__ sc_dst, int G, int ld) {
   griddep_wait();
   griddep_launch_dependents();
   const int rows = min(meta[1], cap);
   const long long n_copy = static_cast<long long>(rows) * chunks_per_row;
   const long long total = n_copy + zero_chunks;
   const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  if (sc_src != nullptr) {
+    const long long n_sc = static_cast<long long>(rows) * G;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_sc; i += stride) {
+      const int g = static_cast<int>(i / rows);
+      const int r = static_cast<int>(i - static_cast<long long>(g) * rows);
+      const int slot = sorted_ids[r];
+      sc_dst[static_cast<size_t>(g) * ld + r] =
+          (slot >= 0 && slot < P) ? __ldg(sc_src + static_cast<size_t>(slot / topk) * G + g) : 1.0f;
+    }
+  }
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
     if (i < n_copy) {
       const int r = static_cast<int>(i / chunks_per_row);
@@ -51,9 +64,11 @@ __device__ __forceinline__ void load4<__half>(const __half* p, float (&v)[4]) {
   v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
 }
 
-// One warp per (row, 128-wide group): amax by shuffles, scale = max(amax, eps)/448,
-// q = rne_satfinite(x / scale) with an IEEE divide so that the bits match a CPU
-// restatement.  sorted_ids == nullptr: rows map to themselves.
+// One warp per (row, run of up to eight 128-wide groups): the loads of the run are issued
+// together (one 8-byte load per lane and group in flight is too little to cover the memory
+// latency), then per group amax by shuffles, scale = max(amax, eps)/448,
+// q = rne_satfinite(x / scale) with an IEEE divide so that the bits match a CPU restatement.
+// sorted_ids == nullptr: rows map to themselves.
 // scale_t != 0: scales stored [K/128][ld_scale] (group-major) instead of [rows][K/128].
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -67,14 +82,17 @@ group_quant_fp8_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* 
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < zero_chunks;
        i += static_cast<long long>(gridDim.x) * blockDim.x)
     zero[i] = make_uint4(0, 0, 0, 0);
+  constexpr int RUN = 8;
   const int groups = K >> 7;
+  const int runs = (groups + RUN - 1) / RUN;
   const int lane = threadIdx.x & 31;
   const int rows = (meta != nullptr) ? min(meta[1], n_rows_static) : n_rows_static;
-  const long long total = static_cast<long long>(rows) * groups;
+  const long long total = static_cast<long long>(rows) * runs;
   const int warps = (gridDim.x * blockDim.x) >> 5;
   for (long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; w < total;
        w += warps) {
-    const int r = static_cast<int>(w / groups), g = static_cast<int>(w - static_cast<long long>(r) * groups);
+    const int r = static_cast<int>(w / runs);
+    const int g0 = static_cast<int>(w - static_cast<long long>(r) * runs) * RUN;
     int src_row = r;
     bool pad = false;
     if (sorted_ids != nullptr) {
@@ -82,22 +100,31 @@ group_quant_fp8_kernel(const T* __restrict__ x, uint8_t* __restrict__ q, float* 
       pad = (slot < 0 || slot >= P);
       src_row = pad ? 0 : slot / topk;
     }
-    float v[4] = {0.f, 0.f, 0.f, 0.f};
-    if (!pad) load4<T>(x + static_cast<size_t>(src_row) * K + g * 128 + lane * 4, v);
-    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    float v[RUN][4];
 #pragma unroll
-    for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
-    const float s = __fdiv_rn(fmaxf(amax, 1e-10f), 448.0f);
-    uint32_t packed = 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      __nv_fp8_storage_t b = __nv_cvt_float_to_fp8(__fdiv_rn(v[i], s), __NV_SATFINITE, __NV_E4M3);
-      packed |= static_cast<uint32_t>(b) << (8 * i);
+    for (int u = 0; u < RUN; ++u) {
+      v[u][0] = v[u][1] = v[u][2] = v[u][3] = 0.f;
+      if (!pad && g0 + u < groups) load4<T>(x + static_cast<size_t>(src_row) * K + (g0 + u) * 128 + lane * 4, v[u]);
     }
-    *reinterpret_cast<uint32_t*>(q + static_cast<size_t>(r) * K + g * 128 + lane * 4) = packed;
-    if (lane == 0) {
-      if (scale_t) scales[static_cast<size_t>(g) * ld_scale + r] = s;
-      else scales[static_cast<size_t>(r) * groups + g] = s;
+#pragma unroll
+    for (int u = 0; u < RUN; ++u) {
+      const int g = g0 + u;
+      if (g >= groups) break;
+      float amax = fmaxf(fmaxf(fabsf(v[u][0]), fabsf(v[u][1])), fmaxf(fabsf(v[u][2]), fabsf(v[u][3])));
+      // non-negative floats order like their bit patterns: one redux instead of five shuffles
+      amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(amax)));
+      const float s = __fdiv_rn(fmaxf(amax, 1e-10f), 448.0f);
+      uint32_t packed = 0;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        __nv_fp8_storage_t b = __nv_cvt_float_to_fp8(__fdiv_rn(v[u][i], s), __NV_SATFINITE, __NV_E4M3);
+        packed |= static_cast<uint32_t>(b) << (8 * i);
+      }
+      *reinterpret_cast<uint32_t*>(q + static_cast<size_t>(r) * K + g * 128 + lane * 4) = packed;
+      if (lane == 0) {
+        if (scale_t) scales[static_cast<size_t>(g) * ld_scale + r] = s;
+        else scales[static_cast<size_t>(r) * groups + g] = s;
+      }
     }
   }
 }
@@ -177,11 +204,58 @@ finalize_kernel(const float4* __restrict__ acc, T* __restrict__ out, size_t n4, 
   }
 }
 
+// One thread per (token, run of 8 columns): fp32 sum of the token's valid pair rows.
+template <typename T>
+__global__ void __launch_bounds__(256)
+finalize_pairs_kernel(const uint4* __restrict__ pairs, const uint8_t* __restrict__ pair_valid, uint4* __restrict__ out,
+                      int M, int topk, int chunks_per_row, float scale) {
+  griddep_wait();
+  griddep_launch_dependents();
+  const long long total = static_cast<long long>(M) * chunks_per_row;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int t = static_cast<int>(i / chunks_per_row);
+    const int c = static_cast<int>(i - static_cast<long long>(t) * chunks_per_row);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < topk; ++j) {
+      const size_t slot = static_cast<size_t>(t) * topk + j;
+      if (!pair_valid[slot]) continue;
+      const uint4 v = __ldg(pairs + slot * chunks_per_row + c);
+      const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += to_f32<T>(e[k]);
+    }
+    T o[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) o[k] = from_f32<T>(acc[k] * scale);
+    out[i] = *reinterpret_cast<uint4*>(o);
+  }
+}
+
 }  // namespace
+
+int launch_finalize_pairs(const void* pairs, const uint8_t* pair_valid, void* out, int dtype, int M, int topk,
+                          int H, float scale, int num_sms, cudaStream_t stream, bool pdl) {
+  if (H % 8 != 0) return B200MOE_ERR_UNSUPPORTED;
+  const long long total = static_cast<long long>(M) * (H / 8);
+  long long ctas = (total + 255) / 256;
+  if (ctas > static_cast<long long>(num_sms) * 16) ctas = static_cast<long long>(num_sms) * 16;
+  if (ctas < 1) ctas = 1;
+  cudaError_t err;
+  if (dtype == B200MOE_DTYPE_BF16)
+    err = launch_kernel(finalize_pairs_kernel<__nv_bfloat16>, dim3(static_cast<unsigned>(ctas)), dim3(256), 0, stream,
+                        pdl, reinterpret_cast<const uint4*>(pairs), pair_valid, reinterpret_cast<uint4*>(out), M, topk,
+                        H / 8, scale);
+  else
+    err = launch_kernel(finalize_pairs_kernel<__half>, dim3(static_cast<unsigned>(ctas)), dim3(256), 0, stream, pdl,
+                        reinterpret_cast<const uint4*>(pairs), pair_valid, reinterpret_cast<uint4*>(out), M, topk, H / 8,
+                        scale);
+  return err == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
+}
 
 int launch_gather_rows(const void* x, void* xs, const int* sorted_ids, const int* meta, int P, int topk,
                        int row_bytes, int cap, void* zero, size_t zero_bytes, int num_sms,
-                       cudaStream_t stream, bool pdl) {
+                       cudaStream_t stream, bool pdl, const float* sc_src, float* sc_dst, int G, int ld) {
   if (row_bytes % 16 != 0 || zero_bytes % 16 != 0) return B200MOE_ERR_UNSUPPORTED;
   const long long work = static_cast<long long>(cap) * (row_bytes / 16) + static_cast<long long>(zero_bytes / 16);
   long long ctas = (work + 255) / 256;
@@ -190,7 +264,7 @@ int launch_gather_rows(const void* x, void* xs, const int* sorted_ids, const int
   cudaError_t err = launch_kernel(gather_rows_kernel, dim3(static_cast<unsigned>(ctas)), dim3(256), 0, stream, pdl,
                                   reinterpret_cast<const uint4*>(x), reinterpret_cast<uint4*>(xs), sorted_ids, meta,
                                   P, topk, row_bytes / 16, cap, reinterpret_cast<uint4*>(zero),
-                                  static_cast<long long>(zero_bytes / 16));
+                                  static_cast<long long>(zero_bytes / 16), sc_src, sc_dst, G, ld);
   return err == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
 }
 
@@ -198,7 +272,7 @@ int launch_group_quant_fp8(const void* x, int dtype, void* q, float* scales, con
                            const int* meta, int P, int topk, int rows, int K, int scale_t, int ld_scale,
                            void* zero, size_t zero_bytes, int num_sms, cudaStream_t stream, bool pdl) {
   if (K % 128 != 0 || zero_bytes % 16 != 0) return B200MOE_ERR_UNSUPPORTED;
-  long long warps = static_cast<long long>(rows) * (K / 128);
+  long long warps = static_cast<long long>(rows) * ((K / 128 + 7) / 8);
   long long ctas = (warps + 7) / 8;
   if (ctas > num_sms * 16) ctas = num_sms * 16;
   if (ctas < 1) ctas = 1;

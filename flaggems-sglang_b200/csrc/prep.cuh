@@ -5,10 +5,13 @@
 namespace b200moe {
 
 // xs[r] = x[sorted_ids[r] / topk] for r < meta[1]; padding rows zero-filled.  Also clears
-// `zero_bytes` bytes at `zero` (the fp32 combine buffer) in the same launch.
+// `zero_bytes` bytes at `zero` (the fp32 combine buffer) in the same launch.  With sc_src
+// ([tokens][G] group scales of already quantised rows) the scales follow their rows into the
+// group-major table sc_dst [G][ld].
 int launch_gather_rows(const void* x, void* xs, const int* sorted_ids, const int* meta, int P, int topk,
                        int row_bytes, int cap, void* zero, size_t zero_bytes, int num_sms,
-                       cudaStream_t stream, bool pdl);
+                       cudaStream_t stream, bool pdl, const float* sc_src = nullptr, float* sc_dst = nullptr,
+                       int G = 0, int ld = 0);
 
 // Per-token-group (1x128) FP8 quantisation, optionally gathering rows through
 // sorted_ids like launch_gather_rows.  scale_t: store scales group-major.
@@ -28,5 +31,9 @@ int launch_group_split_i8(const void* x, uint8_t* planes, float* scales, int* su
 // out[i] = cast(acc[i] * scale)
 int launch_finalize(const float* acc, void* out, int dtype, size_t n, float scale, int num_sms,
                     cudaStream_t stream, bool pdl);
+
+// out[t][c] = cast(scale * sum_j pairs[t * topk + j][c]) over the pairs marked valid.
+int launch_finalize_pairs(const void* pairs, const uint8_t* pair_valid, void* out, int dtype, int M, int topk,
+                          int H, float scale, int num_sms, cudaStream_t stream, bool pdl);
 
 }  // namespace b200moe

@@ -77,3 +77,26 @@ def test_fp8_through_reference_signature(cuda_device):
     with pytest.raises(AssertionError):
         flaggems_sglang.triton_kernel_fused_experts(x.to(d), w13q.to(d), w2q.to(d), rd, gi, si, use_fp8_w8a8=True,
                                                     w1_scale=s13.to(d), w2_scale=s2.to(d), block_shape=[64, 64])
+
+
+@pytest.mark.parametrize("masked", [False, True])
+def test_fp8_many_pairs_stored_per_pair(cuda_device, masked):
+    """Enough (token, choice) pairs that the down projection stores 16-bit rows per pair and the
+    output conversion sums them (instead of fp32 atomics); with an expert map, masked pairs must
+    contribute nothing."""
+    import flaggems_sglang_b200 as F
+    h, i, e, k, m = 2048, 256, 16, 8, 640           # 5120 pairs / 128 * 8 column tiles >= 2 * SMs
+    x, tw, ids, w13q, s13, w2q, s2 = _fp8_case(h, i, e, k, m, seed=77)
+    d = cuda_device
+    kw = dict(use_fp8_w8a8=True, w13_scale=s13.to(d), w2_scale=s2.to(d), routed_scaling_factor=1.5)
+    if masked:
+        emap = torch.arange(e, dtype=torch.int32)
+        emap[1::3] = -1                              # every third expert lives elsewhere
+        out = F.fused_experts(x.to(d), w13q.to(d), w2q.to(d), tw.to(d), ids.to(d), expert_map=emap.to(d), **kw)
+        tw_ref = torch.where(emap[ids.long()] >= 0, tw, torch.zeros_like(tw))
+    else:
+        out = F.fused_experts(x.to(d), w13q.to(d), w2q.to(d), tw.to(d), ids.to(d), **kw)
+        tw_ref = tw
+    F.check_status()
+    ref = OM.fused_experts_fp8(x, w13q, w2q, s13, s2, tw_ref, ids)
+    assert_parity(out, (ref.float() * 1.5).to(ref.dtype), what=f"fp8 pair rows masked={masked}")
