@@ -344,6 +344,7 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 // activations of its thread in group 0 plus the 64 of its thread in group 1: the two partial
 // maxima meet in shared memory, no shuffles.
 constexpr int kThreadsFp8TokM = 7 * 32 + 128;
+constexpr int kPairStageBytes = 2 * 128 * 144;   // staging of 16-bit pair rows: two groups x 128 rows x (128 + 16) bytes
 
 #ifdef B200MOE_STALL_STATS
 __device__ unsigned long long g_stall_fp8[16];
@@ -366,16 +367,20 @@ moe_gemm_fp8_tokm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
   constexpr int PCOLS = 256;
   const int stages = a.stages;
 
+  const int KBS = a.kblocks;   // reduction slices of a whole row: size of the per-tile scale tables
   uint8_t* ctrl_base = smem + static_cast<size_t>(stages) * STAGE_BYTES;
-  float* s_xs = reinterpret_cast<float*>(ctrl_base);                    // [2][kMaxKB][128] activation scales
-  float* s_ws = s_xs + 2 * kMaxKB * BT;                                 // [2][2][kMaxKB] weight scales
-  uint64_t* bar_full = reinterpret_cast<uint64_t*>(s_ws + 2 * 2 * kMaxKB);
+  float* s_xs = reinterpret_cast<float*>(ctrl_base);                    // [2][KBS][128] activation scales
+  float* s_ws = s_xs + 2 * KBS * BT;                                    // [2][2][KBS] weight scales
+  // mode 1 with rows stored per pair: staging for coalesced stores, [2 groups][128 rows][144 bytes]
+  uint8_t* s_stage = reinterpret_cast<uint8_t*>(s_ws + 2 * 2 * KBS);
+  uint64_t* bar_full = reinterpret_cast<uint64_t*>(s_stage + ((MODE == 1 && a.out_pairs != nullptr) ? kPairStageBytes : 0));
   uint64_t* bar_empty = bar_full + stages;
   uint64_t* bar_pfull = bar_empty + stages;
   uint64_t* bar_pempty = bar_pfull + 2;
   uint64_t* bar_sfull = bar_pempty + 2;
   uint64_t* bar_sempty = bar_sfull + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_sempty + 2);
+  uint64_t* bar_meet = bar_sempty + 2;          // [2] one per promotion group: meetings around the staged stores
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_meet + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* s_col_row = reinterpret_cast<int*>(tmem_slot + 4);               // [2][128] output row of each token
   float* s_col_gam = reinterpret_cast<float*>(s_col_row + 2 * 128);     // [2][128]
@@ -395,6 +400,7 @@ moe_gemm_fp8_tokm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
       mbar_init(smem_u32(&bar_pempty[s]), 8);
       mbar_init(smem_u32(&bar_sfull[s]), 1);
       mbar_init(smem_u32(&bar_sempty[s]), 8);
+      mbar_init(smem_u32(&bar_meet[s]), 4);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -517,17 +523,17 @@ moe_gemm_fp8_tokm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
       const float* ws0 = a.w_scale + (static_cast<size_t>(t.e) * a.w_scale_rows + nb0) * kb_total + t.kb0;
       const float* ws1 = a.w_scale + (static_cast<size_t>(t.e) * a.w_scale_rows + nb1) * kb_total + t.kb0;
       const bool second_ok = nb1 < a.w_scale_rows;
-      float* ws_t = s_ws + buf * 2 * kMaxKB;
+      float* ws_t = s_ws + buf * 2 * KBS;
       for (int i = lane; i < nkb; i += 32) {
         ws_t[i] = __ldg(ws0 + i);
-        ws_t[kMaxKB + i] = second_ok ? __ldg(ws1 + i) : 0.f;
+        ws_t[KBS + i] = second_ok ? __ldg(ws1 + i) : 0.f;
       }
       __syncwarp();
       const uint32_t sfull = smem_u32(&bar_sfull[buf]);
       if (lane == 0) mbar_arrive_expect_tx(sfull, static_cast<uint32_t>(nkb * BT * 4));
       __syncwarp();
       for (int i = lane; i < nkb; i += 32)
-        bulk_copy_g2s(smem_u32(s_xs + (buf * kMaxKB + i) * BT),
+        bulk_copy_g2s(smem_u32(s_xs + (buf * KBS + i) * BT),
                       a.x_scale + static_cast<size_t>(t.kb0 + i) * a.ld_xscale + t.row0, BT * 4, sfull);
     }
   } else if (active && warp >= 2 && warp != 6) {
@@ -540,6 +546,7 @@ moe_gemm_fp8_tokm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
     const uint32_t colA = (MODE == 0) ? 64u * grp : 128u * grp;
     const uint32_t colB = (MODE == 0) ? 128u + 64u * grp : 128u * grp + 64u;
     uint32_t j = 0;
+    uint32_t meet_phase = 0;
     int iter = 0;
     bool ok = true;
     unsigned long long w_pfull = 0, w_sfull = 0, t_tail = 0;
@@ -547,8 +554,8 @@ moe_gemm_fp8_tokm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
     for (int tile = blockIdx.x; ok && tile < c.total; tile += c.grid_eff, ++iter) {
       const TileCoord t = decode_tile(tile, c, s_blk_off, a.E, BT, a.num_nt, a.kblocks, kTileN);
       const int buf = iter & 1;
-      const float* xs_t = s_xs + buf * kMaxKB * BT;
-      const float* ws_t = s_ws + buf * 2 * kMaxKB;
+      const float* xs_t = s_xs + buf * KBS * BT;
+      const float* ws_t = s_ws + buf * 2 * KBS;
       if (!mbar_wait_t(smem_u32(&bar_sfull[buf]), (iter >> 1) & 1, abort_flag, DEV_TIMEOUT_EPILOGUE, w_sfull)) break;
       const int orow = s_col_row[buf * 128 + lrow];
       const float gam = s_col_gam[buf * 128 + lrow];
@@ -563,8 +570,8 @@ moe_gemm_fp8_tokm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
         const float sx = xs_t[(kb - t.kb0) * BT + lrow];
         // mode 0: A columns belong to the first weight block, B columns to the second;
         // mode 1: group g works entirely inside weight block g
-        const float fA = sx * ws_t[(MODE == 0 ? 0 : grp * kMaxKB) + kb - t.kb0];
-        const float fB = sx * ws_t[(MODE == 0 ? kMaxKB : grp * kMaxKB) + kb - t.kb0];
+        const float fA = sx * ws_t[(MODE == 0 ? 0 : grp * KBS) + kb - t.kb0];
+        const float fB = sx * ws_t[(MODE == 0 ? KBS : grp * KBS) + kb - t.kb0];
         const uint32_t pb = j & 1u;
         if (!mbar_wait_t(smem_u32(&bar_pfull[pb]), (j >> 1) & 1u, abort_flag, DEV_TIMEOUT_EPILOGUE, w_pfull)) {
           ok = false;
@@ -621,19 +628,32 @@ moe_gemm_fp8_tokm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
         uint4* dst = reinterpret_cast<uint4*>(a.out_q + static_cast<size_t>(r) * a.ld_out + t.n0 + 64 * grp);
 #pragma unroll
         for (int q = 0; q < 4; ++q) dst[q] = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
-      } else if (orow >= 0 && a.out_pairs != nullptr) {
-        // the pair's row, weighted and rounded to the 16-bit type: 128 contiguous columns per thread
+      } else if (a.out_pairs != nullptr) {
+        // The pair's row, weighted and rounded to the 16-bit type.  A thread owns 128 contiguous
+        // columns of one row; storing them directly would touch 32 rows per warp instruction, so
+        // the group's four warps stage 64 columns at a time in shared memory (144-byte row pitch)
+        // and write them out with 16-byte stores that cover four rows per instruction.
         const float scale = w_on_input ? 1.0f : gam;
-        if (t.n0 + 128 * grp < a.N) {
-          uint16_t* prow = reinterpret_cast<uint16_t*>(a.out_pairs) + static_cast<size_t>(orow) * a.N + t.n0 + 128 * grp;
-          const bool bf = a.dtype == B200MOE_DTYPE_BF16;
+        const bool bf = a.dtype == B200MOE_DTYPE_BF16;
+        uint8_t* stage_g = s_stage + grp * (128 * 144);
+        const int gtid = quad * 32 + lane;            // thread within the group
+        const uint32_t meet = smem_u32(&bar_meet[grp]);
+        auto group_meets = [&]() -> bool {            // bounded: a bar.sync would hang if a warp had given up
+          __syncwarp();
+          if (lane == 0) mbar_arrive(meet);
+          const bool arrived = mbar_wait(meet, meet_phase, abort_flag, DEV_TIMEOUT_EPILOGUE);
+          meet_phase ^= 1u;
+          return arrived;
+        };
 #pragma unroll
-          for (int q = 0; q < 16; ++q) {
-            const float* src = (q < 8) ? accA + 8 * q : accB + 8 * (q - 8);
+        for (int round = 0; round < 2 && ok; ++round) {
+          const float* src = (round == 0) ? accA : accB;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
             uint32_t w[4];
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
-              const float lo = src[2 * b] * scale, hi = src[2 * b + 1] * scale;
+              const float lo = src[8 * q + 2 * b] * scale, hi = src[8 * q + 2 * b + 1] * scale;
               if (bf) {
                 __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
                 w[b] = *reinterpret_cast<uint32_t*>(&v);
@@ -642,10 +662,31 @@ moe_gemm_fp8_tokm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
                 w[b] = *reinterpret_cast<uint32_t*>(&v);
               }
             }
-            *reinterpret_cast<uint4*>(prow + 8 * q) = make_uint4(w[0], w[1], w[2], w[3]);
+            *reinterpret_cast<uint4*>(stage_g + gtid * 144 + q * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+          if (!group_meets()) {
+            ok = false;
+            break;
+          }
+          const int col0 = t.n0 + 128 * grp + 64 * round;
+          if (col0 < a.N) {
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+              const int idx = it * 128 + gtid;
+              const int row = idx >> 3, ch = idx & 7;
+              const int prow = s_col_row[buf * 128 + row];
+              if (prow >= 0)
+                *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(a.out_pairs) + static_cast<size_t>(prow) * a.N + col0 +
+                                          ch * 8) = *reinterpret_cast<const uint4*>(stage_g + row * 144 + ch * 16);
+            }
+          }
+          if (!group_meets()) {
+            ok = false;
+            break;
           }
         }
-        if (t.n0 == 0 && grp == 0) a.pair_valid[orow] = 1;
+        if (!ok) break;
+        if (orow >= 0 && t.n0 == 0 && grp == 0) a.pair_valid[orow] = 1;
       } else if (orow >= 0) {
         const float scale = w_on_input ? 1.0f : gam;
         float* out = reinterpret_cast<float*>(a.out) + static_cast<size_t>(orow) * a.ld_out + t.n0 + 128 * grp;
@@ -686,8 +727,9 @@ moe_gemm_fp8_tokm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
 }
 
 size_t fp8_tokm_ctrl_bytes(const GemmArgs& a) {
-  return 2 * static_cast<size_t>(kMaxKB) * 128 * 4 + 2 * 2 * kMaxKB * 4 + 512 + 2 * 128 * 8 + 2 * 2 * 128 * 4 +
-         static_cast<size_t>(a.E + 1) * 4 + 64;
+  const size_t kbs = static_cast<size_t>(a.kblocks);
+  return 2 * kbs * 128 * 4 + 2 * 2 * kbs * 4 + ((a.mode == 1 && a.out_pairs != nullptr) ? kPairStageBytes : 0) + 512 +
+         2 * 128 * 8 + 2 * 2 * 128 * 4 + static_cast<size_t>(a.E + 1) * 4 + 64;
 }
 
 template <int MODE>
