@@ -375,6 +375,18 @@ __host__ __device__ __forceinline__ uint32_t make_idesc_i8(bool a_signed, bool b
   return d;
 }
 
+// Two fp32 fused multiply-adds in one instruction (packed f32x2, sm_100): c += a * s.
+__device__ __forceinline__ void ffma2(float& c0, float& c1, float a0, float a1, float s) {
+  asm("{\n\t.reg .b64 ra, rc, rs;\n\t"
+      "mov.b64 ra, {%2, %3};\n\t"
+      "mov.b64 rc, {%0, %1};\n\t"
+      "mov.b64 rs, {%4, %4};\n\t"
+      "fma.rn.f32x2 rc, ra, rs, rc;\n\t"
+      "mov.b64 {%0, %1}, rc;\n\t}"
+      : "+f"(c0), "+f"(c1)
+      : "f"(a0), "f"(a1), "f"(s));
+}
+
 // Programmatic dependent launch: a kernel launched with the stream-serialisation attribute may
 // start while its predecessor still runs; everything it does before griddep_wait() must not
 // touch global memory the predecessor writes.  Without the attribute both are no-ops.

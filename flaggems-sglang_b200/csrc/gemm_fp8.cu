@@ -583,10 +583,11 @@ moe_gemm_fp8_tokm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
         for (int c0 = 0; c0 < 64; c0 += 32) {
           float g[32], u[32];
           tmem_ld32x2_wait(taddr + colA + c0, taddr + colB + c0, g, u);
+          // packed f32x2 FMAs: the promotion is bound by instruction issue
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            accA[c0 + i] = fmaf(g[i], fA, accA[c0 + i]);
-            accB[c0 + i] = fmaf(u[i], fB, accB[c0 + i]);
+          for (int i = 0; i < 32; i += 2) {
+            ffma2(accA[c0 + i], accA[c0 + i + 1], g[i], g[i + 1], fA);
+            ffma2(accB[c0 + i], accB[c0 + i + 1], u[i], u[i + 1], fB);
           }
         }
         tc_fence_before();
@@ -619,11 +620,12 @@ moe_gemm_fp8_tokm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
         uint32_t pk[16];
 #pragma unroll
         for (int q = 0; q < 16; ++q) {
-          uint32_t w = 0;
-#pragma unroll
-          for (int b = 0; b < 4; ++b)
-            w |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(accA[4 * q + b] * inv, __NV_SATFINITE, __NV_E4M3)) << (8 * b);
-          pk[q] = w;
+          // two values per conversion instruction
+          const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(accA[4 * q] * inv, accA[4 * q + 1] * inv),
+                                                       __NV_SATFINITE, __NV_E4M3);
+          const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(accA[4 * q + 2] * inv, accA[4 * q + 3] * inv),
+                                                       __NV_SATFINITE, __NV_E4M3);
+          pk[q] = lo | (hi << 16);
         }
         uint4* dst = reinterpret_cast<uint4*>(a.out_q + static_cast<size_t>(r) * a.ld_out + t.n0 + 64 * grp);
 #pragma unroll
