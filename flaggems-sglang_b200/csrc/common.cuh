@@ -102,6 +102,18 @@ __device__ __forceinline__ bool mbar_wait_t(uint32_t bar, uint32_t parity, volat
 #endif
 }
 
+// Meeting point of several warps with a bounded wait, in place of a named bar.sync (which would
+// hang the CTA if one of the warps had given up on a time-out): `bar` is an mbarrier initialised to
+// the number of warps, lane 0 of each arrives, `phase` is the caller's running parity.
+__device__ __forceinline__ bool warps_meet(uint32_t bar, uint32_t& phase, int lane, volatile int* abort_flag,
+                                           int code) {
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar);
+  const bool ok = mbar_wait(bar, phase, abort_flag, code);
+  phase ^= 1u;
+  return ok;
+}
+
 // Short bounded wait used on the abort path to let copies in flight land.
 __device__ __forceinline__ void mbar_wait_brief(uint32_t bar, uint32_t parity) {
 #pragma unroll 1

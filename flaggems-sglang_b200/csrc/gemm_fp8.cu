@@ -54,7 +54,8 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   uint64_t* bar_pempty = bar_pfull + 4;
   uint64_t* bar_sfull = bar_pempty + 4;   // per-tile tables ready
   uint64_t* bar_sempty = bar_sfull + 2;   // per-tile tables released
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_sempty + 2);
+  uint64_t* bar_meet = bar_sempty + 2;    // [NG] meeting point of a promotion group's four warps
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_meet + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* s_col_row = reinterpret_cast<int*>(tmem_slot + 4);               // [2][128]
   float* s_col_gam = reinterpret_cast<float*>(s_col_row + 2 * 128);     // [2][128]
@@ -77,6 +78,7 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     for (int s = 0; s < 2; ++s) {
       mbar_init(smem_u32(&bar_sfull[s]), 1);
       mbar_init(smem_u32(&bar_sempty[s]), 4 * NG);
+      mbar_init(smem_u32(&bar_meet[s]), 4);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -220,6 +222,7 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     const int cb = grp * CPT;                       // first token column of this thread
     const bool w_on_input = (a.flags & B200MOE_FLAG_WEIGHT_ON_INPUT) != 0;
     uint32_t j = 0;
+    uint32_t meet_phase = 0;
     int iter = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < c.total; tile += c.grid_eff, ++iter) {
@@ -287,14 +290,14 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           const unsigned m = __reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(av)));
           if (lane == 0) red[gw * 64 + i] = __uint_as_float(m);
         }
-        named_bar_sync(2 + 3 * grp, 128);
+        if (!warps_meet(smem_u32(&bar_meet[grp]), meet_phase, lane, abort_flag, DEV_TIMEOUT_EPILOGUE)) break;
         if (ep_tid < CPT) {
           const float amax = fmaxf(fmaxf(red[ep_tid], red[64 + ep_tid]), fmaxf(red[128 + ep_tid], red[192 + ep_tid]));
           const float sc = __fdiv_rn(fmaxf(amax, 1e-10f), 448.0f);
           a.out_scale[static_cast<size_t>(t.n0 / 128) * a.ld_xscale + t.row0 + cb + ep_tid] = sc;
           red[ep_tid] = __fdiv_rn(1.0f, sc);
         }
-        named_bar_sync(4 + 2 * grp, 128);
+        if (!warps_meet(smem_u32(&bar_meet[grp]), meet_phase, lane, abort_flag, DEV_TIMEOUT_EPILOGUE)) break;
         uint8_t* outq = a.out_q + static_cast<size_t>(t.row0 + cb) * a.ld_out + n;
 #pragma unroll
         for (int i = 0; i < CPT; ++i) {
@@ -380,7 +383,8 @@ moe_gemm_fp8_tokm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
   uint64_t* bar_sfull = bar_pempty + 2;
   uint64_t* bar_sempty = bar_sfull + 2;
   uint64_t* bar_meet = bar_sempty + 2;          // [2] one per promotion group: meetings around the staged stores
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_meet + 2);
+  uint64_t* bar_meet8 = bar_meet + 2;           // both groups: the halves of a quantisation group's maximum
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_meet8 + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* s_col_row = reinterpret_cast<int*>(tmem_slot + 4);               // [2][128] output row of each token
   float* s_col_gam = reinterpret_cast<float*>(s_col_row + 2 * 128);     // [2][128]
@@ -402,6 +406,7 @@ moe_gemm_fp8_tokm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
       mbar_init(smem_u32(&bar_sempty[s]), 8);
       mbar_init(smem_u32(&bar_meet[s]), 4);
     }
+    mbar_init(smem_u32(bar_meet8), 8);
     *abort_flag = 0;
     fence_mbar_init();
     fence_proxy_async_smem();
@@ -546,7 +551,7 @@ moe_gemm_fp8_tokm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
     const uint32_t colA = (MODE == 0) ? 64u * grp : 128u * grp;
     const uint32_t colB = (MODE == 0) ? 128u + 64u * grp : 128u * grp + 64u;
     uint32_t j = 0;
-    uint32_t meet_phase = 0;
+    uint32_t meet_phase = 0, meet8_phase = 0;
     int iter = 0;
     bool ok = true;
     unsigned long long w_pfull = 0, w_sfull = 0, t_tail = 0;
@@ -611,7 +616,7 @@ moe_gemm_fp8_tokm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
         }
         float* red = s_red + buf * 2 * 128;
         red[grp * 128 + lrow] = amax;
-        named_bar_sync(2, 256);
+        if (!warps_meet(smem_u32(bar_meet8), meet8_phase, lane, abort_flag, DEV_TIMEOUT_EPILOGUE)) break;
         amax = fmaxf(red[lrow], red[128 + lrow]);
         const float sc = __fdiv_rn(fmaxf(amax, 1e-10f), 448.0f);
         const float inv = __fdiv_rn(1.0f, sc);
@@ -640,13 +645,7 @@ moe_gemm_fp8_tokm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
         uint8_t* stage_g = s_stage + grp * (128 * 144);
         const int gtid = quad * 32 + lane;            // thread within the group
         const uint32_t meet = smem_u32(&bar_meet[grp]);
-        auto group_meets = [&]() -> bool {            // bounded: a bar.sync would hang if a warp had given up
-          __syncwarp();
-          if (lane == 0) mbar_arrive(meet);
-          const bool arrived = mbar_wait(meet, meet_phase, abort_flag, DEV_TIMEOUT_EPILOGUE);
-          meet_phase ^= 1u;
-          return arrived;
-        };
+        auto group_meets = [&]() -> bool { return warps_meet(meet, meet_phase, lane, abort_flag, DEV_TIMEOUT_EPILOGUE); };
 #pragma unroll
         for (int round = 0; round < 2 && ok; ++round) {
           const float* src = (round == 0) ? accA : accB;

@@ -100,7 +100,8 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   uint64_t* bar_dq = bar_empty + stages;  // W4: operand tile dequantised
   uint64_t* bar_tfull = bar_dq + stages;
   uint64_t* bar_tempty = bar_tfull + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_tempty + 2);
+  uint64_t* bar_meet = bar_tempty + 2;    // meeting point of the four epilogue warps
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_meet + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* s_col_row = reinterpret_cast<int*>(tmem_slot + 4);               // [2][kMaxBT]
   float* s_col_gam = reinterpret_cast<float*>(s_col_row + 2 * kMaxBT);  // [2][kMaxBT]
@@ -119,6 +120,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       mbar_init(smem_u32(&bar_tfull[s]), 1);
       mbar_init(smem_u32(&bar_tempty[s]), 4);
     }
+    mbar_init(smem_u32(bar_meet), 4);
     *abort_flag = 0;
     fence_mbar_init();
     fence_proxy_async_smem();
@@ -311,7 +313,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     const ActParams ap = act_params(a);
     const bool has_bias = EXT && a.bias != nullptr;
     int acc = 0, iter = 0;
-    uint32_t acc_phase = 0;
+    uint32_t acc_phase = 0, meet_phase = 0;
     for (int tile = blockIdx.x; tile < c.total; tile += c.grid_eff, ++iter) {
       const TileCoord t = decode_tile(tile, c, s_blk_off, a.E, BT, a.num_nt, a.kblocks, G::kTileN);
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
@@ -392,7 +394,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
           col_row[cidx] = valid ? (MODE == 1 ? slot / a.topk : slot) : -1;
           col_gam[cidx] = valid ? a.row_gamma[t.row0 + cidx] : 0.f;
         }
-        named_bar_sync(1, 128);
+        if (!warps_meet(smem_u32(bar_meet), meet_phase, lane, abort_flag, DEV_TIMEOUT_EPILOGUE)) break;
         if (!mbar_wait(smem_u32(&bar_tfull[acc]), acc_phase, abort_flag, DEV_TIMEOUT_EPILOGUE)) break;
         tc_fence_after();
         const int n = t.n0 + lrow;
