@@ -8,6 +8,7 @@ namespace b200moe {
 namespace {
 
 constexpr int kAlignThreads = 1024;
+constexpr int kAhead = 8;   // iterations of 32 slots whose ids are fetched together
 
 __device__ __forceinline__ int load_id(const void* ids, int is64, int i) {
   return is64 ? static_cast<int>(reinterpret_cast<const long long*>(ids)[i])
@@ -60,11 +61,12 @@ __device__ __forceinline__ int upper_expert(const int* offs, int n, int x) {
 //   s_cnt   [nwarps][E] shared counters
 //   s_base  [E+1] shared: padded start row of each expert
 //   s_hist  [E]   shared: slots per expert
-// The caller provides place(slot, pos) to record a placement.
+// The caller provides place(slot, pos, pre[slot]) to record a placement.
+// `pre` (optional, [P]): a per-slot value fetched alongside the ids and handed to place().
 template <typename Place>
 __device__ __forceinline__ void group_by_expert(const void* ids, int is64, const int* map, int P, int E,
                                                 int block, int* s_cnt, int* s_base, int* s_hist,
-                                                int* s_scan, int nwarps, Place place) {
+                                                int* s_scan, int nwarps, const float* pre, Place place) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int i = threadIdx.x; i < nwarps * E; i += blockDim.x) s_cnt[i] = 0;
   __syncthreads();
@@ -75,18 +77,30 @@ __device__ __forceinline__ void group_by_expert(const void* ids, int is64, const
   const int begin = warp * seg;
   const int end = min(P, begin + seg);
 
+  // Both passes fetch the ids of kAhead iterations before they rank them: one dependent global
+  // load per 32 slots would otherwise set the pace of the whole kernel.
+  auto fetch = [&](int i) -> int {
+    int e = -1;
+    if (i < end) {
+      e = load_id(ids, is64, i);
+      if (map != nullptr && e >= 0) e = map[e];
+      if (e < 0 || e >= E) e = -1;
+    }
+    return e;
+  };
   if (warp < nwarps) {
-    for (int i0 = begin; i0 < end; i0 += 32) {
-      int i = i0 + lane;
-      int e = -1;
-      if (i < end) {
-        e = load_id(ids, is64, i);
-        if (map != nullptr && e >= 0) e = map[e];
-        if (e < 0 || e >= E) e = -1;
+    for (int i0 = begin; i0 < end; i0 += 32 * kAhead) {
+      int ev[kAhead];
+#pragma unroll
+      for (int u = 0; u < kAhead; ++u) ev[u] = fetch(i0 + 32 * u + lane);
+#pragma unroll
+      for (int u = 0; u < kAhead; ++u) {
+        if (i0 + 32 * u >= end) break;
+        const int e = ev[u];
+        unsigned m = __match_any_sync(0xffffffffu, e);
+        if (e >= 0 && (m & ((1u << lane) - 1)) == 0) s_cnt[warp * E + e] += __popc(m);
+        __syncwarp();
       }
-      unsigned m = __match_any_sync(0xffffffffu, e);
-      if (e >= 0 && (m & ((1u << lane) - 1)) == 0) s_cnt[warp * E + e] += __popc(m);
-      __syncwarp();
     }
   }
   __syncthreads();
@@ -118,24 +132,31 @@ __device__ __forceinline__ void group_by_expert(const void* ids, int is64, const
   __syncthreads();
 
   if (warp < nwarps) {
-    for (int i0 = begin; i0 < end; i0 += 32) {
-      int i = i0 + lane;
-      int e = -1;
-      if (i < end) {
-        e = load_id(ids, is64, i);
-        if (map != nullptr && e >= 0) e = map[e];
-        if (e < 0 || e >= E) e = -1;
+    for (int i0 = begin; i0 < end; i0 += 32 * kAhead) {
+      int ev[kAhead];
+      float wv[kAhead];
+#pragma unroll
+      for (int u = 0; u < kAhead; ++u) {
+        const int i = i0 + 32 * u + lane;
+        ev[u] = fetch(i);
+        wv[u] = (pre != nullptr && i < end) ? pre[i] : 0.f;
       }
-      unsigned m = __match_any_sync(0xffffffffu, e);
-      int rank = __popc(m & ((1u << lane) - 1));
-      int cur = 0;
-      if (e >= 0) cur = s_cnt[warp * E + e];
-      __syncwarp();
-      if (e >= 0) {
-        place(i, s_base[e] + cur + rank);
-        if (rank == 0) s_cnt[warp * E + e] = cur + __popc(m);
+#pragma unroll
+      for (int u = 0; u < kAhead; ++u) {
+        if (i0 + 32 * u >= end) break;
+        const int i = i0 + 32 * u + lane;
+        const int e = ev[u];
+        unsigned m = __match_any_sync(0xffffffffu, e);
+        int rank = __popc(m & ((1u << lane) - 1));
+        int cur = 0;
+        if (e >= 0) cur = s_cnt[warp * E + e];
+        __syncwarp();
+        if (e >= 0) {
+          place(i, s_base[e] + cur + rank, wv[u]);
+          if (rank == 0) s_cnt[warp * E + e] = cur + __popc(m);
+        }
+        __syncwarp();
       }
-      __syncwarp();
     }
   }
   __syncthreads();
@@ -160,9 +181,9 @@ align_block_kernel(const void* ids, int is64, const int* map, const float* weigh
   __syncthreads();
 
   group_by_expert(ids, is64, map, P, E, block, s_cnt, s_base, s_hist, s_scan, nwarps,
-                  [&](int slot, int pos) {
+                  row_gamma != nullptr ? weights : nullptr, [&](int slot, int pos, float w) {
                     sorted_ids[pos] = slot;
-                    if (row_gamma != nullptr) row_gamma[pos] = weights[slot];
+                    if (row_gamma != nullptr) row_gamma[pos] = w;
                   });
 
   const int rows = s_base[E];
@@ -256,8 +277,8 @@ routing_from_topk_kernel(const float* weights, const void* ids, int is64, int M,
   for (int i = threadIdx.x; i < 4 * max_tiles; i += blockDim.x) block_pid_map[i] = -1;
   __syncthreads();
 
-  group_by_expert(expt_indx, 0, nullptr, P, E, 1, s_cnt, s_base, s_hist, s_scan, nwarps,
-                  [&](int slot, int pos) {
+  group_by_expert(expt_indx, 0, nullptr, P, E, 1, s_cnt, s_base, s_hist, s_scan, nwarps, nullptr,
+                  [&](int slot, int pos, float) {
                     topk_indx[pos] = slot;
                     gate_indx[slot] = pos;
                     // the weight that the per-token sort moved to rank (slot % k):
