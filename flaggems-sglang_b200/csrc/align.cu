@@ -203,6 +203,155 @@ align_block_kernel(const void* ids, int is64, const int* map, const float* weigh
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same grouping spread over kAlignCtas CTAs in three launches, for tens of thousands of slots
+// (one CTA pushes every store through one SM's memory pipe: 77 us at 32 k slots).  CTA c owns the
+// contiguous slots [c * per, (c + 1) * per); stability follows from ordering by (CTA, warp, lane).
+//   count  per-CTA slots per expert -> cnt[c][e]; all CTAs share the filling of the defaults
+//   scan   one CTA: padded expert starts, per-CTA bases base[c][e], block tables
+//   place  each CTA recounts its chunk (cheaper than keeping the per-warp counts) and writes
+constexpr int kAlignCtas = 32;
+
+// warp-private counts of the chunk [begin, end): s_cnt[w][e]
+__device__ __forceinline__ void count_chunk(const void* ids, int is64, const int* map, int begin, int end, int E,
+                                            int* s_cnt, int nwarps, int* seg_begin, int* seg_end) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < nwarps * E; i += blockDim.x) s_cnt[i] = 0;
+  __syncthreads();
+  int seg = (max(end - begin, 0) + nwarps - 1) / nwarps;
+  seg = (seg + 31) & ~31;
+  const int b = begin + warp * seg;
+  const int e_ = min(end, b + seg);
+  *seg_begin = b;
+  *seg_end = e_;
+  if (warp < nwarps) {
+    for (int i0 = b; i0 < e_; i0 += 32) {
+      const int i = i0 + lane;
+      int e = -1;
+      if (i < e_) {
+        e = load_id(ids, is64, i);
+        if (map != nullptr && e >= 0) e = map[e];
+        if (e < 0 || e >= E) e = -1;
+      }
+      unsigned m = __match_any_sync(0xffffffffu, e);
+      if (e >= 0 && (m & ((1u << lane) - 1)) == 0) s_cnt[warp * E + e] += __popc(m);
+      __syncwarp();
+    }
+  }
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(kAlignThreads)
+align_count_kernel(const void* ids, int is64, const int* map, int P, int E, int block, int cap, int per, int nwarps,
+                   int* sorted_ids, int* expert_ids, float* row_gamma, int* cnt) {
+  extern __shared__ int smem[];
+  int* s_cnt = smem;
+  const int nblk_cap = (cap + block - 1) / block;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < cap; i += gridDim.x * blockDim.x) {
+    sorted_ids[i] = P;
+    if (row_gamma != nullptr) row_gamma[i] = 0.f;
+  }
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < nblk_cap; i += gridDim.x * blockDim.x) expert_ids[i] = -1;
+  const int begin = min(P, static_cast<int>(blockIdx.x) * per), end = min(P, begin + per);
+  int sb, se;
+  count_chunk(ids, is64, map, begin, end, E, s_cnt, nwarps, &sb, &se);
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int run = 0;
+    for (int w = 0; w < nwarps; ++w) run += s_cnt[w * E + e];
+    cnt[blockIdx.x * E + e] = run;
+  }
+}
+
+__global__ void __launch_bounds__(kAlignThreads)
+align_scan_kernel(const int* cnt, int E, int block, int nctas, int* base, int* expert_ids, int* num_post_pad,
+                  int* blk_off, int* meta) {
+  extern __shared__ int smem[];
+  int* s_base = smem;            // E + 1 padded starts
+  int* s_hist = s_base + (E + 1);
+  int* s_scan = s_hist + E;      // 33
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int run = 0;
+    for (int c = 0; c < nctas; ++c) {
+      const int t = cnt[c * E + e];
+      base[c * E + e] = run;     // slots of this expert in earlier CTAs
+      run += t;
+    }
+    s_hist[e] = run;
+  }
+  __syncthreads();
+  int carry = 0;
+  for (int e0 = 0; e0 < E; e0 += blockDim.x) {
+    const int e = e0 + threadIdx.x;
+    int padded = 0;
+    if (e < E) padded = (s_hist[e] + block - 1) / block * block;
+    int total;
+    const int ex = block_exclusive_scan(padded, s_scan, &total);
+    if (e < E) s_base[e] = carry + ex;
+    carry += total;
+  }
+  if (threadIdx.x == 0) s_base[E] = carry;
+  __syncthreads();
+  for (int i = threadIdx.x; i < nctas * E; i += blockDim.x) base[i] += s_base[i % E];
+  const int rows = s_base[E];
+  const int nblk = rows / block;
+  for (int b = threadIdx.x; b < nblk; b += blockDim.x) expert_ids[b] = upper_expert(s_base, E + 1, b * block);
+  if (blk_off != nullptr)
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) blk_off[e] = s_base[e] / block;
+  if (threadIdx.x == 0) {
+    num_post_pad[0] = rows;
+    if (meta != nullptr) {
+      meta[0] = nblk;
+      meta[1] = rows;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kAlignThreads)
+align_place_kernel(const void* ids, int is64, const int* map, const float* weights, int P, int E, int per, int nwarps,
+                   const int* base, int* sorted_ids, float* row_gamma) {
+  extern __shared__ int smem[];
+  int* s_cnt = smem;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int begin = min(P, static_cast<int>(blockIdx.x) * per), end = min(P, begin + per);
+  int sb, se;
+  count_chunk(ids, is64, map, begin, end, E, s_cnt, nwarps, &sb, &se);
+  // start of (warp, expert) = this CTA's base + the counts of the warps before it
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int run = base[blockIdx.x * E + e];
+    for (int w = 0; w < nwarps; ++w) {
+      const int t = s_cnt[w * E + e];
+      s_cnt[w * E + e] = run;
+      run += t;
+    }
+  }
+  __syncthreads();
+  if (warp < nwarps) {
+    for (int i0 = sb; i0 < se; i0 += 32) {
+      const int i = i0 + lane;
+      int e = -1;
+      float w = 0.f;
+      if (i < se) {
+        e = load_id(ids, is64, i);
+        if (map != nullptr && e >= 0) e = map[e];
+        if (e < 0 || e >= E) e = -1;
+        if (row_gamma != nullptr) w = weights[i];
+      }
+      unsigned m = __match_any_sync(0xffffffffu, e);
+      const int rank = __popc(m & ((1u << lane) - 1));
+      int cur = 0;
+      if (e >= 0) cur = s_cnt[warp * E + e];
+      __syncwarp();
+      if (e >= 0) {
+        const int pos = cur + rank;
+        sorted_ids[pos] = i;
+        if (row_gamma != nullptr) row_gamma[pos] = w;
+        if (rank == 0) s_cnt[warp * E + e] = cur + __popc(m);
+      }
+      __syncwarp();
+    }
+  }
+}
+
 // Internal tables from the reference's routing triple: hist[E], topk_indx[P]
 // (sorted row -> slot), gate_scal[P] (sorted row order).
 __global__ void __launch_bounds__(kAlignThreads)
@@ -358,6 +507,29 @@ int launch_align_block(const void* ids, int is64, const int* map, const float* w
   align_block_kernel<<<1, kAlignThreads, smem, stream>>>(ids, is64, map, weights, P, E, block, cap, nw,
                                                          sorted_ids, expert_ids, num_post_pad,
                                                          row_gamma, blk_off, meta);
+  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
+}
+
+size_t align_multi_tmp_bytes(int E) { return 2 * static_cast<size_t>(kAlignCtas) * E * sizeof(int); }
+
+int launch_align_block_multi(const void* ids, int is64, const int* map, const float* weights, int P, int E,
+                             int block, int cap, int* sorted_ids, int* expert_ids, int* num_post_pad,
+                             float* row_gamma, int* blk_off, int* meta, int* tmp, cudaStream_t stream) {
+  if (P < 0 || E <= 0 || block <= 0 || cap < 0 || tmp == nullptr) return B200MOE_ERR_BAD_ARG;
+  const int nw = pick_warps(E);
+  const size_t smem = (static_cast<size_t>(nw) * E + 40) * sizeof(int);
+  const size_t smem_scan = (2 * static_cast<size_t>(E) + 1 + 40) * sizeof(int);
+  if (smem > 48 * 1024 || smem_scan > 48 * 1024) return B200MOE_ERR_TOO_LARGE;
+  int per = (P + kAlignCtas - 1) / kAlignCtas;
+  per = (per + 31) & ~31;
+  int* cnt = tmp;
+  int* base = tmp + static_cast<size_t>(kAlignCtas) * E;
+  align_count_kernel<<<kAlignCtas, kAlignThreads, smem, stream>>>(ids, is64, map, P, E, block, cap, per, nw,
+                                                                  sorted_ids, expert_ids, row_gamma, cnt);
+  align_scan_kernel<<<1, kAlignThreads, smem_scan, stream>>>(cnt, E, block, kAlignCtas, base, expert_ids,
+                                                             num_post_pad, blk_off, meta);
+  align_place_kernel<<<kAlignCtas, kAlignThreads, smem, stream>>>(ids, is64, map, weights, P, E, per, nw, base,
+                                                                  sorted_ids, row_gamma);
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
 }
 

@@ -13,6 +13,13 @@ int launch_align_block(const void* ids, int is64, const int* map, const float* w
                        int block, int cap, int* sorted_ids, int* expert_ids, int* num_post_pad,
                        float* row_gamma, int* blk_off, int* meta, cudaStream_t stream);
 
+// The same tables from 32 CTAs in three launches (tens of thousands of slots); `tmp` holds
+// align_multi_tmp_bytes(E) bytes of scratch.  Output identical to launch_align_block.
+size_t align_multi_tmp_bytes(int E);
+int launch_align_block_multi(const void* ids, int is64, const int* map, const float* weights, int P, int E,
+                             int block, int cap, int* sorted_ids, int* expert_ids, int* num_post_pad,
+                             float* row_gamma, int* blk_off, int* meta, int* tmp, cudaStream_t stream);
+
 // Same internal tables from hist / topk_indx / gate_scal of the routing triple.
 int launch_align_from_routing(const int* hist, const int* topk_indx, const float* gate_scal, int P,
                               int E, int block, int cap, int* sorted_ids, float* row_gamma,

@@ -92,6 +92,7 @@ void prof_mark(int slot, int mark, cudaStream_t st) {
 
 struct Layout {
   int BT, cap, P;
+  bool align_multi; // alignment on 32 CTAs (many slots)
   bool quant_once; // FP8: quantise each token once, then gather the quantised rows (many pairs per token)
   bool pair_rows; // the down projection stores one 16-bit row per pair, the output conversion sums them
   bool w4p;       // int4 decode path: integer MMAs on three-plane int8 activations
@@ -99,7 +100,7 @@ struct Layout {
   int orient;     // GEMM tile orientation that goes with BT
   int act_bytes;  // bytes per activation element fed to the GEMMs
   size_t meta, blk_off, sorted_ids, expert_ids, num_post, row_gamma, xs, xs_scale, xs_sum, a2, a2_scale,
-      a2_sum, out32, pairs, pair_valid, xq_tok, xq_scale, route_w, route_ids, total;
+      a2_sum, out32, pairs, pair_valid, xq_tok, xq_scale, route_w, route_ids, align_tmp, total;
 };
 
 int pick_bt(const b200moe_cfg* c) {
@@ -150,6 +151,7 @@ int check_cfg(const b200moe_cfg* c) {
 }
 
 int query_sms(const b200moe_cfg* c);
+constexpr int kAlignMultiSlots = 8192;   // from here on the alignment runs on 32 CTAs
 
 int make_layout(const b200moe_cfg* c, Layout* L) {
   L->BT = pick_bt(c);
@@ -206,6 +208,8 @@ int make_layout(const b200moe_cfg* c, Layout* L) {
   L->pair_valid = take(L->pair_rows ? align_up(static_cast<size_t>(L->P), 16) : 0);
   L->route_w = take(static_cast<size_t>(L->P > 0 ? L->P : 1) * 4);    // router output when the call starts from logits
   L->route_ids = take(static_cast<size_t>(L->P > 0 ? L->P : 1) * 4);
+  L->align_multi = L->P >= kAlignMultiSlots && !(c->flags & B200MOE_FLAG_ALIGN_ONE_CTA);
+  L->align_tmp = take(L->align_multi ? align_multi_tmp_bytes(c->E) : 0);
   L->total = off;
   return B200MOE_OK;
 }
@@ -253,6 +257,22 @@ int query_sms(const b200moe_cfg* c) {
     cached[dev] = n;
   }
   return cached[dev];
+}
+
+// Block alignment into the workspace tables: one CTA, or 32 CTAs in three launches for many slots.
+int align_into_workspace(const b200moe_cfg* c, const Layout& L, uint8_t* ws, const void* ids, int is64,
+                         const int32_t* expert_map, const float* weights, cudaStream_t st) {
+  int* sorted_ids = reinterpret_cast<int*>(ws + L.sorted_ids);
+  int* expert_ids = reinterpret_cast<int*>(ws + L.expert_ids);
+  int* num_post = reinterpret_cast<int*>(ws + L.num_post);
+  float* row_gamma = reinterpret_cast<float*>(ws + L.row_gamma);
+  int* blk_off = reinterpret_cast<int*>(ws + L.blk_off);
+  int* meta = reinterpret_cast<int*>(ws + L.meta);
+  if (L.align_multi)
+    return launch_align_block_multi(ids, is64, expert_map, weights, L.P, c->E, L.BT, L.cap, sorted_ids, expert_ids,
+                                    num_post, row_gamma, blk_off, meta, reinterpret_cast<int*>(ws + L.align_tmp), st);
+  return launch_align_block(ids, is64, expert_map, weights, L.P, c->E, L.BT, L.cap, sorted_ids, expert_ids, num_post,
+                            row_gamma, blk_off, meta, st);
 }
 
 // Everything after the internal routing tables exist in the workspace.
@@ -541,11 +561,8 @@ int b200moe_forward_topk(const b200moe_cfg* cfg, const void* x, const void* w1, 
   uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
   const int slot = prof_slot();
   prof_mark(slot, 0, st);
-  rc = launch_align_block(topk_ids, (cfg->flags & B200MOE_FLAG_IDS_I64) ? 1 : 0, expert_map, topk_weights, L.P,
-                          cfg->E, L.BT, L.cap, reinterpret_cast<int*>(ws + L.sorted_ids),
-                          reinterpret_cast<int*>(ws + L.expert_ids), reinterpret_cast<int*>(ws + L.num_post),
-                          reinterpret_cast<float*>(ws + L.row_gamma), reinterpret_cast<int*>(ws + L.blk_off),
-                          reinterpret_cast<int*>(ws + L.meta), st);
+  rc = align_into_workspace(cfg, L, ws, topk_ids, (cfg->flags & B200MOE_FLAG_IDS_I64) ? 1 : 0, expert_map,
+                            topk_weights, st);
   if (rc != B200MOE_OK) return rc;
   return run_experts(cfg, L, x, w1, w2, quant, ws, out, status, st, slot);
 }
@@ -577,10 +594,7 @@ int b200moe_forward_logits(const b200moe_cfg* cfg, const b200moe_router* router,
   prof_mark(slot, 0, st);
   rc = launch_route_topk(router, logits, cfg->M, cfg->E, cfg->topk, tw, ids, query_sms(cfg), st);
   if (rc != B200MOE_OK) return rc;
-  rc = launch_align_block(ids, 0, expert_map, tw, L.P, cfg->E, L.BT, L.cap, reinterpret_cast<int*>(ws + L.sorted_ids),
-                          reinterpret_cast<int*>(ws + L.expert_ids), reinterpret_cast<int*>(ws + L.num_post),
-                          reinterpret_cast<float*>(ws + L.row_gamma), reinterpret_cast<int*>(ws + L.blk_off),
-                          reinterpret_cast<int*>(ws + L.meta), st);
+  rc = align_into_workspace(cfg, L, ws, ids, 0, expert_map, tw, st);
   if (rc != B200MOE_OK) return rc;
   return run_experts(cfg, L, x, w1, w2, quant, ws, out, status, st, slot);
 }

@@ -55,8 +55,8 @@ constexpr int kDqWarps = 4;
 constexpr int kPromoWarps = 8;
 constexpr int kThreadsW4P = 3 * 32 + 32 * kDqWarps + 32 * kPromoWarps;  // 480
 constexpr int kPackedRowBytes = 64;                  // 128 k of one weight row
-constexpr int kMaxGroupsW4 = 128;
-constexpr int kSzSlots = 16;                         // ring of per-group scale / zero words (1 KiB each)                    // reduction groups whose tables fit in shared memory
+constexpr int kMaxGroupsW4 = 128;                    // reduction groups whose tables fit in shared memory
+constexpr int kSzSlots = 16;                         // ring of per-group scale / zero words (1 KiB each)
 
 // position inside an aligned run of eight k at which element e is stored
 __device__ __forceinline__ int plane_pos(int e) { return ((e & 3) << 1) | ((e >> 2) & 1); }

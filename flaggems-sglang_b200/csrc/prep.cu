@@ -33,16 +33,32 @@ gather_rows_kernel(const uint4* __restrict__ x, uint4* __restrict__ xs, const in
           (slot >= 0 && slot < P) ? __ldg(sc_src + static_cast<size_t>(slot / topk) * G + g) : 1.0f;
     }
   }
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-    if (i < n_copy) {
-      const int r = static_cast<int>(i / chunks_per_row);
-      const int c = static_cast<int>(i - static_cast<long long>(r) * chunks_per_row);
-      const int slot = sorted_ids[r];
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (slot >= 0 && slot < P) v = __ldg(x + static_cast<size_t>(slot / topk) * chunks_per_row + c);
-      xs[i] = v;
-    } else {
-      zero[i - n_copy] = make_uint4(0, 0, 0, 0);
+  // four chunks per thread and trip: first the four row ids, then the four loads, then the stores
+  for (long long i0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < total; i0 += 4 * stride) {
+    int slot[4];
+    int col[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long i = i0 + u * stride;
+      slot[u] = -1;
+      col[u] = 0;
+      if (i < n_copy) {
+        const int r = static_cast<int>(i / chunks_per_row);
+        col[u] = static_cast<int>(i - static_cast<long long>(r) * chunks_per_row);
+        slot[u] = sorted_ids[r];
+      }
+    }
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      v[u] = make_uint4(0, 0, 0, 0);
+      if (slot[u] >= 0 && slot[u] < P) v[u] = __ldg(x + static_cast<size_t>(slot[u] / topk) * chunks_per_row + col[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < n_copy) xs[i] = v[u];
+      else if (i < total) zero[i - n_copy] = make_uint4(0, 0, 0, 0);
     }
   }
 }
@@ -217,13 +233,27 @@ finalize_pairs_kernel(const uint4* __restrict__ pairs, const uint8_t* __restrict
     const int t = static_cast<int>(i / chunks_per_row);
     const int c = static_cast<int>(i - static_cast<long long>(t) * chunks_per_row);
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int j = 0; j < topk; ++j) {
-      const size_t slot = static_cast<size_t>(t) * topk + j;
-      if (!pair_valid[slot]) continue;
-      const uint4 v = __ldg(pairs + slot * chunks_per_row + c);
-      const T* e = reinterpret_cast<const T*>(&v);
+    // four pairs at a time: the validity bytes first, then the row chunks, so that the loads of a
+    // batch are in flight together
+    for (int j0 = 0; j0 < topk; j0 += 4) {
+      uint4 v[4];
+      bool ok[4];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) acc[k] += to_f32<T>(e[k]);
+      for (int u = 0; u < 4; ++u) {
+        const size_t slot = static_cast<size_t>(t) * topk + j0 + u;
+        ok[u] = (j0 + u < topk) && pair_valid[slot] != 0;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const size_t slot = static_cast<size_t>(t) * topk + j0 + u;
+        v[u] = ok[u] ? __ldg(pairs + slot * chunks_per_row + c) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const T* e = reinterpret_cast<const T*>(&v[u]);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] += to_f32<T>(e[k]);   // zeros for pairs that are not there
+      }
     }
     T o[8];
 #pragma unroll

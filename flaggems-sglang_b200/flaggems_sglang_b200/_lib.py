@@ -20,7 +20,8 @@ LAYOUT_LAYER, LAYOUT_OP = 0, 1
 ACT_SILU, ACT_GELU, ACT_SWIGLU_OAI = 0, 1, 2
 NOALLOC_SCRATCH_BYTES = 16 * 1024 * 1024
 FLAG_WEIGHT_ON_INPUT, FLAG_MIMIC_ROUNDING, FLAG_SIMT, FLAG_IDS_I64, FLAG_NO_SPLIT_K, \
-    FLAG_NO_GRID_BALANCE, FLAG_NO_PDL, FLAG_W4_SMEM_OPERANDS, FLAG_NO_COMBINE = 1, 2, 4, 8, 16, 32, 64, 128, 256
+    FLAG_NO_GRID_BALANCE, FLAG_NO_PDL, FLAG_W4_SMEM_OPERANDS, FLAG_NO_COMBINE, FLAG_ALIGN_ONE_CTA = \
+    1, 2, 4, 8, 16, 32, 64, 128, 256, 512
 
 
 class Cfg(C.Structure):

@@ -96,6 +96,8 @@ def _env_flags() -> int:
     f = 0
     if os.environ.get("B200MOE_SIMT", "0") == "1":
         f |= _lib.FLAG_SIMT
+    if os.environ.get("B200MOE_ALIGN_ONE_CTA", "0") == "1":
+        f |= _lib.FLAG_ALIGN_ONE_CTA
     if os.environ.get("B200MOE_NO_SPLIT_K", "0") == "1":
         f |= _lib.FLAG_NO_SPLIT_K
     if os.environ.get("B200MOE_NO_GRID_BALANCE", "0") == "1":

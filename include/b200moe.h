@@ -59,6 +59,7 @@ extern "C" {
 #define B200MOE_FLAG_NO_GRID_BALANCE 32 /* tuning aid: every CTA takes tiles round-robin       */
 #define B200MOE_FLAG_NO_PDL 64          /* launch every kernel fully serialised                */
 #define B200MOE_FLAG_W4_SMEM_OPERANDS 128 /* int4: always stage fp16 operands in shared memory (tuning aid) */
+#define B200MOE_FLAG_ALIGN_ONE_CTA 512  /* tuning aid: single-CTA alignment however many slots           */
 #define B200MOE_FLAG_NO_COMBINE 256     /* out is [M*topk, H]: row t*topk+j holds pair j of token t,
                                            routing weight applied, nothing summed, routed_scaling ignored
                                            (the adapter's no_combine, fused_moe.py:392-397)               */

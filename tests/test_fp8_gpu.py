@@ -100,3 +100,23 @@ def test_fp8_many_pairs_stored_per_pair(cuda_device, masked):
     F.check_status()
     ref = OM.fused_experts_fp8(x, w13q, w2q, s13, s2, tw_ref, ids)
     assert_parity(out, (ref.float() * 1.5).to(ref.dtype), what=f"fp8 pair rows masked={masked}")
+
+
+def test_alignment_on_many_ctas_matches_single_cta(cuda_device, monkeypatch):
+    """From 8192 slots on, the alignment runs on 32 CTAs in three launches; it must order the rows
+    exactly like the single-CTA kernel.  The FP8 path with pair rows has no atomics, so the two
+    outputs must be bit-equal."""
+    import flaggems_sglang_b200 as F
+    h, i, e, k, m = 2048, 256, 64, 8, 1100          # 8800 slots, skewed routing, some experts empty
+    x, tw, ids, w13q, s13, w2q, s2 = _fp8_case(h, i, e, k, m, seed=5, skew=True)
+    d = cuda_device
+    args = (x.to(d), w13q.to(d), w2q.to(d), tw.to(d), ids.to(d))
+    kw = dict(use_fp8_w8a8=True, w13_scale=s13.to(d), w2_scale=s2.to(d))
+    multi = F.fused_experts(*args, **kw)
+    F.check_status()
+    monkeypatch.setenv("B200MOE_ALIGN_ONE_CTA", "1")
+    single = F.fused_experts(*args, **kw)
+    F.check_status()
+    assert torch.equal(multi, single)
+    ref = OM.fused_experts_fp8(x, w13q, w2q, s13, s2, tw, ids)
+    assert_parity(multi, ref, what="fp8 after multi-CTA alignment")
