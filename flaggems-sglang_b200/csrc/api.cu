@@ -132,6 +132,7 @@ int check_cfg(const b200moe_cfg* c) {
     return B200MOE_ERR_BAD_ARG;
   if (static_cast<long long>(c->M) * c->topk > (1LL << 24)) return B200MOE_ERR_TOO_LARGE;
   if (c->H % 8 != 0 || c->I % 8 != 0) return B200MOE_ERR_UNSUPPORTED;  // 16-byte rows for TMA
+  if ((c->flags & B200MOE_FLAG_X_FP8) && c->wmode != B200MOE_W_FP8_BLOCK) return B200MOE_ERR_UNSUPPORTED;
   if (c->wmode == B200MOE_W_16BIT) {
     if (c->w_layout != B200MOE_LAYOUT_LAYER) return B200MOE_ERR_UNSUPPORTED;
   } else if (c->wmode == B200MOE_W_FP8_BLOCK) {
@@ -201,7 +202,7 @@ int make_layout(const b200moe_cfg* c, Layout* L) {
   L->out32 = take(L->pair_rows ? 16 : static_cast<size_t>(L->out_rows > 0 ? L->out_rows : 1) * c->H * 4);
   // Quantising inside the gather repeats the work topk times; beyond a few thousand pairs it pays to
   // quantise the M token rows once and gather bytes.
-  L->quant_once = fp8 && L->P >= 2048 && c->topk > 1;
+  L->quant_once = fp8 && L->P >= 2048 && c->topk > 1 && !(c->flags & B200MOE_FLAG_X_FP8);
   L->xq_tok = take(L->quant_once ? static_cast<size_t>(c->M) * c->H : 0);
   L->xq_scale = take(L->quant_once ? static_cast<size_t>(c->M) * (c->H / 128) * 4 : 0);
   L->pairs = take(L->pair_rows ? static_cast<size_t>(L->P) * c->H * 2 : 0);
@@ -299,7 +300,12 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
     void* zero = L.pair_rows ? static_cast<void*>(ws + L.pair_valid) : static_cast<void*>(out32);
     const size_t zero_bytes = L.pair_rows ? align_up(static_cast<size_t>(L.P), 16)
                                           : static_cast<size_t>(L.out_rows) * c->H * 4;
-    if (L.quant_once) {
+    if (c->flags & B200MOE_FLAG_X_FP8) {
+      // rows arrive quantised (e.g. from an expert-parallel dispatch that sends bytes): gather only
+      if (quant->x_scale == nullptr) return B200MOE_ERR_BAD_ARG;
+      rc = launch_gather_rows(x, xs, sorted_ids, meta, L.P, c->topk, c->H, L.cap, zero, zero_bytes, sms, st, pdl,
+                              quant->x_scale, reinterpret_cast<float*>(ws + L.xs_scale), c->H / 128, L.cap);
+    } else if (L.quant_once) {
       float* tok_scale = reinterpret_cast<float*>(ws + L.xq_scale);
       rc = launch_group_quant_fp8(x, c->dtype, ws + L.xq_tok, tok_scale, nullptr, nullptr, L.P, c->topk, c->M, c->H, 0,
                                   0, zero, zero_bytes, sms, st, pdl);

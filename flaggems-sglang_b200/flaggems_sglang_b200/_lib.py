@@ -20,8 +20,8 @@ LAYOUT_LAYER, LAYOUT_OP = 0, 1
 ACT_SILU, ACT_GELU, ACT_SWIGLU_OAI = 0, 1, 2
 NOALLOC_SCRATCH_BYTES = 16 * 1024 * 1024
 FLAG_WEIGHT_ON_INPUT, FLAG_MIMIC_ROUNDING, FLAG_SIMT, FLAG_IDS_I64, FLAG_NO_SPLIT_K, \
-    FLAG_NO_GRID_BALANCE, FLAG_NO_PDL, FLAG_W4_SMEM_OPERANDS, FLAG_NO_COMBINE, FLAG_ALIGN_ONE_CTA = \
-    1, 2, 4, 8, 16, 32, 64, 128, 256, 512
+    FLAG_NO_GRID_BALANCE, FLAG_NO_PDL, FLAG_W4_SMEM_OPERANDS, FLAG_NO_COMBINE, FLAG_ALIGN_ONE_CTA, FLAG_X_FP8 = \
+    1, 2, 4, 8, 16, 32, 64, 128, 256, 512, 1024
 
 
 class Cfg(C.Structure):
@@ -35,7 +35,8 @@ class Cfg(C.Structure):
 
 class Quant(C.Structure):
     _fields_ = [("w1_scale", C.c_void_p), ("w2_scale", C.c_void_p), ("w1_sz", C.c_void_p), ("w2_sz", C.c_void_p),
-                ("b1", C.c_void_p), ("b2", C.c_void_p), ("swiglu_alpha", C.c_float), ("swiglu_limit", C.c_float)]
+                ("b1", C.c_void_p), ("b2", C.c_void_p), ("swiglu_alpha", C.c_float), ("swiglu_limit", C.c_float),
+                ("x_scale", C.c_void_p)]
 
 
 class Router(C.Structure):

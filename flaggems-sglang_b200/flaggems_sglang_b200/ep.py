@@ -93,6 +93,7 @@ def ep_fused_experts(
     ``local_fn(x, w13, w2, topk_weights, topk_ids, **kwargs)`` computes the local
     experts; it defaults to the CUDA operator of this package.
     """
+    own_operator = local_fn is None
     if local_fn is None:
         from .ops.fused_moe import fused_experts as local_fn
     world = dist.get_world_size(group)
@@ -106,15 +107,31 @@ def ep_fused_experts(
     if mode == "allgather":
         rank = dist.get_rank(group)
         x = hidden_states.contiguous()
-        xg = torch.empty(world * m, h, dtype=x.dtype, device=x.device)
-        dist.all_gather_into_tensor(xg, x, group=group)
-        meta = torch.cat([topk_ids.to(torch.int32), topk_weights.to(torch.float32).view(torch.int32)], dim=1).contiguous()
-        mg = torch.empty(world * m, 2 * k, dtype=torch.int32, device=x.device)
+        parts = [topk_ids.to(torch.int32), topk_weights.to(torch.float32).view(torch.int32)]
+        fp8_rows = (own_operator and bool(kwargs.get("use_fp8_w8a8")) and x.is_cuda and h % 128 == 0
+                    and x.dtype != torch.float8_e4m3fn)
+        if fp8_rows:
+            # FP8 weights: quantise this rank's rows before they travel (half the bytes on the wire, and
+            # no rank quantises another rank's rows again); the 1x128 scales ride with ids and weights
+            from .ops.quant import per_token_group_quant_fp8
+            xq, xsc = per_token_group_quant_fp8(x)
+            payload = xq.view(torch.uint8)
+            parts.append(xsc.view(torch.int32))
+        else:
+            payload = x
+        xg = torch.empty(world * m, h, dtype=payload.dtype, device=x.device)
+        dist.all_gather_into_tensor(xg, payload, group=group)
+        meta = torch.cat(parts, dim=1).contiguous()
+        mg = torch.empty(world * m, meta.shape[1], dtype=torch.int32, device=x.device)
         dist.all_gather_into_tensor(mg, meta, group=group)
         ids_all = mg[:, :k].contiguous()
-        w_all = mg[:, k:].contiguous().view(torch.float32)
+        w_all = mg[:, k:2 * k].contiguous().view(torch.float32)
         emap = local_expert_map(e_loc * world, e_loc, rank, x.device)
-        partial = local_fn(xg, w13_local, w2_local, w_all, ids_all, expert_map=emap, **kwargs)
+        if fp8_rows:
+            partial = local_fn(xg.view(torch.float8_e4m3fn), w13_local, w2_local, w_all, ids_all, expert_map=emap,
+                               x_scale=mg[:, 2 * k:].contiguous().view(torch.float32), out_dtype=x.dtype, **kwargs)
+        else:
+            partial = local_fn(xg, w13_local, w2_local, w_all, ids_all, expert_map=emap, **kwargs)
         return _reduce_scatter_rows(partial.contiguous(), m, group)
     assert mode == "alltoall", f"unknown expert-parallel mode {mode!r}"
 

@@ -140,8 +140,14 @@ def fused_experts(
     swiglu_limit: Optional[float] = None,
     no_combine: bool = False,
     router=None,
+    x_scale: Optional[torch.Tensor] = None,
+    out_dtype: Optional[torch.dtype] = None,
 ) -> torch.Tensor:
     """Fused experts on layer-layout weights ``w13 [E, 2I, H]``, ``w2 [E, H, I]``.
+
+    ``x_scale`` (FP8 weights only): ``hidden_states`` is already ``float8_e4m3fn``, quantised per
+    1x128 group with these scales ``[M, H/128]`` (as ``per_token_group_quant_fp8`` returns them);
+    ``out_dtype`` (default bfloat16) then names the type of the intermediate and of the result.
 
     ``router``: ``(make_router(...) result, topk)``; the call then starts from the gating
     logits and runs the router kernel in front (see ``fused_moe``).
@@ -176,9 +182,19 @@ def fused_experts(
     assert hw * pack == h, "hidden size mismatch"
     assert w2.shape[0] == e and w2.shape[1] == h and w2.shape[2] * pack == i, "intermediate size mismatch"
     assert w13.is_contiguous() and w2.is_contiguous(), "weights must be contiguous"
-    dtype = _DTYPES[x.dtype]
-
     flags = _env_flags()
+    odt = x.dtype
+    xs_keep = None
+    if x.dtype == torch.float8_e4m3fn:
+        assert use_fp8_w8a8 and x_scale is not None, "FP8 activations need FP8 weights and x_scale"
+        assert h % 128 == 0 and x_scale.shape == (m, h // 128), "x_scale must be [M, H/128]"
+        odt = out_dtype or torch.bfloat16
+        xs_keep = x_scale.to(torch.float32).contiguous()
+        flags |= _lib.FLAG_X_FP8
+    else:
+        assert x_scale is None, "x_scale goes with float8_e4m3fn hidden_states"
+    dtype = _DTYPES[odt]
+
     if apply_router_weight_on_input:
         flags |= _lib.FLAG_WEIGHT_ON_INPUT
     if mimic_reference_rounding:
@@ -193,6 +209,8 @@ def fused_experts(
         s1 = w13_scale.to(torch.float32).contiguous()
         s2 = w2_scale.to(torch.float32).contiguous()
         quant = _lib.Quant(s1.data_ptr(), s2.data_ptr(), None, None)
+        if xs_keep is not None:
+            quant.x_scale = xs_keep.data_ptr()
     elif use_int4_w4a16:
         wmode = _lib.W_INT4_AWQ
         assert x.dtype == torch.float16, "int4 w4a16 takes fp16 activations"
@@ -242,7 +260,7 @@ def fused_experts(
         flags |= _lib.FLAG_NO_COMBINE
     cfg = _make_cfg(m, h, i, e, k, dtype, wmode, _ACTS[activation], flags,
                     block_tokens or _block_tokens_env(), float(routed_scaling_factor))
-    out = torch.empty((m, k, h) if no_combine else (m, h), dtype=x.dtype, device=dev)
+    out = torch.empty((m, k, h) if no_combine else (m, h), dtype=odt, device=dev)
     if m == 0:
         return out
     nbytes = lib.b200moe_workspace_bytes(C.byref(cfg))

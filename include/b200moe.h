@@ -59,6 +59,10 @@ extern "C" {
 #define B200MOE_FLAG_NO_GRID_BALANCE 32 /* tuning aid: every CTA takes tiles round-robin       */
 #define B200MOE_FLAG_NO_PDL 64          /* launch every kernel fully serialised                */
 #define B200MOE_FLAG_W4_SMEM_OPERANDS 128 /* int4: always stage fp16 operands in shared memory (tuning aid) */
+#define B200MOE_FLAG_X_FP8 1024         /* FP8 weights only: x is already e4m3 [M, H], quantised per
+                                           1 x 128 group with scales quant->x_scale [M, H/128] (what
+                                           b200moe_per_token_group_quant_fp8 writes); cfg->dtype still
+                                           names the 16-bit type of the intermediate and the output   */
 #define B200MOE_FLAG_ALIGN_ONE_CTA 512  /* tuning aid: single-CTA alignment however many slots           */
 #define B200MOE_FLAG_NO_COMBINE 256     /* out is [M*topk, H]: row t*topk+j holds pair j of token t,
                                            routing weight applied, nothing summed, routed_scaling ignored
@@ -100,6 +104,7 @@ typedef struct b200moe_quant {
   const float *b2;
   float swiglu_alpha;     /* B200MOE_ACT_SWIGLU_OAI */
   float swiglu_limit;     /* B200MOE_ACT_SWIGLU_OAI: <= 0 disables the clamps */
+  const float *x_scale;   /* B200MOE_FLAG_X_FP8: [M, H/128] activation scales    */
 } b200moe_quant;
 
 int b200moe_version(void);

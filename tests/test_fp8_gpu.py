@@ -120,3 +120,22 @@ def test_alignment_on_many_ctas_matches_single_cta(cuda_device, monkeypatch):
     assert torch.equal(multi, single)
     ref = OM.fused_experts_fp8(x, w13q, w2q, s13, s2, tw, ids)
     assert_parity(multi, ref, what="fp8 after multi-CTA alignment")
+
+
+@pytest.mark.parametrize("h,i,e,k,m", [(512, 384, 8, 2, 100), (2048, 256, 16, 8, 640)])
+def test_fp8_prequantised_activations(cuda_device, h, i, e, k, m):
+    """Rows that arrive already quantised (expert-parallel dispatch sends bytes) give what the
+    in-call quantisation gives."""
+    import flaggems_sglang_b200 as F
+    from flaggems_sglang_b200.ops.quant import per_token_group_quant_fp8
+    x, tw, ids, w13q, s13, w2q, s2 = _fp8_case(h, i, e, k, m, seed=h + 1)
+    d = cuda_device
+    kw = dict(use_fp8_w8a8=True, w13_scale=s13.to(d), w2_scale=s2.to(d))
+    plain = F.fused_experts(x.to(d), w13q.to(d), w2q.to(d), tw.to(d), ids.to(d), **kw)
+    xq, xs = per_token_group_quant_fp8(x.to(d))
+    pre = F.fused_experts(xq, w13q.to(d), w2q.to(d), tw.to(d), ids.to(d), x_scale=xs, out_dtype=x.dtype, **kw)
+    F.check_status()
+    assert pre.dtype == plain.dtype
+    torch.testing.assert_close(pre.float(), plain.float(), rtol=1e-2, atol=1e-3)
+    ref = OM.fused_experts_fp8(x, w13q, w2q, s13, s2, tw, ids)
+    assert_parity(pre, ref, what=f"fp8 prequantised {(h, i, e, k, m)}")
