@@ -363,6 +363,39 @@ def run_ours(args, rank, local_rank, world):
                  "peak_source": peaks["source"], "kernel_ms": g1_ms, "gemm2_ms": g2_ms, "call_ms": tot_ms,
                  "algorithmic_bytes": g1_bytes, "algorithmic_flops": g1_flops})
 
+    # ---- this package's kernels launched by one call (mirrors the choices in csrc/api.cu; NCCL's own kernels
+    # in the expert-parallel runs are not counted)
+    m_loc = m * world if layer.ep else m          # tokens the local operator sees
+    p_loc = m_loc * k
+    kernel_names = []
+    if layer.ep and bw == 1:
+        kernel_names.append("group_quant_fp8 (own tokens, before the all-gather)")
+    kernel_names += (["align_count", "align_scan", "align_place"] if p_loc >= 8192 else ["align_block"])
+    bt = lib.b200moe_pick_block_tokens(C.byref(_lib.Cfg(C.sizeof(_lib.Cfg), m_loc, h, i, e // world if layer.ep else e, k,
+                                                        _lib.DTYPE_FP16 if bw == 0.5 else _lib.DTYPE_BF16,
+                                                        {2: _lib.W_16BIT, 1: _lib.W_FP8_BLOCK, 0.5: _lib.W_INT4_AWQ}[bw],
+                                                        _lib.LAYOUT_LAYER, 0, 0, 0, 1.0, 0)))
+    pair_rows = False
+    if bw == 1:
+        if layer.ep:
+            kernel_names.append("gather_rows (FP8 rows + scales)")
+        elif p_loc >= 2048 and k > 1:
+            kernel_names += ["group_quant_fp8 (once per token)", "gather_rows (FP8 rows + scales)"]
+        else:
+            kernel_names.append("group_quant_fp8 (gather + quantise)")
+        tokm = bt == 128
+        pair_rows = tokm and (p_loc // 128) * ((h + 255) // 256) >= 2 * 148
+        kernel_names += ["moe_gemm_fp8_tokm<gate/up>", "moe_gemm_fp8_tokm<down>"] if tokm else \
+                        ["moe_gemm_fp8<gate/up>", "moe_gemm_fp8<down>"]
+    elif bw == 0.5:
+        if bt <= 32:
+            kernel_names += ["group_split_i8", "moe_gemm_w4<gate/up>", "moe_gemm_w4<down>"]
+        else:
+            kernel_names += ["gather_rows", "moe_gemm_tc<gate/up, int4 operands>", "moe_gemm_tc<down, int4 operands>"]
+    else:
+        kernel_names += ["gather_rows", "moe_gemm_tc<gate/up>", "moe_gemm_tc<down>"]
+    kernel_names.append("finalize_pairs" if pair_rows else "finalize")
+
     # ---- end to end: pinned host -> device, public entry point, device -> pinned host
     hx, htw, hids = x.cpu().pin_memory(), tw.cpu().pin_memory(), ids.cpu().pin_memory()
     hout = torch.empty(m, h, dtype=x.dtype).pin_memory()
@@ -485,9 +518,8 @@ def run_ours(args, rank, local_rank, world):
                                        f"expert parallel over {world} ranks, all-to-all dispatch/combine, global M {m * world}"
                                        if layer.ep else f"{world} independent replicas (no collective)")},
             "clocks": clocks.summary(), "e2e": e2e,
-            "gpu_launches": 5 * args.steps,
-            "launches_per_step": {"kernels": 5, "names": ["align_block", "gather_rows | group_quant_fp8", "moe_gemm<gate/up>",
-                                                          "moe_gemm<down>", "finalize"]},
+            "gpu_launches": len(kernel_names) * args.steps,
+            "launches_per_step": {"kernels": len(kernel_names), "names": kernel_names},
             "roofline": roof, "cpu_baseline": cpu, "sweep": sweep,
             "whole_call": {"algorithmic_bytes": bytes_alg, "algorithmic_flops": flops_alg, "experts_hit": hit},
         }
