@@ -85,3 +85,57 @@ def test_reference_error_conventions():
         flaggems_sglang.triton_kernel_fused_experts(x, w1, w2, rd, gi, si, per_channel_quant=True)
     with pytest.raises(ValueError):
         flaggems_sglang.triton_kernel_fused_experts(x, w1, w2, rd, gi, si, activation="relu")
+
+
+def test_bias_variant_error_conventions():
+    """Same exception types as the reference's bias variant (fused_moe.py:247-261): asserts for
+    inplace / dtype, ValueError for any activation but silu."""
+    import torch
+    import flaggems_sglang
+    from flaggems_sglang_b200 import RoutingData, GatherIndx, ScatterIndx
+    z = torch.zeros(1, dtype=torch.int32)
+    rd = RoutingData(torch.ones(2), z, 2, 1, None)
+    gi, si = GatherIndx(z, z), ScatterIndx(z, z)
+    x = torch.zeros(2, 128, dtype=torch.bfloat16)
+    w1 = torch.zeros(2, 128, 256, dtype=torch.bfloat16)
+    w2 = torch.zeros(2, 128, 128, dtype=torch.bfloat16)
+    b1 = torch.zeros(2, 256, dtype=torch.bfloat16)
+    b2 = torch.zeros(2, 128, dtype=torch.bfloat16)
+    f = flaggems_sglang.triton_kernel_fused_experts_with_bias
+    with pytest.raises(AssertionError):
+        f(x, w1, None, b1, w2, None, b2, rd, gi, si, inplace=True)
+    with pytest.raises(AssertionError):
+        f(x.float(), w1, None, b1, w2, None, b2, rd, gi, si)
+    with pytest.raises(ValueError):
+        f(x, w1, None, b1, w2, None, b2, rd, gi, si, activation="gelu")
+
+
+def test_router_python_validation():
+    """The router's Python layer refuses CPU tensors (no CPU path) and unknown scoring names."""
+    import torch
+    from flaggems_sglang_b200.ops.router import make_router
+    with pytest.raises(AssertionError):
+        make_router(torch.zeros(4, 8), 2, True)
+    if torch.cuda.is_available():
+        with pytest.raises(ValueError):
+            make_router(torch.zeros(4, 8, device="cuda"), 2, True, scoring_func="tanh")
+
+
+def test_workspace_grows_with_the_optional_paths(built_lib):
+    """Workspace queries run without a GPU and account for the path-specific buffers."""
+    import ctypes as C
+    from flaggems_sglang_b200 import _lib
+    lib = _lib.lib()
+
+    def ws(m, h, i, e, k, wmode, dtype=_lib.DTYPE_BF16, flags=0):
+        cfg = _lib.Cfg(C.sizeof(_lib.Cfg), m, h, i, e, k, dtype, wmode, _lib.LAYOUT_LAYER, 0, flags, 0, 1.0, 0)
+        return lib.b200moe_workspace_bytes(C.byref(cfg))
+
+    small = ws(64, 1024, 512, 8, 2, _lib.W_16BIT)
+    assert 0 < small < ws(64, 1024, 512, 8, 2, _lib.W_16BIT, flags=_lib.FLAG_NO_COMBINE)      # [P, H] instead of [M, H]
+    big_fp8 = ws(4096, 7168, 2048, 256, 8, _lib.W_FP8_BLOCK)
+    assert big_fp8 > 4096 * 8 * 7168 * 2                        # 16-bit pair rows are part of it
+    assert ws(4096, 7168, 2048, 256, 8, _lib.W_FP8_BLOCK, flags=_lib.FLAG_X_FP8) < big_fp8     # no quantise-once buffers
+    assert ws(32, 4096, 14336, 8, 2, _lib.W_INT4_AWQ, dtype=_lib.DTYPE_FP16) > 0
+    assert ws(32, 4096, 14336, 8, 2, _lib.W_INT4_AWQ) == 0      # int4 needs fp16 activations
+    assert ws(64, 1024, 512, 8, 2, _lib.W_16BIT, flags=_lib.FLAG_X_FP8) == 0                   # FP8 rows need FP8 weights
