@@ -7,7 +7,7 @@
 // a quarter of what the packed weights need to keep HBM busy.  8-bit operands double the k per
 // instruction, and integer ones make the conversion almost free:
 //
-//   weights      the raw nibbles q (0..15) as unsigned bytes: two logic instructions per eight
+//   weights      the raw nibbles q (0..15) as unsigned bytes: three logic instructions per eight
 //                weights, written straight into tensor memory (tcgen05.st), never into shared
 //                memory.  The zero point is not subtracted here.
 //   activations  per (token, 128-k group) a power-of-two scale f and the exact integers
@@ -36,8 +36,11 @@
 //
 // Warps: 0 TMA producer, 1 MMA issuer, 6 per-tile table loader, 7-10 nibble -> byte conversion,
 // 2-5 and 11-14 promotion + tail: a thread owns one weight row (its TMEM lane) and half of the
-// token block, so that two promotion warps share each scheduler and hide each other's
-// tensor-memory load latency (with one set of warps the promotion, not the MMA, set the pace).
+// token block, so that two promotion warps share each scheduler.  The group's scale / zero words
+// reach the promotion through a shared-memory ring that the producer fills by bulk copy: a
+// global load per group, however far ahead it is issued in the source, ends up waited for in
+// the same iteration once its register is rotated, and that wait set the pace of every earlier
+// version of this kernel.
 #include "gemm_sched.cuh"
 
 namespace b200moe {
