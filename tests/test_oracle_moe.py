@@ -131,3 +131,54 @@ def test_product_quantisers_agree_with_oracle():
     pq, ps, pz = PQ.quantize_awq(wk)
     oq, os_, oz = Q.quant_weight_awq(wk)
     assert torch.equal(pq, Q.awq_pack(oq)) and torch.equal(ps, os_) and torch.equal(pz, Q.awq_pack(oz))
+
+
+def test_bias_variant_against_a_direct_loop():
+    """The oracle's bias / clamped-swiglu branch (order: bias, activation, routing weight, as the
+    dependency's grouped matmul applies them) against a token-by-token loop in fp32."""
+    import torch
+    from flaggems_sglang_b200.testing import route
+    from oracle import moe as OM
+    g = torch.Generator().manual_seed(0)
+    M, H, I, E, k = 5, 32, 16, 4, 2
+    x = torch.randn(M, H, generator=g)
+    w13 = torch.randn(E, 2 * I, H, generator=g) * 0.1
+    w2 = torch.randn(E, H, I, generator=g) * 0.1
+    b1 = torch.randn(E, 2 * I, generator=g)
+    b2 = torch.randn(E, H, generator=g)
+    tw, ids = route(torch.randn(M, E, generator=g), k)
+    out = OM.fused_experts(x, w13, w2, tw, ids, activation="swiglu_oai", b1=b1, b2=b2, swiglu_alpha=1.7,
+                           swiglu_limit=2.0, mimic_rounding=False)
+    ref = torch.zeros(M, H)
+    for t in range(M):
+        for j in range(k):
+            e = int(ids[t, j])
+            y = w13[e] @ x[t] + b1[e]
+            gate, lin = y[:I].clamp(max=2.0), y[I:].clamp(-2.0, 2.0)
+            s = gate * torch.sigmoid(1.7 * gate)
+            ref[t] += tw[t, j] * (w2[e] @ (s * (lin + 1)) + b2[e])
+    assert float((out - ref).abs().max()) < 1e-5
+
+
+def test_no_combine_rows_follow_topk_columns():
+    """no_combine returns pair j of token t in the column order of topk_ids, whatever order the
+    routing tables sort a token's experts in."""
+    import torch
+    from flaggems_sglang_b200.testing import route
+    from oracle import moe as OM
+    g = torch.Generator().manual_seed(1)
+    M, H, I, E, k = 6, 32, 16, 5, 3
+    x = torch.randn(M, H, generator=g)
+    w13 = torch.randn(E, 2 * I, H, generator=g) * 0.1
+    w2 = torch.randn(E, H, I, generator=g) * 0.1
+    tw, ids = route(torch.randn(M, E, generator=g), k)
+    pairs = OM.fused_experts(x, w13, w2, tw, ids, no_combine=True, mimic_rounding=False)
+    assert pairs.shape == (M, k, H)
+    for t in range(M):
+        for j in range(k):
+            e = int(ids[t, j])
+            y = w13[e] @ x[t]
+            a = torch.nn.functional.silu(y[:I]) * y[I:]
+            assert float((pairs[t, j] - tw[t, j] * (w2[e] @ a)).abs().max()) < 1e-5
+    whole = OM.fused_experts(x, w13, w2, tw, ids, mimic_rounding=False)
+    assert float((pairs.sum(1) - whole).abs().max()) < 1e-5
