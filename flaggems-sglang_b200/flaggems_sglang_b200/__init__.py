@@ -2,6 +2,7 @@
 fused-MoE entry points (src/flaggems_sglang/__init__.py:7-10 in the reference)."""
 from .ops import (
     check_status,
+    release_workspaces,
     fused_experts,
     fused_moe,
     fused_moe_flagos,
@@ -20,6 +21,7 @@ vendor_name = "nvidia"
 
 __all__ = [
     "check_status",
+    "release_workspaces",
     "fused_experts",
     "fused_moe",
     "fused_moe_flagos",

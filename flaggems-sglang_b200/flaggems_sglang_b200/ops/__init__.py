@@ -1,5 +1,6 @@
 from .fused_moe import (
     check_status,
+    release_workspaces,
     fused_experts,
     fused_moe,
     fused_moe_flagos,
@@ -11,6 +12,7 @@ from ..routing import moe_align_block_size, topk_to_routing
 
 __all__ = [
     "check_status",
+    "release_workspaces",
     "fused_experts",
     "fused_moe",
     "fused_moe_flagos",

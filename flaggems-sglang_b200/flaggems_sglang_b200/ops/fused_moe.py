@@ -10,11 +10,11 @@ from __future__ import annotations
 import ctypes as C
 import logging
 import os
-import weakref
 from types import SimpleNamespace
 from typing import Optional
 
 import torch
+from torch.utils.weak import WeakIdKeyDictionary
 
 from .. import _lib
 from ..routing import topk_to_routing
@@ -29,16 +29,40 @@ _ACTS = {"silu": _lib.ACT_SILU, "gelu": _lib.ACT_GELU, "swiglu_oai": _lib.ACT_SW
 # ---------------------------------------------------------------------------- state
 _workspaces: dict = {}     # (device index, stream handle) -> uint8 tensor
 _status: dict = {}         # device index -> int32[1]
-_relayout: "weakref.WeakKeyDictionary" = weakref.WeakKeyDictionary()
+# re-laid-out weights, keyed by the identity of the caller's tensor object (a dictionary keyed by
+# tensor *value* would compare two tensors with ==, which has no truth value)
+_relayout = WeakIdKeyDictionary()
+
+
+MAX_CACHED_WORKSPACES = 8     # (device, stream) pairs that keep a scratch buffer between calls
+_captured: list = []          # buffers a CUDA graph under capture was given: a replay writes to them
 
 
 def _workspace(dev: torch.device, nbytes: int) -> torch.Tensor:
+    """Scratch buffer of the calling (device, stream), kept between calls so that the hot path
+    does not allocate; it grows to the largest call seen on that stream.  At most
+    MAX_CACHED_WORKSPACES pairs keep one (the least recently used goes first) and
+    ``release_workspaces`` drops them all.  A buffer handed out while the stream is being
+    captured into a CUDA graph is never dropped: replays of the graph keep using it."""
     key = (dev.index, torch.cuda.current_stream(dev).cuda_stream)
-    ws = _workspaces.get(key)
+    ws = _workspaces.pop(key, None)
     if ws is None or ws.numel() < nbytes:
         ws = torch.empty(int(nbytes * 1.25) + 4096, dtype=torch.uint8, device=dev)
-        _workspaces[key] = ws
+    _workspaces[key] = ws                     # re-inserted last: dict order is the LRU order
+    while len(_workspaces) > MAX_CACHED_WORKSPACES:
+        _workspaces.pop(next(iter(_workspaces)))
+    if torch.cuda.is_current_stream_capturing() and not any(ws is c for c in _captured):
+        _captured.append(ws)
     return ws
+
+
+def release_workspaces(device=None) -> None:
+    """Drop the cached scratch buffers (of one device, or of all), e.g. after a one-off
+    prefill-sized call whose scratch should not stay allocated.  Buffers that a captured CUDA
+    graph uses are kept."""
+    idx = None if device is None else (torch.device(device).index or 0)
+    for key in [k for k in _workspaces if idx is None or k[0] == idx]:
+        _workspaces.pop(key)
 
 
 def _status_word(dev: torch.device) -> torch.Tensor:
@@ -63,6 +87,21 @@ def check_status(device=None) -> None:
             raise RuntimeError(f"b200moe: device-side wait timed out (code {code}) on cuda:{idx}")
 
 
+def _cached(w: torch.Tensor, kind: str, stamp: tuple, make):
+    """One derived layout per (tensor object, kind), rebuilt when the tensor was written to
+    in place (version counter), re-pointed at other storage, or `stamp` changed."""
+    per_tensor = _relayout.get(w)
+    if per_tensor is None:
+        per_tensor = {}
+        _relayout[w] = per_tensor
+    stamp = (w._version, w.data_ptr()) + stamp
+    ent = per_tensor.get(kind)
+    if ent is None or ent[0] != stamp:
+        ent = (stamp, make())
+        per_tensor[kind] = ent
+    return ent[1]
+
+
 def _layer_layout(w: torch.Tensor) -> torch.Tensor:
     """Op-level weights are [E, K, N] (reference layout, output dim contiguous);
     the kernels stream [E, N, K].  A transposed view of a [E, N, K] tensor is used
@@ -70,21 +109,14 @@ def _layer_layout(w: torch.Tensor) -> torch.Tensor:
     wt = w.transpose(-1, -2)
     if wt.is_contiguous():
         return wt
-    ent = _relayout.get(w)
-    if ent is None or ent[0] != w._version or ent[1] != w.data_ptr():
-        ent = (w._version, w.data_ptr(), wt.contiguous())
-        _relayout[w] = ent
-    return ent[2]
+    return _cached(w, "layer", (), wt.contiguous)
 
 
 def _awq_repacked(qweight: torch.Tensor, scales: torch.Tensor, qzeros: torch.Tensor):
     """AWQ checkpoint tensors -> kernel layout, once per qweight tensor object."""
     from ..quant import repack_awq_for_kernel
-    ent = _relayout.get(qweight)
-    if ent is None or ent[0] != qweight._version or ent[1] != qweight.data_ptr():
-        ent = (qweight._version, qweight.data_ptr(), repack_awq_for_kernel(qweight, scales, qzeros))
-        _relayout[qweight] = ent
-    return ent[2]
+    return _cached(qweight, "awq", (scales._version, scales.data_ptr(), qzeros._version, qzeros.data_ptr()),
+                   lambda: repack_awq_for_kernel(qweight, scales, qzeros))
 
 
 def _make_cfg(m, h, i, e, k, dtype, wmode, activation, flags, block_tokens, routed_scaling) -> _lib.Cfg:
@@ -413,14 +445,12 @@ def _deinterleaved(w1: torch.Tensor, b1: torch.Tensor, layer_layout: bool = Fals
     linear; the dependency's swiglu splits them that way).  The kernels want the gate rows
     first and the linear rows after them: re-laid out once per weight tensor object.
     ``w1`` is ``[E, H, 2I]`` (op level) or, with ``layer_layout``, ``[E, 2I, H]``."""
-    ent = _relayout.get(w1)
-    if ent is None or ent[0] != w1._version or ent[1] != w1.data_ptr() or ent[2] != b1._version:
+    def make():
         rows = w1 if layer_layout else w1.transpose(1, 2)                                   # [E, 2I, H]
         w13 = torch.cat([rows[:, 0::2, :], rows[:, 1::2, :]], dim=1).contiguous()
         b13 = torch.cat([b1[:, 0::2], b1[:, 1::2]], dim=1).to(torch.float32).contiguous()   # [E, 2I]
-        ent = (w1._version, w1.data_ptr(), b1._version, (w13, b13))
-        _relayout[w1] = ent
-    return ent[3]
+        return w13, b13
+    return _cached(w1, "split_ll" if layer_layout else "split_op", (b1._version, b1.data_ptr()), make)
 
 
 def triton_kernel_fused_experts_with_bias(

@@ -31,3 +31,16 @@ def cuda_device():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     return torch.device("cuda:0")
+
+
+def pytest_sessionfinish(session, exitstatus):
+    """With B200MOE_PARITY_REPORT=<file>: one line per floating-point comparison of the run
+    (fraction within the strict bound, worst element, bit-equal fraction)."""
+    path = os.environ.get("B200MOE_PARITY_REPORT")
+    if not path:
+        return
+    import json
+    from parity import RESULTS
+    with open(path, "a") as f:
+        for r in RESULTS:
+            f.write(json.dumps(r) + "\n")
