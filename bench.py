@@ -9,7 +9,15 @@ the same through the public Python entry point with pinned-host inputs and
 outputs copied inside the timed region.  With --gpus N every rank runs its own
 replica of the layer on its own M tokens (weak scaling, no collective).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+At every N the line also carries `config.expert_parallel`: the DeepSeek-V3-shaped FP8 layer
+(256 experts, zipf-skewed routing) at a fixed global batch of 4096 tokens -- on one GPU at N = 1,
+with the experts partitioned over the ranks at N > 1 (strong scaling).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference | reference-gpu]
+
+`--impl reference` times the CPU restatement of the reference's algorithm on the host cores (the
+reference has no CPU implementation); `--impl reference-gpu` times the reference's own Triton
+operator on the GPU through baseline/ref_shim.py (context only: not the reference arm).
 """
 from __future__ import annotations
 
@@ -50,7 +58,8 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the
 # ncu capture summarised under profiles/ (None until such a capture exists for the workload).
-NCU_TRAFFIC_BYTES = {("mixtral", 4096): 2201926400}   # profiles/moe_gemm_tc_mixtral_m4096_launch_list.md
+NCU_TRAFFIC = {("mixtral", 4096): {"kernel": "moe_gemm_tc_kernel<gate/up>", "bytes": 2201926400,
+                                   "source": "profiles/moe_gemm_tc_mixtral_m4096_launch_list.md"}}
 
 
 def load_peaks():
@@ -86,6 +95,7 @@ class Layer:
         self.act_dtype = torch.float16 if self.int4 else torch.bfloat16
         self.ep = self.fp8 and world > 1
         self.world = world
+        self.ep_collective = None
         e_ids = range(self.e)
         if self.ep:
             assert self.e % world == 0
@@ -126,16 +136,19 @@ class Layer:
 
     def forward(self, x, tw, ids):
         if self.ep:
-            from flaggems_sglang_b200.ep import ep_fused_experts
-            return ep_fused_experts(x, self.w13, self.w2, tw, ids, **self.kw)
+            from flaggems_sglang_b200 import ep
+            out = ep.ep_fused_experts(x, self.w13, self.w2, tw, ids, **self.kw)
+            self.ep_collective = ep.last_collective()
+            return out
         return self.F.fused_experts(x, self.w13, self.w2, tw, ids, **self.kw)
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+    """Samples SM clock and throttle reasons through NVML while timed regions run; every sample
+    carries its host time so that a region can be given its own median."""
 
     def __init__(self, index: int):
-        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.samples, self.reasons, self.max_mhz = [], set(), None      # samples: (perf_counter, MHz)
         self._stop = threading.Event()
         self._thr = None
         try:
@@ -157,7 +170,7 @@ class ClockSampler:
         }
         while not self._stop.is_set():
             try:
-                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                self.samples.append((time.perf_counter(), nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
                 r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
                 for n, bit in names.items():
                     if r & bit:
@@ -177,9 +190,14 @@ class ClockSampler:
         if self._thr is not None:
             self._thr.join()
 
+    def median_between(self, t0, t1):
+        v = [mhz for (t, mhz) in self.samples if t0 <= t <= t1]
+        return statistics.median(v) if v else None
+
     def summary(self):
-        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
-                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+        v = [mhz for (_, mhz) in self.samples]
+        return {"sm_mhz": statistics.median(v) if v else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(v)}
 
 
 def physical_index(local_rank: int) -> int:
@@ -193,9 +211,14 @@ def physical_index(local_rank: int) -> int:
 
 
 # ------------------------------------------------------------------ CPU arm (oracle)
-def cpu_arm(args, h, i, e, k, m, steps, warmup, budget_s=12.0):
+def workload_string(name, h, i, e, k, m):
+    return f"{name} H{h} I{i} E{e} top{k} M{m} per GPU, layer-layout weights"
+
+
+def cpu_arm(args, h, i, e, k, m, steps, warmup, budget_s=12.0, keep=None):
     """Times the CPU per-expert-loop restatement (oracle/moe.py) on a bounded
-    sample of the workload: the first m_cpu tokens of the batch."""
+    sample of the workload: the first m_cpu tokens of the batch.  `keep` (a dict) receives the
+    fp32 host weights so that the caller can reuse them for its output check."""
     from flaggems_sglang_b200.testing import make_tokens, make_weights
     from oracle import moe as OM
     cores = os.cpu_count() or 1
@@ -204,6 +227,8 @@ def cpu_arm(args, h, i, e, k, m, steps, warmup, budget_s=12.0):
     w13, w2 = make_weights(h, i, e, device=gen_dev, seed=0)
     w13f, w2f = w13.cpu().float(), w2.cpu().float()
     del w13, w2
+    if keep is not None:
+        keep["w13f"], keep["w2f"] = w13f, w2f
     x, tw, ids = make_tokens(m, h, e, k, device="cpu", seed=0)
     m_cpu = min(m, 64)
     t0 = time.perf_counter()
@@ -228,22 +253,78 @@ def cpu_arm(args, h, i, e, k, m, steps, warmup, budget_s=12.0):
 
 
 def run_reference(args, rank, world):
+    """CPU arm: rank 0 alone runs it, whatever N is (one host, one set of cores), so the line says
+    n_gpus 1 when launched under N ranks: its value does not grow with N."""
     h, i, e, k, dt = WORKLOADS[args.workload]
     if rank != 0:
         return
     res = cpu_arm(args, h, i, e, k, args.M, max(1, args.steps), max(0, args.warmup), budget_s=60.0)
     line = {
         "impl": "reference", "metric": "fused_moe_tokens_per_s", "value": res["value"], "unit": "tokens/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_step"],
+        "n_gpus": 1 if world > 1 else args.gpus, "launched_ranks": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_step"],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dt, "data": "synthetic",
-        "config": {"workload": f"{args.workload} H{h} I{i} E{e} top{k} M{args.M}",
+        "config": {"workload": workload_string(args.workload, h, i, e, k, args.M),
                    "note": "the reference has no CPU implementation of this path; this arm times the CPU "
-                           "restatement of its algorithm (oracle/moe.py) on the host cores"},
+                           "restatement of its algorithm (oracle/moe.py) on the host cores of rank 0 only"},
         "cpu_baseline": {"value": res["value"], "unit": "tokens/s", "cores": res["cores"], "kind": "port",
                          "sample": res["sample"]},
         "e2e": {"value": res["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    print(json.dumps(line), flush=True)
+
+
+def run_reference_gpu(args):
+    """The reference's own Triton operator (src/flaggems_sglang/ops/fused_moe.py:133-216) on this
+    GPU, through the import shim: CUDA-event median of >= 20 calls after >= 5 warm-ups for every M
+    of the workload's sweep.  Context for the bf16 rows; not the reference arm."""
+    sys.path.insert(0, str(ROOT / "baseline"))
+    h, i, e, k, dt = WORKLOADS[args.workload]
+    line = {"impl": "reference-gpu", "workload": args.workload, "shape": {"H": h, "I": i, "E": e, "topk": k},
+            "dtype": dt, "rows": []}
+    if dt != "bf16":
+        line["unavailable"] = "the reference rejects quantised weights (fused_moe.py:154-169)"
+        print(json.dumps(line), flush=True)
+        return
+    try:
+        from ref_shim import load_reference
+        ref, to_routing = load_reference()
+    except Exception as ex:  # noqa: BLE001
+        line["unavailable"] = f"reference not importable here: {ex!r}"[:300]
+        print(json.dumps(line), flush=True)
+        return
+    from flaggems_sglang_b200.testing import make_tokens, make_weights
+    dev = torch.device("cuda:0")
+    scale = 0.1 if args.workload == "reference-bench" else 0.02
+    w13, w2 = make_weights(h, i, e, device=dev, seed=0, scale=scale)
+    w1_op = w13.transpose(1, 2).contiguous()       # the reference's layout [E, H, 2I] / [E, I, H]
+    del w13
+    w2_op = w2.transpose(1, 2).contiguous()
+    del w2
+    n_calls = max(20, args.steps)
+    for m in SWEEP_M[args.workload]:
+        row = {"M": m}
+        try:
+            x, tw, ids = make_tokens(m, h, e, k, device=dev, seed=0)
+            rd, gi, si = to_routing(tw, ids.long(), e)
+            call = lambda: ref.triton_kernel_fused_experts(x, w1_op, w2_op, rd, gi, si)
+            for _ in range(max(5, args.warmup)):
+                call()
+            torch.cuda.synchronize()
+            times = []
+            for _ in range(n_calls):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                call()
+                e1.record()
+                e1.synchronize()
+                times.append(e0.elapsed_time(e1))
+            row.update(us=statistics.median(times) * 1e3, us_min=min(times) * 1e3, calls=n_calls,
+                       tokens_per_s=m / (statistics.median(times) / 1e3))
+        except Exception as ex:  # noqa: BLE001
+            row["unavailable"] = repr(ex)[:300]
+        line["rows"].append(row)
     print(json.dumps(line), flush=True)
 
 
@@ -266,6 +347,40 @@ def time_calls(fn, steps, warmup, barrier=None):
     return ev0.elapsed_time(ev1)  # ms
 
 
+def time_regions(fn, steps, warmup, barrier, dist, dev, clocks, min_total_s=1.0, max_regions=64):
+    """Regions of exactly `steps` calls, each bracketed by barrier + synchronize and timed with CUDA
+    events on the launching stream (maximum over ranks), repeated until at least `min_total_s` of
+    device time has been measured.  The number of regions follows from the first region's
+    (rank-maximum) time, so every rank runs the same number.  Returns [{ms, sm_mhz}]."""
+    for _ in range(warmup):
+        fn()
+    regions, target = [], None
+    while target is None or len(regions) < target:
+        torch.cuda.synchronize()
+        if barrier:
+            barrier()
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        ev0.record()
+        for _ in range(steps):
+            fn()
+        ev1.record()
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        if barrier:
+            barrier()
+        ms = ev0.elapsed_time(ev1)
+        if dist:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        regions.append({"ms": ms, "sm_mhz": clocks.median_between(t0, t1) if clocks else None})
+        if target is None:
+            target = max(1, min(max_regions, int(min_total_s * 1e3 / max(ms, 1e-3)) + 1))
+    return regions
+
+
 def time_graph_replays(fn, steps, warmup=3):
     """Captures one call of `fn` in a CUDA graph and times replays (device time per
     replay in ms), the way a serving stack issues decode steps; returns None if the
@@ -281,6 +396,58 @@ def time_graph_replays(fn, steps, warmup=3):
     except Exception as ex:  # noqa: BLE001
         sys.stderr.write(f"[bench] CUDA graph capture failed: {ex!r}\n")
         return None
+
+
+def expert_parallel_leg(args, dev, rank, local_rank, world, dist, barrier):
+    """DeepSeek-V3-shaped FP8 layer, one fixed global batch of 4096 tokens (seed 0, zipf-skewed routing over all
+    256 experts) whatever N is: on one GPU at N = 1, experts partitioned over the ranks and each rank bringing its
+    contiguous share of the tokens at N > 1.  Device-timed like the headline (regions of `steps` calls, median)."""
+    import flaggems_sglang_b200 as F
+    from flaggems_sglang_b200 import _lib
+    name, m_global = "deepseek-v3", 4096
+    h, i, e, k, dt = WORKLOADS[name]
+    layer = Layer(name, dev, rank, world)
+    gx, gtw, gids = layer.tokens(m_global, dev, 0)
+    m = m_global // world
+    x, tw, ids = (t[rank * m:(rank + 1) * m].contiguous() for t in (gx, gtw, gids))
+    del gx, gtw
+    step = lambda: layer.forward(x, tw, ids)
+    steps = max(5, min(args.steps, 20))
+    with ClockSampler(physical_index(local_rank)) as clocks:
+        regions = time_regions(step, steps, 3, barrier, dist, dev, clocks, min_total_s=0.5)
+    F.check_status()
+    med = statistics.median(r["ms"] for r in regions)
+    # time inside this package's local operator (alignment to output conversion), from events the library records
+    lib = _lib.lib()
+    _lib.check(lib.b200moe_profile_begin(steps), "profile_begin")
+    for _ in range(steps):
+        step()
+    g1, g2, tot, calls = C.c_double(), C.c_double(), C.c_double(), C.c_int()
+    _lib.check(lib.b200moe_profile_end(C.byref(g1), C.byref(g2), C.byref(tot), C.byref(calls)), "profile_end")
+    n = max(1, calls.value)
+    local_ms = tot.value / n
+    if dist:
+        t = torch.tensor([local_ms, g1.value / n + g2.value / n], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        local_ms, gemms_ms = float(t[0]), float(t[1])
+    else:
+        gemms_ms = g1.value / n + g2.value / n
+    _, names = _lib.launch_stats()
+    hit = int(torch.unique(gids).numel())
+    b, f = algorithmic_work(h, i, k, m_global, hit, 1)
+    ms_step = med / steps
+    res = {"workload": f"{name} H{h} I{i} E{e} top{k}, FP8 e4m3 128x128 block scales, zipf(1.1) routing skew, "
+                       f"global M {m_global} (seed 0), {e // world} experts and {m} tokens per rank",
+           "collective": layer.ep_collective if world > 1 else "none (one GPU)",
+           "ms_per_step": ms_step, "tokens_per_s": m_global / (ms_step / 1e3), "steps": steps,
+           "regions_ms": [round(r["ms"], 4) for r in regions],
+           "local_op_ms": local_ms, "gemms_ms": gemms_ms, "comm_and_glue_ms": max(0.0, ms_step - local_ms),
+           "kernels_last_call": names, "experts_hit": hit, "hbm_roofline_frac_whole_job":
+               (b / (load_peaks()["hbm_gbs"] * 1e9)) / world / (ms_step / 1e3),
+           "clocks": clocks.summary()}
+    del layer
+    torch.cuda.empty_cache()
+    return res
 
 
 def run_ours(args, rank, local_rank, world):
@@ -308,17 +475,18 @@ def run_ours(args, rank, local_rank, world):
         x, tw, ids = layer.tokens(mm, dev, seed)
         return x, tw, ids, (lambda: layer.forward(x, tw, ids))
 
-    # ---- headline: device-resident inputs
+    # ---- headline: device-resident inputs; regions of `steps` calls until >= 1 s is timed, median region
     x, tw, ids, step = make_step(m, rank)
+    warm = max(3, args.warmup)
     with ClockSampler(physical_index(local_rank)) as clocks:
-        ms = time_calls(step, args.steps, max(3, args.warmup), barrier)
+        launches0, _ = _lib.launch_stats()
+        regions = time_regions(step, args.steps, warm, barrier, dist, dev, clocks, min_total_s=args.min_seconds)
+        launches1, kernel_names = _lib.launch_stats()
     F.check_status()
-    if dist:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+    ms = statistics.median(r["ms"] for r in regions)
     ms_per_step = ms / args.steps
     value = world * m * args.steps / (ms / 1e3)
+    launches_per_step = (launches1 - launches0) // (len(regions) * args.steps + warm)
 
     # ---- per-kernel timing (same call, CUDA events recorded inside the library on the same stream)
     _lib.check(lib.b200moe_profile_begin(args.steps), "profile_begin")
@@ -357,44 +525,18 @@ def run_ours(args, rank, local_rank, world):
         ach = g1_bytes / (g1_ms / 1e3) / 1e9
         roof = {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": ach / peaks["hbm_gbs"]}
-    roof.update({"traffic": NCU_TRAFFIC_BYTES.get((args.workload, m)),
-                 "kernel": ("moe_gemm_fp8_kernel<0>" if bw == 1 else "moe_gemm_tc_kernel<0>") + " (gate/up + SiLU*mul)"
-                           + (", int4 dequant warps" if bw == 0.5 else ""),
+    gemm1_name = next((n for n in kernel_names if "gate/up" in n), None)
+    traffic = NCU_TRAFFIC.get((args.workload, m))
+    if traffic is not None and traffic["kernel"] != gemm1_name:
+        traffic = None                      # the capture on record is of another kernel than the one that ran
+    roof.update({"traffic": traffic["bytes"] if traffic else None,
+                 "traffic_source": traffic["source"] if traffic else None,
+                 "kernel": f"{gemm1_name} (gate/up projection + activation)",
                  "peak_source": peaks["source"], "kernel_ms": g1_ms, "gemm2_ms": g2_ms, "call_ms": tot_ms,
+                 "note": "kernel_ms and gemm2_ms come from CUDA events recorded between the kernels of a call; those "
+                         "records serialise what programmatic dependent launch otherwise overlaps, so kernel_ms + "
+                         "gemm2_ms can exceed ms_per_step and the fraction is a lower bound",
                  "algorithmic_bytes": g1_bytes, "algorithmic_flops": g1_flops})
-
-    # ---- this package's kernels launched by one call (mirrors the choices in csrc/api.cu; NCCL's own kernels
-    # in the expert-parallel runs are not counted)
-    m_loc = m * world if layer.ep else m          # tokens the local operator sees
-    p_loc = m_loc * k
-    kernel_names = []
-    if layer.ep and bw == 1:
-        kernel_names.append("group_quant_fp8 (own tokens, before the all-gather)")
-    kernel_names += (["align_count", "align_scan", "align_place"] if p_loc >= 8192 else ["align_block"])
-    bt = lib.b200moe_pick_block_tokens(C.byref(_lib.Cfg(C.sizeof(_lib.Cfg), m_loc, h, i, e // world if layer.ep else e, k,
-                                                        _lib.DTYPE_FP16 if bw == 0.5 else _lib.DTYPE_BF16,
-                                                        {2: _lib.W_16BIT, 1: _lib.W_FP8_BLOCK, 0.5: _lib.W_INT4_AWQ}[bw],
-                                                        _lib.LAYOUT_LAYER, 0, 0, 0, 1.0, 0)))
-    pair_rows = False
-    if bw == 1:
-        if layer.ep:
-            kernel_names.append("gather_rows (FP8 rows + scales)")
-        elif p_loc >= 2048 and k > 1:
-            kernel_names += ["group_quant_fp8 (once per token)", "gather_rows (FP8 rows + scales)"]
-        else:
-            kernel_names.append("group_quant_fp8 (gather + quantise)")
-        tokm = bt == 128
-        pair_rows = tokm and (p_loc // 128) * ((h + 255) // 256) >= 2 * 148
-        kernel_names += ["moe_gemm_fp8_tokm<gate/up>", "moe_gemm_fp8_tokm<down>"] if tokm else \
-                        ["moe_gemm_fp8<gate/up>", "moe_gemm_fp8<down>"]
-    elif bw == 0.5:
-        if bt <= 32:
-            kernel_names += ["group_split_i8", "moe_gemm_w4<gate/up>", "moe_gemm_w4<down>"]
-        else:
-            kernel_names += ["gather_rows", "moe_gemm_tc<gate/up, int4 operands>", "moe_gemm_tc<down, int4 operands>"]
-    else:
-        kernel_names += ["gather_rows", "moe_gemm_tc<gate/up>", "moe_gemm_tc<down>"]
-    kernel_names.append("finalize_pairs" if pair_rows else "finalize")
 
     # ---- end to end: pinned host -> device, public entry point, device -> pinned host
     hx, htw, hids = x.cpu().pin_memory(), tw.cpu().pin_memory(), ids.cpu().pin_memory()
@@ -417,16 +559,16 @@ def run_ours(args, rank, local_rank, world):
         t0 = time.perf_counter()
         fn_loop()
         torch.cuda.synchronize()
-        dt = time.perf_counter() - t0
+        dt_ = time.perf_counter() - t0
         if dist:
-            t = torch.tensor([dt], device=dev)
+            t = torch.tensor([dt_], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            dt = float(t.item())
-        return dt
+            dt_ = float(t.item())
+        return dt_
 
     for _ in range(3):
         e2e_step()
-    serial_s = timed_host(lambda: [e2e_step() for _ in range(e2e_steps)])
+    serial_s = min(timed_host(lambda: [e2e_step() for _ in range(e2e_steps)]) for _ in range(3))
     e2e_s, e2e_mode = serial_s, "serial: copy in, call, copy out on one stream"
 
     if not layer.ep:
@@ -441,10 +583,10 @@ def run_ours(args, rank, local_rank, world):
         ev_out = [torch.cuda.Event() for _ in range(2)]
 
         def pipelined(n):
-            for i in range(n):
-                b = i & 1
+            for it in range(n):
+                b = it & 1
                 with torch.cuda.stream(s_in):
-                    if i >= 2:
+                    if it >= 2:
                         s_in.wait_event(ev_run[b])       # the call that last read these input buffers
                     bx, btw, bids = bufs[b]
                     bx.copy_(hx, non_blocking=True)
@@ -457,7 +599,7 @@ def run_ours(args, rank, local_rank, world):
                     ev_run[b].record(s_run)
                 with torch.cuda.stream(s_out):
                     s_out.wait_event(ev_run[b])
-                    if i >= 2:
+                    if it >= 2:
                         s_out.wait_event(ev_out[b])
                     houts[b].copy_(out, non_blocking=True)
                     out.record_stream(s_out)
@@ -466,10 +608,10 @@ def run_ours(args, rank, local_rank, world):
         for st_ in (s_in, s_run, s_out):
             st_.wait_stream(torch.cuda.current_stream(dev))
         pipelined(4)
-        pipe_s = timed_host(lambda: pipelined(e2e_steps))
+        pipe_s = min(timed_host(lambda: pipelined(e2e_steps)) for _ in range(3))
         F.check_status()
         if not torch.equal(houts[(e2e_steps - 1) & 1], hout):
-            # fp32 atomics may flip a last bit; anything larger means the pipeline raced
+            # split reductions merge with fp32 atomics and may flip a last bit; anything larger means the pipeline raced
             d = (houts[(e2e_steps - 1) & 1].float() - hout.float()).abs().max().item()
             assert d <= 0.05 * max(1.0, hout.float().abs().max().item()), f"pipelined e2e result differs by {d}"
         if pipe_s < serial_s:
@@ -477,7 +619,7 @@ def run_ours(args, rank, local_rank, world):
     e2e = {"value": world * m * e2e_steps / e2e_s, "unit": "tokens/s",
            "h2d_bytes_per_step": hx.numel() * 2 + htw.numel() * 4 + hids.numel() * 4,
            "d2h_bytes_per_step": hout.numel() * 2, "steps": e2e_steps, "ms_per_step": e2e_s / e2e_steps * 1e3,
-           "mode": e2e_mode, "serial_ms_per_step": serial_s / e2e_steps * 1e3}
+           "mode": e2e_mode, "serial_ms_per_step": serial_s / e2e_steps * 1e3, "best_of": 3}
 
     # ---- sweep over the configuration's other M values (rank 0 of a single-GPU run only)
     sweep = []
@@ -485,7 +627,9 @@ def run_ours(args, rank, local_rank, world):
         for mm in SWEEP_M[args.workload]:
             _, _, ids_m, st = make_step(mm, 0)
             n = max(5, min(args.steps, 30))
-            t_eager = time_calls(st, n, 3) / n
+            with ClockSampler(physical_index(local_rank)) as ck:
+                reg = time_regions(st, n, 3, None, None, dev, ck, min_total_s=0.25)
+            t_eager = statistics.median(r["ms"] for r in reg) / n
             t_graph = time_graph_replays(st, n)
             t_ms = min(t_eager, t_graph) if t_graph else t_eager
             hit_m = int(torch.unique(ids_m).numel())
@@ -497,30 +641,53 @@ def run_ours(args, rank, local_rank, world):
                           "tokens_per_s": mm / (t_ms / 1e3), "experts_hit": hit_m,
                           "gbs": b / (t_ms / 1e3) / 1e9, "tflops": f / (t_ms / 1e3) / 1e12,
                           "bound": "hbm" if b / (peaks["hbm_gbs"] * 1e9) >= t_tc else "tensor",
-                          "roofline_frac": t_roof / (t_ms / 1e3)})
+                          "roofline_frac": t_roof / (t_ms / 1e3), "regions": len(reg),
+                          "sm_mhz": ck.summary()["sm_mhz"], "clock_reasons": ck.summary()["reasons"],
+                          "kernels": _lib.launch_stats()[1]})
         F.check_status()
 
-    cpu = None
+    # ---- the timed call's output against the CPU oracle, once (rank 0 of a single-GPU bf16 run)
+    cpu, check = None, {"checked": False}
     if rank == 0 and world == 1 and not args.no_cpu and not layer.fp8 and not layer.int4:
+        from oracle import moe as OM
+        out_dev = step().float().cpu()
+        hx_, htw_, hids_ = x.cpu(), tw.cpu(), ids.cpu()
         del x, tw, ids
-        cpu = cpu_arm(args, h, i, e, k, m, 3, 1, budget_s=15.0)
+        keep = {}
+        cpu = cpu_arm(args, h, i, e, k, m, 3, 1, budget_s=15.0, keep=keep)
         cpu = {kk: cpu[kk] for kk in ("value", "unit", "cores", "kind", "sample")}
+        ref = OM.fused_experts(hx_, keep["w13f"], keep["w2f"], htw_, hids_).float()
+        err = (out_dev - ref).abs()
+        check = {"checked": True, "against": "oracle/moe.py on the same seeded inputs, whole output",
+                 "frac_within_1e-2": float((err <= 1e-2 + 1e-2 * ref.abs()).float().mean()),
+                 "max_err": float(err.max()), "max_ref": float(ref.abs().max()),
+                 "bit_equal_frac": float((out_dev == ref).float().mean())}
+        del keep, ref, err
+
+    ep_leg = None
+    if not args.no_ep_leg and args.workload == "mixtral":
+        ep_leg = expert_parallel_leg(args, dev, rank, local_rank, world, dist, barrier)
 
     if rank == 0:
         line = {
             "metric": "fused_moe_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step,
-            "higher_is_better": True, "scaling": "strong" if layer.ep else "weak", "vs_baseline": None,
-            "dtype": dt, "data": "synthetic",
-            "config": {"workload": f"{args.workload} H{h} I{i} E{e} top{k} M{m} per GPU, layer-layout weights",
+            "steps": args.steps, "warmup": warm, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "strong" if WORKLOADS[args.workload][4] == "fp8" and world > 1 else "weak",
+            "vs_baseline": None, "dtype": dt, "data": "synthetic",
+            "config": {"workload": workload_string(args.workload, h, i, e, k, m),
                        "l2": "expert weights (GBs) exceed the 126 MB L2; no flush between steps",
+                       "timing": f"{len(regions)} regions of {args.steps} steps (>= {args.min_seconds:g} s of device time "
+                                 f"in total), value from the median region",
                        "parallelism": ("single GPU" if world == 1 else
-                                       f"expert parallel over {world} ranks, all-to-all dispatch/combine, global M {m * world}"
-                                       if layer.ep else f"{world} independent replicas (no collective)")},
+                                       f"{world} independent replicas (no collective)" if not layer_is_ep(args.workload, world)
+                                       else f"expert parallel over {world} ranks, global M {m * world}"),
+                       "expert_parallel": ep_leg},
+            "regions": [{"ms_per_step": r["ms"] / args.steps, "sm_mhz": r["sm_mhz"]} for r in regions],
             "clocks": clocks.summary(), "e2e": e2e,
-            "gpu_launches": len(kernel_names) * args.steps,
-            "launches_per_step": {"kernels": len(kernel_names), "names": kernel_names},
-            "roofline": roof, "cpu_baseline": cpu, "sweep": sweep,
+            "gpu_launches": launches_per_step * args.steps,
+            "launches_per_step": {"kernels": launches_per_step, "names": kernel_names,
+                                  "source": "counted by the library (b200moe_launch_stats)"},
+            "roofline": roof, "cpu_baseline": cpu, "check": check, "sweep": sweep,
             "whole_call": {"algorithmic_bytes": bytes_alg, "algorithmic_flops": flops_alg, "experts_hit": hit},
         }
         print(json.dumps(line), flush=True)
@@ -528,22 +695,32 @@ def run_ours(args, rank, local_rank, world):
         dist.destroy_process_group()
 
 
+def layer_is_ep(workload, world):
+    return WORKLOADS[workload][4] == "fp8" and world > 1
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"])
     ap.add_argument("--workload", default="mixtral", choices=sorted(WORKLOADS))
     ap.add_argument("--M", type=int, default=4096)
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-ep-leg", action="store_true", help="skip the expert-parallel DeepSeek-V3 leg")
+    ap.add_argument("--min-seconds", type=float, default=1.0, help="device time to accumulate over timed regions")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.impl == "reference-gpu":
+        if rank == 0:
+            run_reference_gpu(args)
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the fused-MoE path has no CPU fallback "

@@ -64,7 +64,7 @@ __device__ __forceinline__ int upper_expert(const int* offs, int n, int x) {
 // The caller provides place(slot, pos, pre[slot]) to record a placement.
 // `pre` (optional, [P]): a per-slot value fetched alongside the ids and handed to place().
 template <typename Place>
-__device__ __forceinline__ void group_by_expert(const void* ids, int is64, const int* map, int P, int E,
+__device__ __forceinline__ void group_by_expert(const void* ids, int is64, const int* map, int map_len, int P, int E,
                                                 int block, int* s_cnt, int* s_base, int* s_hist,
                                                 int* s_scan, int nwarps, const float* pre, Place place) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -83,7 +83,7 @@ __device__ __forceinline__ void group_by_expert(const void* ids, int is64, const
     int e = -1;
     if (i < end) {
       e = load_id(ids, is64, i);
-      if (map != nullptr && e >= 0) e = map[e];
+      if (map != nullptr && e >= 0) e = (e < map_len) ? map[e] : -1;
       if (e < 0 || e >= E) e = -1;
     }
     return e;
@@ -163,7 +163,7 @@ __device__ __forceinline__ void group_by_expert(const void* ids, int is64, const
 }
 
 __global__ void __launch_bounds__(kAlignThreads)
-align_block_kernel(const void* ids, int is64, const int* map, const float* weights, int P, int E,
+align_block_kernel(const void* ids, int is64, const int* map, int map_len, const float* weights, int P, int E,
                    int block, int cap, int nwarps, int* sorted_ids, int* expert_ids, int* num_post_pad,
                    float* row_gamma, int* blk_off, int* meta) {
   extern __shared__ int smem[];
@@ -180,7 +180,7 @@ align_block_kernel(const void* ids, int is64, const int* map, const float* weigh
   for (int i = threadIdx.x; i < nblk_cap; i += blockDim.x) expert_ids[i] = -1;
   __syncthreads();
 
-  group_by_expert(ids, is64, map, P, E, block, s_cnt, s_base, s_hist, s_scan, nwarps,
+  group_by_expert(ids, is64, map, map_len, P, E, block, s_cnt, s_base, s_hist, s_scan, nwarps,
                   row_gamma != nullptr ? weights : nullptr, [&](int slot, int pos, float w) {
                     sorted_ids[pos] = slot;
                     if (row_gamma != nullptr) row_gamma[pos] = w;
@@ -213,7 +213,7 @@ align_block_kernel(const void* ids, int is64, const int* map, const float* weigh
 constexpr int kAlignCtas = 32;
 
 // warp-private counts of the chunk [begin, end): s_cnt[w][e]
-__device__ __forceinline__ void count_chunk(const void* ids, int is64, const int* map, int begin, int end, int E,
+__device__ __forceinline__ void count_chunk(const void* ids, int is64, const int* map, int map_len, int begin, int end, int E,
                                             int* s_cnt, int nwarps, int* seg_begin, int* seg_end) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int i = threadIdx.x; i < nwarps * E; i += blockDim.x) s_cnt[i] = 0;
@@ -230,7 +230,7 @@ __device__ __forceinline__ void count_chunk(const void* ids, int is64, const int
       int e = -1;
       if (i < e_) {
         e = load_id(ids, is64, i);
-        if (map != nullptr && e >= 0) e = map[e];
+        if (map != nullptr && e >= 0) e = (e < map_len) ? map[e] : -1;
         if (e < 0 || e >= E) e = -1;
       }
       unsigned m = __match_any_sync(0xffffffffu, e);
@@ -242,7 +242,7 @@ __device__ __forceinline__ void count_chunk(const void* ids, int is64, const int
 }
 
 __global__ void __launch_bounds__(kAlignThreads)
-align_count_kernel(const void* ids, int is64, const int* map, int P, int E, int block, int cap, int per, int nwarps,
+align_count_kernel(const void* ids, int is64, const int* map, int map_len, int P, int E, int block, int cap, int per, int nwarps,
                    int* sorted_ids, int* expert_ids, float* row_gamma, int* cnt) {
   extern __shared__ int smem[];
   int* s_cnt = smem;
@@ -254,7 +254,7 @@ align_count_kernel(const void* ids, int is64, const int* map, int P, int E, int 
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < nblk_cap; i += gridDim.x * blockDim.x) expert_ids[i] = -1;
   const int begin = min(P, static_cast<int>(blockIdx.x) * per), end = min(P, begin + per);
   int sb, se;
-  count_chunk(ids, is64, map, begin, end, E, s_cnt, nwarps, &sb, &se);
+  count_chunk(ids, is64, map, map_len, begin, end, E, s_cnt, nwarps, &sb, &se);
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     int run = 0;
     for (int w = 0; w < nwarps; ++w) run += s_cnt[w * E + e];
@@ -307,14 +307,14 @@ align_scan_kernel(const int* cnt, int E, int block, int nctas, int* base, int* e
 }
 
 __global__ void __launch_bounds__(kAlignThreads)
-align_place_kernel(const void* ids, int is64, const int* map, const float* weights, int P, int E, int per, int nwarps,
+align_place_kernel(const void* ids, int is64, const int* map, int map_len, const float* weights, int P, int E, int per, int nwarps,
                    const int* base, int* sorted_ids, float* row_gamma) {
   extern __shared__ int smem[];
   int* s_cnt = smem;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int begin = min(P, static_cast<int>(blockIdx.x) * per), end = min(P, begin + per);
   int sb, se;
-  count_chunk(ids, is64, map, begin, end, E, s_cnt, nwarps, &sb, &se);
+  count_chunk(ids, is64, map, map_len, begin, end, E, s_cnt, nwarps, &sb, &se);
   // start of (warp, expert) = this CTA's base + the counts of the warps before it
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     int run = base[blockIdx.x * E + e];
@@ -332,7 +332,7 @@ align_place_kernel(const void* ids, int is64, const int* map, const float* weigh
       float w = 0.f;
       if (i < se) {
         e = load_id(ids, is64, i);
-        if (map != nullptr && e >= 0) e = map[e];
+        if (map != nullptr && e >= 0) e = (e < map_len) ? map[e] : -1;
         if (e < 0 || e >= E) e = -1;
         if (row_gamma != nullptr) w = weights[i];
       }
@@ -426,7 +426,7 @@ routing_from_topk_kernel(const float* weights, const void* ids, int is64, int M,
   for (int i = threadIdx.x; i < 4 * max_tiles; i += blockDim.x) block_pid_map[i] = -1;
   __syncthreads();
 
-  group_by_expert(expt_indx, 0, nullptr, P, E, 1, s_cnt, s_base, s_hist, s_scan, nwarps, nullptr,
+  group_by_expert(expt_indx, 0, nullptr, 0, P, E, 1, s_cnt, s_base, s_hist, s_scan, nwarps, nullptr,
                   [&](int slot, int pos, float) {
                     topk_indx[pos] = slot;
                     gate_indx[slot] = pos;
@@ -497,14 +497,15 @@ int routing_max_tiles(int n_slots, int n_experts) {
   return n_experts - 1 - fl;
 }
 
-int launch_align_block(const void* ids, int is64, const int* map, const float* weights, int P, int E,
+int launch_align_block(const void* ids, int is64, const int* map, int map_len, const float* weights, int P, int E,
                        int block, int cap, int* sorted_ids, int* expert_ids, int* num_post_pad,
                        float* row_gamma, int* blk_off, int* meta, cudaStream_t stream) {
   if (P < 0 || E <= 0 || block <= 0 || cap < 0) return B200MOE_ERR_BAD_ARG;
   int nw = pick_warps(E);
   size_t smem = (static_cast<size_t>(nw) * E + (E + 1) + E + 40) * sizeof(int);
   if (smem > 48 * 1024) return B200MOE_ERR_TOO_LARGE;
-  align_block_kernel<<<1, kAlignThreads, smem, stream>>>(ids, is64, map, weights, P, E, block, cap, nw,
+  note_launch("align_block_kernel");
+  align_block_kernel<<<1, kAlignThreads, smem, stream>>>(ids, is64, map, map_len, weights, P, E, block, cap, nw,
                                                          sorted_ids, expert_ids, num_post_pad,
                                                          row_gamma, blk_off, meta);
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
@@ -512,7 +513,7 @@ int launch_align_block(const void* ids, int is64, const int* map, const float* w
 
 size_t align_multi_tmp_bytes(int E) { return 2 * static_cast<size_t>(kAlignCtas) * E * sizeof(int); }
 
-int launch_align_block_multi(const void* ids, int is64, const int* map, const float* weights, int P, int E,
+int launch_align_block_multi(const void* ids, int is64, const int* map, int map_len, const float* weights, int P, int E,
                              int block, int cap, int* sorted_ids, int* expert_ids, int* num_post_pad,
                              float* row_gamma, int* blk_off, int* meta, int* tmp, cudaStream_t stream) {
   if (P < 0 || E <= 0 || block <= 0 || cap < 0 || tmp == nullptr) return B200MOE_ERR_BAD_ARG;
@@ -524,11 +525,14 @@ int launch_align_block_multi(const void* ids, int is64, const int* map, const fl
   per = (per + 31) & ~31;
   int* cnt = tmp;
   int* base = tmp + static_cast<size_t>(kAlignCtas) * E;
-  align_count_kernel<<<kAlignCtas, kAlignThreads, smem, stream>>>(ids, is64, map, P, E, block, cap, per, nw,
+  note_launch("align_count_kernel");
+  note_launch("align_scan_kernel");
+  note_launch("align_place_kernel");
+  align_count_kernel<<<kAlignCtas, kAlignThreads, smem, stream>>>(ids, is64, map, map_len, P, E, block, cap, per, nw,
                                                                   sorted_ids, expert_ids, row_gamma, cnt);
   align_scan_kernel<<<1, kAlignThreads, smem_scan, stream>>>(cnt, E, block, kAlignCtas, base, expert_ids,
                                                              num_post_pad, blk_off, meta);
-  align_place_kernel<<<kAlignCtas, kAlignThreads, smem, stream>>>(ids, is64, map, weights, P, E, per, nw, base,
+  align_place_kernel<<<kAlignCtas, kAlignThreads, smem, stream>>>(ids, is64, map, map_len, weights, P, E, per, nw, base,
                                                                   sorted_ids, row_gamma);
   return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
 }
@@ -539,6 +543,7 @@ int launch_align_from_routing(const int* hist, const int* topk_indx, const float
   if (P < 0 || E <= 0 || block <= 0) return B200MOE_ERR_BAD_ARG;
   size_t smem = (2 * static_cast<size_t>(E + 1) + 40) * sizeof(int);
   if (smem > 48 * 1024) return B200MOE_ERR_TOO_LARGE;
+  note_launch("align_from_routing_kernel");
   align_from_routing_kernel<<<1, kAlignThreads, smem, stream>>>(hist, topk_indx, gate_scal, P, E, block,
                                                                 cap, sorted_ids, row_gamma, blk_off,
                                                                 meta);
@@ -554,6 +559,7 @@ int launch_routing_from_topk(const float* weights, const void* ids, int is64, in
   size_t smem = (static_cast<size_t>(nw) * E + (E + 1) + E + 40) * sizeof(int);
   if (smem > 48 * 1024) return B200MOE_ERR_TOO_LARGE;
   int mt = routing_max_tiles(M * k, E);
+  note_launch("routing_from_topk_kernel");
   routing_from_topk_kernel<<<1, kAlignThreads, smem, stream>>>(
       weights, ids, is64, M, k, E, mt, nw, expt_indx, topk_indx, gate_indx, gate_scal, hist,
       token_offs_raw, token_offs_pad, block_pid_map);

@@ -1,5 +1,7 @@
 // C ABI: argument checks, workspace layout, tensor-map encoding and the launch sequence.
+#include <cstring>
 #include <mutex>
+#include <string>
 #include <vector>
 
 #include "align.cuh"
@@ -8,6 +10,10 @@
 #include "router.cuh"
 
 using namespace b200moe;
+
+namespace b200moe {
+void note_launch(const char* name);
+}
 
 namespace {
 
@@ -90,6 +96,18 @@ void prof_mark(int slot, int mark, cudaStream_t st) {
   if (slot >= 0) cudaEventRecord(g_prof.ev[static_cast<size_t>(slot) * kMarks + mark], st);
 }
 
+// Launch accounting (see common.cuh: note_launch).
+struct LaunchLog {
+  std::mutex mu;
+  long long total = 0;
+  std::string last_call;   // kernels of the most recent forward call, comma separated
+};
+LaunchLog g_launches;
+void launch_log_new_call() {
+  std::lock_guard<std::mutex> lk(g_launches.mu);
+  g_launches.last_call.clear();
+}
+
 struct Layout {
   int BT, cap, P;
   bool align_multi; // alignment on 32 CTAs (many slots)
@@ -133,6 +151,7 @@ int check_cfg(const b200moe_cfg* c) {
   if (static_cast<long long>(c->M) * c->topk > (1LL << 24)) return B200MOE_ERR_TOO_LARGE;
   if (c->H % 8 != 0 || c->I % 8 != 0) return B200MOE_ERR_UNSUPPORTED;  // 16-byte rows for TMA
   if ((c->flags & B200MOE_FLAG_X_FP8) && c->wmode != B200MOE_W_FP8_BLOCK) return B200MOE_ERR_UNSUPPORTED;
+  if (c->n_global_experts < 0) return B200MOE_ERR_BAD_ARG;
   if (c->wmode == B200MOE_W_16BIT) {
     if (c->w_layout != B200MOE_LAYOUT_LAYER) return B200MOE_ERR_UNSUPPORTED;
   } else if (c->wmode == B200MOE_W_FP8_BLOCK) {
@@ -152,6 +171,7 @@ int check_cfg(const b200moe_cfg* c) {
 }
 
 int query_sms(const b200moe_cfg* c);
+bool reference_rounds_pairs(int P, int E, int n, int k, int sms);
 constexpr int kAlignMultiSlots = 8192;   // from here on the alignment runs on 32 CTAs
 
 int make_layout(const b200moe_cfg* c, Layout* L) {
@@ -194,11 +214,20 @@ int make_layout(const b200moe_cfg* c, Layout* L) {
   L->a2_scale = take(tables ? static_cast<size_t>(cap) * (c->I / 128) * 4 : 0);
   L->a2_sum = take(L->w4p ? static_cast<size_t>(cap) * (c->I / 128) * 4 : 0);
   L->out_rows = (c->flags & B200MOE_FLAG_NO_COMBINE) ? L->P : c->M;   // one fp32 row per pair when nothing is summed
-  // Many pairs (FP8, 128-token blocks): fp32 atomics into the combine buffer would bound the down
-  // projection's tail, and its tiles fill the GPU without splitting the reduction; store 16-bit pair
-  // rows instead.  The combine buffer shrinks to the pairs' validity bytes.
-  L->pair_rows = fp8 && L->BT == 128 && !(c->flags & B200MOE_FLAG_NO_COMBINE) &&
-                 (static_cast<long long>(L->P) / L->BT) * ((c->H + 255) / 256) >= 2LL * query_sms(c);
+  // Many pairs on 128-token blocks: fp32 atomics into the combine buffer would bound the down
+  // projection's tail (every add is a read-modify-write of a row another tile also touches), and
+  // its tiles fill the GPU without splitting the reduction; store one 16-bit row per pair instead
+  // and let the output conversion sum a token's rows in a fixed order.  The combine buffer shrinks
+  // to the pairs' validity bytes.  16-bit weights: only where the reference, too, rounds each
+  // pair's row to the 16-bit type (or its rounding is not asked for).
+  const int sms_l = query_sms(c);
+  const bool many_tiles = (static_cast<long long>(L->P) / L->BT) * ((c->H + 255) / 256) >=
+                          (fp8 ? 2LL : 1LL) * sms_l;
+  const bool pairs_ok16 = !fp8 && !L->w4p && L->orient == 1 &&
+                          (!(c->flags & B200MOE_FLAG_MIMIC_ROUNDING) ||
+                           reference_rounds_pairs(L->P, c->E, c->H, c->I, sms_l));
+  L->pair_rows = (fp8 || pairs_ok16) && L->BT == 128 && !(c->flags & B200MOE_FLAG_NO_COMBINE) &&
+                 !(c->flags & B200MOE_FLAG_SIMT) && many_tiles;
   L->out32 = take(L->pair_rows ? 16 : static_cast<size_t>(L->out_rows > 0 ? L->out_rows : 1) * c->H * 4);
   // Quantising inside the gather repeats the work topk times; beyond a few thousand pairs it pays to
   // quantise the M token rows once and gather bytes.
@@ -270,9 +299,9 @@ int align_into_workspace(const b200moe_cfg* c, const Layout& L, uint8_t* ws, con
   int* blk_off = reinterpret_cast<int*>(ws + L.blk_off);
   int* meta = reinterpret_cast<int*>(ws + L.meta);
   if (L.align_multi)
-    return launch_align_block_multi(ids, is64, expert_map, weights, L.P, c->E, L.BT, L.cap, sorted_ids, expert_ids,
+    return launch_align_block_multi(ids, is64, expert_map, c->n_global_experts, weights, L.P, c->E, L.BT, L.cap, sorted_ids, expert_ids,
                                     num_post, row_gamma, blk_off, meta, reinterpret_cast<int*>(ws + L.align_tmp), st);
-  return launch_align_block(ids, is64, expert_map, weights, L.P, c->E, L.BT, L.cap, sorted_ids, expert_ids, num_post,
+  return launch_align_block(ids, is64, expert_map, c->n_global_experts, weights, L.P, c->E, L.BT, L.cap, sorted_ids, expert_ids, num_post,
                             row_gamma, blk_off, meta, st);
 }
 
@@ -294,12 +323,13 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
   int rc;
   if (w4 && (quant == nullptr || quant->w1_sz == nullptr || quant->w2_sz == nullptr)) return B200MOE_ERR_BAD_ARG;
 
+  // cleared alongside the first row mover: the fp32 combine buffer, or the pairs' validity bytes
+  // when rows are stored per pair
+  void* zero = L.pair_rows ? static_cast<void*>(ws + L.pair_valid) : static_cast<void*>(out32);
+  const size_t zero_bytes = L.pair_rows ? align_up(static_cast<size_t>(L.P), 16)
+                                        : static_cast<size_t>(L.out_rows) * c->H * 4;
   if (fp8) {
     if (quant == nullptr || quant->w1_scale == nullptr || quant->w2_scale == nullptr) return B200MOE_ERR_BAD_ARG;
-    // cleared alongside: the fp32 combine buffer, or the pairs' validity bytes when rows are stored per pair
-    void* zero = L.pair_rows ? static_cast<void*>(ws + L.pair_valid) : static_cast<void*>(out32);
-    const size_t zero_bytes = L.pair_rows ? align_up(static_cast<size_t>(L.P), 16)
-                                          : static_cast<size_t>(L.out_rows) * c->H * 4;
     if (c->flags & B200MOE_FLAG_X_FP8) {
       // rows arrive quantised (e.g. from an expert-parallel dispatch that sends bytes): gather only
       if (quant->x_scale == nullptr) return B200MOE_ERR_BAD_ARG;
@@ -319,10 +349,9 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
   } else if (L.w4p) {
     rc = launch_group_split_i8(x, reinterpret_cast<uint8_t*>(xs), reinterpret_cast<float*>(ws + L.xs_scale),
                                reinterpret_cast<int*>(ws + L.xs_sum), sorted_ids, meta, L.P, c->topk, L.cap, c->H,
-                               L.BT, L.cap, out32, static_cast<size_t>(L.out_rows) * c->H * 4, sms, st, pdl);
+                               L.BT, L.cap, zero, zero_bytes, sms, st, pdl);
   } else {
-    rc = launch_gather_rows(x, xs, sorted_ids, meta, L.P, c->topk, c->H * 2, L.cap, out32,
-                            static_cast<size_t>(L.out_rows) * c->H * 4, sms, st, pdl);
+    rc = launch_gather_rows(x, xs, sorted_ids, meta, L.P, c->topk, c->H * 2, L.cap, zero, zero_bytes, sms, st, pdl);
   }
   if (rc != B200MOE_OK) return rc;
 
@@ -395,6 +424,11 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
     if (reference_rounds_pairs(L.P, c->E, c->H, c->I, sms)) g2.flags |= B200MOE_FLAG_NO_SPLIT_K;
     else g2.flags &= ~B200MOE_FLAG_MIMIC_ROUNDING;
   }
+  if (L.pair_rows) {
+    g2.out_pairs = ws + L.pairs;
+    g2.pair_valid = ws + L.pair_valid;
+    g2.flags |= B200MOE_FLAG_NO_SPLIT_K;
+  }
   if (fp8) {
     g2.w_scale = quant->w2_scale;
     g2.w_scale_rows = (c->H + 127) / 128;
@@ -402,11 +436,6 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
     g2.out_q = nullptr;
     g2.out_scale = nullptr;
     g2.flags &= ~B200MOE_FLAG_MIMIC_ROUNDING;
-    if (L.pair_rows) {
-      g2.out_pairs = ws + L.pairs;
-      g2.pair_valid = ws + L.pair_valid;
-      g2.flags |= B200MOE_FLAG_NO_SPLIT_K;
-    }
   }
   if (w4p) {
     g2.x_scale = reinterpret_cast<float*>(ws + L.a2_scale);
@@ -472,6 +501,17 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
 
 }  // namespace
 
+namespace b200moe {
+void note_launch(const char* name) {
+  std::lock_guard<std::mutex> lk(g_launches.mu);
+  ++g_launches.total;
+  if (g_launches.last_call.size() < 4000) {
+    if (!g_launches.last_call.empty()) g_launches.last_call += ',';
+    g_launches.last_call += name;
+  }
+}
+}  // namespace b200moe
+
 extern "C" {
 
 int b200moe_version(void) { return B200MOE_VERSION; }
@@ -509,15 +549,17 @@ int b200moe_align_capacity(int n_slots, int n_experts, int block) {
 }
 
 int b200moe_align_block_size(const void* topk_ids, int ids_are_i64, int n_slots, int n_experts, int block,
-                             const int32_t* expert_map, int32_t* sorted_token_ids, int32_t* expert_ids,
+                             const int32_t* expert_map, int expert_map_len, int32_t* sorted_token_ids,
+                             int32_t* expert_ids,
                              int32_t* num_tokens_post_padded, void* stream) {
   if (n_slots < 0 || n_experts <= 0 || block <= 0) return B200MOE_ERR_BAD_ARG;
   if (num_tokens_post_padded == nullptr) return B200MOE_ERR_BAD_ARG;
   if (n_slots > 0 && topk_ids == nullptr) return B200MOE_ERR_BAD_ARG;
+  if (expert_map != nullptr && expert_map_len <= 0) return B200MOE_ERR_BAD_ARG;
   int cap = align_capacity(n_slots, n_experts, block);
   if (cap < 0) return B200MOE_ERR_TOO_LARGE;
   if (cap > 0 && (sorted_token_ids == nullptr || expert_ids == nullptr)) return B200MOE_ERR_BAD_ARG;
-  return launch_align_block(topk_ids, ids_are_i64, expert_map, nullptr, n_slots, n_experts, block, cap,
+  return launch_align_block(topk_ids, ids_are_i64, expert_map, expert_map_len, nullptr, n_slots, n_experts, block, cap,
                             sorted_token_ids, expert_ids, num_tokens_post_padded, nullptr, nullptr, nullptr,
                             static_cast<cudaStream_t>(stream));
 }
@@ -563,8 +605,10 @@ int b200moe_forward_topk(const b200moe_cfg* cfg, const void* x, const void* w1, 
   if (rc != B200MOE_OK) return rc;
   if (cfg->M == 0) return B200MOE_OK;
   if (!topk_weights || !topk_ids) return B200MOE_ERR_BAD_ARG;
+  if (expert_map != nullptr && cfg->n_global_experts <= 0) return B200MOE_ERR_BAD_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+  launch_log_new_call();
   const int slot = prof_slot();
   prof_mark(slot, 0, st);
   rc = align_into_workspace(cfg, L, ws, topk_ids, (cfg->flags & B200MOE_FLAG_IDS_I64) ? 1 : 0, expert_map,
@@ -592,8 +636,10 @@ int b200moe_forward_logits(const b200moe_cfg* cfg, const b200moe_router* router,
   if (cfg->flags & B200MOE_FLAG_IDS_I64) return B200MOE_ERR_BAD_ARG;   // the router writes int32 ids
   if (cfg->M == 0) return B200MOE_OK;
   if (!logits) return B200MOE_ERR_BAD_ARG;
+  if (expert_map != nullptr && cfg->n_global_experts <= 0) return B200MOE_ERR_BAD_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+  launch_log_new_call();
   float* tw = reinterpret_cast<float*>(ws + L.route_w);
   int* ids = reinterpret_cast<int*>(ws + L.route_ids);
   const int slot = prof_slot();
@@ -616,6 +662,7 @@ int b200moe_forward_routed(const b200moe_cfg* cfg, const void* x, const void* w1
   if (!hist || !topk_indx || !gate_scal) return B200MOE_ERR_BAD_ARG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+  launch_log_new_call();
   const int slot = prof_slot();
   prof_mark(slot, 0, st);
   rc = launch_align_from_routing(hist, topk_indx, gate_scal, L.P, cfg->E, L.BT, L.cap,
@@ -718,8 +765,27 @@ int b200moe_per_token_group_quant_fp8(const void* x, int dtype, int rows, int K,
   if (rows < 0 || K <= 0 || !x || !q || !scales) return B200MOE_ERR_BAD_ARG;
   if (dtype != B200MOE_DTYPE_BF16 && dtype != B200MOE_DTYPE_FP16) return B200MOE_ERR_BAD_ARG;
   if (rows == 0) return B200MOE_OK;
-  return launch_group_quant_fp8(x, dtype, q, scales, nullptr, nullptr, 0, 1, rows, K, 0, 0, nullptr, 0, 148,
-                                static_cast<cudaStream_t>(stream), false);
+  return launch_group_quant_fp8(x, dtype, q, scales, nullptr, nullptr, 0, 1, rows, K, 0, 0, nullptr, 0,
+                                query_sms(nullptr), static_cast<cudaStream_t>(stream), false);
+}
+
+int b200moe_launch_stats(long long* total_launches, char* last_call_names, size_t names_bytes) {
+  std::lock_guard<std::mutex> lk(g_launches.mu);
+  if (total_launches) *total_launches = g_launches.total;
+  int n = 0;
+  for (char ch : g_launches.last_call) n += ch == ',';
+  if (!g_launches.last_call.empty()) ++n;
+  if (last_call_names != nullptr && names_bytes > 0) {
+    const size_t len = g_launches.last_call.size() < names_bytes - 1 ? g_launches.last_call.size() : names_bytes - 1;
+    memcpy(last_call_names, g_launches.last_call.data(), len);
+    last_call_names[len] = 0;
+  }
+  return n;
+}
+
+int b200moe_selftest_timeout(uint64_t limit_ns, int32_t* status, int32_t* observed, void* stream) {
+  if (status == nullptr || observed == nullptr || limit_ns == 0 || limit_ns > 100000000ull) return B200MOE_ERR_BAD_ARG;
+  return launch_selftest_timeout(limit_ns, status, observed, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

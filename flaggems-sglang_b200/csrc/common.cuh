@@ -17,6 +17,8 @@ enum DevStatus : int {
   DEV_TIMEOUT_PRODUCER = 101,
   DEV_TIMEOUT_MMA = 102,
   DEV_TIMEOUT_EPILOGUE = 103,
+  DEV_TIMEOUT_PEER = 104,      // a flag another rank raises (expert parallelism) did not arrive
+  DEV_TIMEOUT_SELFTEST = 105,  // the wait the self-test lets run out on purpose
 };
 
 // A wait gives up after this many nanoseconds of wall clock.
@@ -66,10 +68,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait: returns false when the CTA-wide abort flag is raised or the
-// time limit runs out (it then raises the flag itself).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int code) {
+// Bounded wait: returns false when the CTA-wide abort flag is raised or `limit_ns` of wall clock
+// ran out (it then raises the flag itself).
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
+                                                unsigned long long limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   unsigned long long t0 = 0;
 #pragma unroll 1
@@ -79,12 +81,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (*abort_flag) return false;
       unsigned long long now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      if (now - t0 > kWaitLimitNs) {
+      if (now - t0 > limit_ns) {
         *abort_flag = code;
         return false;
       }
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int code) {
+  return mbar_wait_limit(bar, parity, abort_flag, code, kWaitLimitNs);
 }
 
 // Wait with optional stall accounting (development builds with -DB200MOE_STALL_STATS): the
@@ -410,6 +416,12 @@ __device__ __forceinline__ void griddep_launch_dependents() {
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
+
+// ---------------------------------------------------------------- host: launch accounting
+// Every launcher names the kernel it starts; the C ABI reports the total and the kernels of the
+// most recent forward call (b200moe_launch_stats), so that benchmarks count launches instead of
+// mirroring the launch logic.
+void note_launch(const char* name);
 
 // ---------------------------------------------------------------- host: launch with / without PDL
 template <typename... KArgs, typename... Args>

@@ -741,6 +741,7 @@ int launch_fp8_tokm(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const Gemm
   if (cudaFuncSetAttribute(moe_gemm_fp8_tokm_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(smem)) != cudaSuccess)
     return B200MOE_ERR_CUDA;
+  note_launch(MODE == 0 ? "moe_gemm_fp8_tokm_kernel<gate/up>" : "moe_gemm_fp8_tokm_kernel<down>");
   cudaError_t err = launch_kernel(moe_gemm_fp8_tokm_kernel<MODE>, dim3(num_sms), dim3(kThreadsFp8TokM), smem, stream,
                                   a.pdl != 0, tm_w, tm_x, a);
   return err == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
@@ -762,6 +763,7 @@ int launch_fp8(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmArgs&
   if (cudaFuncSetAttribute(moe_gemm_fp8_kernel<MODE, BT, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(smem)) != cudaSuccess)
     return B200MOE_ERR_CUDA;
+  note_launch(MODE == 0 ? "moe_gemm_fp8_kernel<gate/up>" : "moe_gemm_fp8_kernel<down>");
   cudaError_t err = launch_kernel(moe_gemm_fp8_kernel<MODE, BT, NG>, dim3(num_sms), dim3(fp8_threads(NG)), smem,
                                   stream, a.pdl != 0, tm_w, tm_x, a);
   return err == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;

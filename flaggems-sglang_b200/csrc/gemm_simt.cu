@@ -58,6 +58,7 @@ moe_gemm_simt_kernel(const T* __restrict__ w, const T* __restrict__ x, const Gem
 int launch_gemm_simt(const void* w, const void* x, const GemmArgs& a, cudaStream_t stream, int cap) {
   if (a.wmode != B200MOE_W_16BIT) return B200MOE_ERR_UNSUPPORTED;
   if (cap <= 0) return B200MOE_OK;
+  note_launch("moe_gemm_simt_kernel");
   if (a.dtype == B200MOE_DTYPE_BF16) {
     const __nv_bfloat16* wp = reinterpret_cast<const __nv_bfloat16*>(w);
     const __nv_bfloat16* xp = reinterpret_cast<const __nv_bfloat16*>(x);

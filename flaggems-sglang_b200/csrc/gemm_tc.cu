@@ -11,7 +11,8 @@
 //   the block and the activation needs no data exchange.
 // mode 1 (down):    one 128-row tile; the reduction may be split over CTAs; the epilogue
 //   multiplies by the routing weight and adds into the fp32 combine buffer with
-//   red.global.add.f32 (which also merges the top-k experts of a token).
+//   red.global.add.f32 (which also merges the top-k experts of a token), or, with many pairs on
+//   128-token blocks, stores one 16-bit row per pair for the output conversion to sum.
 //
 // Every wait is bounded; on a time-out the CTA raises an abort flag, all roles leave their
 // loops, the status word is set, TMEM is freed and the kernel returns.
@@ -357,6 +358,30 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             if (in_block && t.n0 + c0 + 16 <= a.N)
               *reinterpret_cast<uint4*>(orow + c0 + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
           }
+        } else if (a.out_pairs != nullptr) {
+          // one 16-bit row per (token, choice) pair, routing weight applied; the output conversion
+          // sums a token's rows in a fixed order (no atomics: a rerun gives the same bits)
+          T* prow = reinterpret_cast<T*>(a.out_pairs) + static_cast<size_t>(valid ? slot : 0) * a.N + t.n0;
+          const float scale = w_on_input ? 1.0f : gam;
+#pragma unroll 1
+          for (int c0 = 0; c0 < 256; c0 += 16) {
+            float v[16];
+            tmem_ld16_wait(taddr + c0, v);
+            if (valid) {
+              if (has_bias) {
+                const float* bo = a.bias + static_cast<size_t>(t.e) * a.N + t.n0 + c0;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] += (t.n0 + c0 + j < a.N) ? __ldg(bo + j) : 0.f;
+              }
+              uint32_t pk[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) pk[j] = pack2<T>(v[2 * j] * scale, v[2 * j + 1] * scale);
+              if (t.n0 + c0 + 8 <= a.N) *reinterpret_cast<uint4*>(prow + c0) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+              if (t.n0 + c0 + 16 <= a.N)
+                *reinterpret_cast<uint4*>(prow + c0 + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            }
+          }
+          if (valid && t.n0 == 0) a.pair_valid[slot] = 1;
         } else {
           const int orow_idx = valid ? slot / a.topk : 0;
           float* orow = reinterpret_cast<float*>(a.out) + static_cast<size_t>(orow_idx) * a.ld_out + t.n0;
@@ -503,6 +528,8 @@ static int launch_one(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const Ge
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem));
   if (err != cudaSuccess) return B200MOE_ERR_CUDA;
+  note_launch(W4 ? (MODE == 0 ? "moe_gemm_tc_kernel<gate/up, int4 operands>" : "moe_gemm_tc_kernel<down, int4 operands>")
+                 : (MODE == 0 ? "moe_gemm_tc_kernel<gate/up>" : "moe_gemm_tc_kernel<down>"));
   err = launch_kernel(moe_gemm_tc_kernel<MODE, T, ORIENT, W4, EXT>, dim3(num_sms), dim3(W4 ? kThreadsW4 : kThreads), smem,
                       stream, a.pdl != 0, tm_w, tm_x, a);
   return err == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;

@@ -554,6 +554,7 @@ int launch_w4(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmArgs& 
   if (cudaFuncSetAttribute(moe_gemm_w4_kernel<MODE, BT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(smem)) != cudaSuccess)
     return B200MOE_ERR_CUDA;
+  note_launch(MODE == 0 ? "moe_gemm_w4_kernel<gate/up>" : "moe_gemm_w4_kernel<down>");
   cudaError_t err = launch_kernel(moe_gemm_w4_kernel<MODE, BT>, dim3(num_sms), dim3(kThreadsW4P), smem, stream,
                                   a.pdl != 0, tm_w, tm_x, a);
   return err == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;

@@ -272,6 +272,7 @@ int launch_finalize_pairs(const void* pairs, const uint8_t* pair_valid, void* ou
   if (ctas > static_cast<long long>(num_sms) * 16) ctas = static_cast<long long>(num_sms) * 16;
   if (ctas < 1) ctas = 1;
   cudaError_t err;
+  note_launch("finalize_pairs_kernel");
   if (dtype == B200MOE_DTYPE_BF16)
     err = launch_kernel(finalize_pairs_kernel<__nv_bfloat16>, dim3(static_cast<unsigned>(ctas)), dim3(256), 0, stream,
                         pdl, reinterpret_cast<const uint4*>(pairs), pair_valid, reinterpret_cast<uint4*>(out), M, topk,
@@ -291,6 +292,7 @@ int launch_gather_rows(const void* x, void* xs, const int* sorted_ids, const int
   long long ctas = (work + 255) / 256;
   if (ctas > static_cast<long long>(num_sms) * 8) ctas = static_cast<long long>(num_sms) * 8;
   if (ctas < 1) ctas = 1;
+  note_launch("gather_rows_kernel");
   cudaError_t err = launch_kernel(gather_rows_kernel, dim3(static_cast<unsigned>(ctas)), dim3(256), 0, stream, pdl,
                                   reinterpret_cast<const uint4*>(x), reinterpret_cast<uint4*>(xs), sorted_ids, meta,
                                   P, topk, row_bytes / 16, cap, reinterpret_cast<uint4*>(zero),
@@ -308,6 +310,7 @@ int launch_group_quant_fp8(const void* x, int dtype, void* q, float* scales, con
   if (ctas < 1) ctas = 1;
   cudaError_t err;
   const long long zc = static_cast<long long>(zero_bytes / 16);
+  note_launch("group_quant_fp8_kernel");
   if (dtype == B200MOE_DTYPE_BF16)
     err = launch_kernel(group_quant_fp8_kernel<__nv_bfloat16>, dim3(static_cast<unsigned>(ctas)), dim3(256), 0, stream,
                         pdl, reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<uint8_t*>(q), scales,
@@ -327,6 +330,7 @@ int launch_group_split_i8(const void* x, uint8_t* planes, float* scales, int* su
   long long ctas = (warps + 7) / 8;
   if (ctas > num_sms * 16) ctas = num_sms * 16;
   if (ctas < 1) ctas = 1;
+  note_launch("group_split_i8_kernel");
   cudaError_t err = launch_kernel(group_split_i8_kernel, dim3(static_cast<unsigned>(ctas)), dim3(256), 0, stream, pdl,
                                   reinterpret_cast<const __half*>(x), planes, scales, sums, sorted_ids, meta, P, topk,
                                   cap, K, BT, ld, reinterpret_cast<uint4*>(zero),
@@ -342,6 +346,7 @@ int launch_finalize(const float* acc, void* out, int dtype, size_t n, float scal
   if (ctas > static_cast<size_t>(num_sms) * 8) ctas = static_cast<size_t>(num_sms) * 8;
   if (ctas < 1) ctas = 1;
   cudaError_t err;
+  note_launch("finalize_kernel");
   if (dtype == B200MOE_DTYPE_BF16)
     err = launch_kernel(finalize_kernel<__nv_bfloat16>, dim3(static_cast<unsigned>(ctas)), dim3(256), 0, stream, pdl,
                         reinterpret_cast<const float4*>(acc), reinterpret_cast<__nv_bfloat16*>(out), n4, scale);

@@ -36,4 +36,9 @@ int launch_finalize(const float* acc, void* out, int dtype, size_t n, float scal
 int launch_finalize_pairs(const void* pairs, const uint8_t* pair_valid, void* out, int dtype, int M, int topk,
                           int H, float scale, int num_sms, cudaStream_t stream, bool pdl);
 
+// Provokes a device-side time-out on purpose (see selftest.cu): observed[0] = 0 when the short wait
+// ran out, observed[1] = 0 when the sibling wait was released by the abort flag, observed[2] = the
+// microseconds the sibling waited; the status word receives DEV_TIMEOUT_SELFTEST.
+int launch_selftest_timeout(unsigned long long limit_ns, int* status, int* observed, cudaStream_t stream);
+
 }  // namespace b200moe

@@ -184,6 +184,7 @@ int launch_route_topk(const b200moe_router* r, const void* logits, int M, int E,
   const size_t smem = static_cast<size_t>(kRouterWarps) * 2 * E * sizeof(float);
   const float scale = r->scale == 0.f ? 1.0f : r->scale;
   cudaError_t err;
+  note_launch("route_topk_kernel");
 #define B200MOE_ROUTE(TL)                                                                                     \
   err = launch_kernel(route_topk_kernel<TL>, dim3(ctas), dim3(kRouterWarps * 32), smem, stream, false,          \
                       reinterpret_cast<const TL*>(logits), r->bias, M, E, topk, r->scoring, r->renormalize,     \

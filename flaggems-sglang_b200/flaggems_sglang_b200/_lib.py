@@ -7,7 +7,7 @@ from pathlib import Path
 
 from ._build import LIB_PATH
 
-VERSION = 1
+VERSION = 2
 
 OK = 0
 ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_TOO_LARGE = -1, -2, -3, -4, -5, -6
@@ -30,6 +30,7 @@ class Cfg(C.Structure):
         ("E", C.c_int32), ("topk", C.c_int32), ("dtype", C.c_int32), ("wmode", C.c_int32),
         ("w_layout", C.c_int32), ("activation", C.c_int32), ("flags", C.c_int32),
         ("block_tokens", C.c_int32), ("routed_scaling", C.c_float), ("num_sms", C.c_int32),
+        ("n_global_experts", C.c_int32),
     ]
 
 
@@ -52,7 +53,7 @@ SYMBOLS = {
     "b200moe_pick_block_tokens": (C.c_int, [C.POINTER(Cfg)]),
     "b200moe_workspace_bytes": (C.c_size_t, [C.POINTER(Cfg)]),
     "b200moe_align_capacity": (C.c_int, [C.c_int, C.c_int, C.c_int]),
-    "b200moe_align_block_size": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
+    "b200moe_align_block_size": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int,
                                            C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "b200moe_routing_max_tiles": (C.c_int, [C.c_int, C.c_int]),
     "b200moe_routing_from_topk": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
@@ -75,6 +76,8 @@ SYMBOLS = {
     "b200moe_profile_begin": (C.c_int, [C.c_int]),
     "b200moe_profile_end": (C.c_int, [C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double),
                                       C.POINTER(C.c_int)]),
+    "b200moe_launch_stats": (C.c_int, [C.POINTER(C.c_longlong), C.c_char_p, C.c_size_t]),
+    "b200moe_selftest_timeout": (C.c_int, [C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p]),
     "b200moe_per_token_group_quant_fp8": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p,
                                                     C.c_void_p, C.c_void_p]),
 }
@@ -105,6 +108,15 @@ def lib() -> C.CDLL:
             raise ExtensionMissing(f"{path} has ABI version {handle.b200moe_version()}, expected {VERSION}")
         _lib = handle
     return _lib
+
+
+def launch_stats():
+    """(kernels launched since the library was loaded, names of the most recent forward call's kernels)."""
+    total = C.c_longlong()
+    buf = C.create_string_buffer(4096)
+    lib().b200moe_launch_stats(C.byref(total), buf, len(buf))
+    names = buf.value.decode()
+    return total.value, (names.split(",") if names else [])
 
 
 def status_string(code: int) -> str:

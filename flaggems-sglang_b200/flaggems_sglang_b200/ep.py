@@ -51,6 +51,13 @@ def dispatch_tables(topk_ids: torch.Tensor, topk_weights: torch.Tensor, n_local_
 
 
 _expert_maps: dict = {}
+_last_collective = "none"
+
+
+def last_collective() -> str:
+    """What the most recent ``ep_fused_experts`` call on this rank used to move rows (for reports)."""
+    return _last_collective
+
 
 
 def local_expert_map(n_global: int, n_local: int, rank: int, device) -> torch.Tensor:
@@ -100,11 +107,14 @@ def ep_fused_experts(
     m, h = hidden_states.shape
     k = topk_ids.shape[1]
     e_loc = w13_local.shape[0]
+    global _last_collective
     if world == 1:
+        _last_collective = "none (one rank)"
         return local_fn(hidden_states, w13_local, w2_local, topk_weights, topk_ids.to(torch.int32), **kwargs)
     if mode is None:
         mode = "allgather" if world <= max(k, 2) else "alltoall"
     if mode == "allgather":
+        _last_collective = "all-gather of token rows and routing (dispatch) + reduce-scatter of partial rows (combine)"
         rank = dist.get_rank(group)
         x = hidden_states.contiguous()
         parts = [topk_ids.to(torch.int32), topk_weights.to(torch.float32).view(torch.int32)]
@@ -134,6 +144,7 @@ def ep_fused_experts(
             partial = local_fn(xg, w13_local, w2_local, w_all, ids_all, expert_map=emap, **kwargs)
         return _reduce_scatter_rows(partial.contiguous(), m, group)
     assert mode == "alltoall", f"unknown expert-parallel mode {mode!r}"
+    _last_collective = "all-to-all of token rows and masked routing (dispatch) + all-to-all of partial rows (combine)"
 
     ids_t, w_t = dispatch_tables(topk_ids, topk_weights, e_loc, world)
     send_x = hidden_states.unsqueeze(0).expand(world, m, h).contiguous()

@@ -119,9 +119,10 @@ def _awq_repacked(qweight: torch.Tensor, scales: torch.Tensor, qzeros: torch.Ten
                    lambda: repack_awq_for_kernel(qweight, scales, qzeros))
 
 
-def _make_cfg(m, h, i, e, k, dtype, wmode, activation, flags, block_tokens, routed_scaling) -> _lib.Cfg:
+def _make_cfg(m, h, i, e, k, dtype, wmode, activation, flags, block_tokens, routed_scaling,
+              n_global_experts=0) -> _lib.Cfg:
     return _lib.Cfg(C.sizeof(_lib.Cfg), m, h, i, e, k, dtype, wmode, _lib.LAYOUT_LAYER, activation, flags,
-                    block_tokens, routed_scaling, 0)
+                    block_tokens, routed_scaling, 0, n_global_experts)
 
 
 def _env_flags() -> int:
@@ -290,8 +291,11 @@ def fused_experts(
 
     if no_combine:
         flags |= _lib.FLAG_NO_COMBINE
+    if expert_map is not None:
+        assert expert_map.ndim == 1 and expert_map.numel() >= e, "expert_map must list every global expert"
     cfg = _make_cfg(m, h, i, e, k, dtype, wmode, _ACTS[activation], flags,
-                    block_tokens or _block_tokens_env(), float(routed_scaling_factor))
+                    block_tokens or _block_tokens_env(), float(routed_scaling_factor),
+                    expert_map.numel() if expert_map is not None else 0)
     out = torch.empty((m, k, h) if no_combine else (m, h), dtype=odt, device=dev)
     if m == 0:
         return out

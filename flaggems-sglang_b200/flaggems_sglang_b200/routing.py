@@ -91,7 +91,7 @@ def moe_align_block_size(topk_ids: torch.Tensor, block_size: int, num_experts: i
     with torch.cuda.device(dev):
         rc = lib.b200moe_align_block_size(
             ids.data_ptr(), int(ids.dtype == torch.int64), n_slots, num_experts, block_size,
-            emap.data_ptr() if emap is not None else None,
+            emap.data_ptr() if emap is not None else None, emap.numel() if emap is not None else 0,
             sorted_ids.data_ptr(), expert_ids.data_ptr(), num_post.data_ptr(), _stream_ptr(dev))
     _lib.check(rc, "moe_align_block_size")
     return sorted_ids, expert_ids, num_post

@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define B200MOE_VERSION 1
+#define B200MOE_VERSION 2
 
 /* status codes */
 #define B200MOE_OK 0
@@ -83,6 +83,8 @@ typedef struct b200moe_cfg {
   int32_t block_tokens;   /* token block of the GEMMs: 0 = choose, else 16..256 */
   float routed_scaling;   /* output multiplier (1.0f for none)                  */
   int32_t num_sms;        /* 0 = query the current device                       */
+  int32_t n_global_experts; /* entries of expert_map (required > 0 when a map is passed); ids at or
+                             beyond it are dropped like ids the map sends to a negative value      */
 } b200moe_cfg;
 
 /* scales / zero points for the quantised weight modes and the optional per-expert biases
@@ -126,13 +128,15 @@ size_t b200moe_workspace_bytes(const b200moe_cfg *cfg);
  *   expert_ids[ceil(cap/block)]  expert of each block; tail = -1
  *   num_tokens_post_padded[1]
  * cap = b200moe_align_capacity(n_slots, n_experts, block).  expert_map (may be
- * NULL) maps ids to local experts, negative = not local (slot dropped).
+ * NULL; expert_map_len entries) maps global ids to local experts, negative = not
+ * local (slot dropped); ids outside [0, expert_map_len) are dropped too.
  */
 int b200moe_align_capacity(int n_slots, int n_experts, int block);
 int b200moe_align_block_size(const void *topk_ids, int ids_are_i64, int n_slots,
                              int n_experts, int block, const int32_t *expert_map,
-                             int32_t *sorted_token_ids, int32_t *expert_ids,
-                             int32_t *num_tokens_post_padded, void *stream);
+                             int expert_map_len, int32_t *sorted_token_ids,
+                             int32_t *expert_ids, int32_t *num_tokens_post_padded,
+                             void *stream);
 
 /*
  * top-k -> routing tables.  Replaces _standard_topk_to_triton_kernels
@@ -186,6 +190,9 @@ int b200moe_forward_topk(const b200moe_cfg *cfg, const void *x, const void *w1,
  *   - Every call on a device uses the same array and finds the previous call's
  *     contents in it; the call re-initialises all it reads.  Two calls that
  *     overlap on the GPU (different streams) race on the array: serialise them.
+ *   - The looked-up address is kept for the life of the process.  After
+ *     cudaDeviceReset (or any teardown of the device's primary context) it no
+ *     longer points at the array: unload and reload the library before calling again.
  */
 #define B200MOE_NOALLOC_SCRATCH_BYTES (16 * 1024 * 1024)
 int b200moe_forward_topk_noalloc(const b200moe_cfg *cfg, const void *x, const void *w1,
@@ -269,6 +276,26 @@ int b200moe_per_token_group_quant_fp8(const void *x, int dtype, int rows, int K,
  */
 int b200moe_profile_begin(int max_calls);
 int b200moe_profile_end(double *gemm1_ms, double *gemm2_ms, double *total_ms, int *calls);
+
+/*
+ * Launch accounting for benchmarks (no counterpart in the reference): the number of
+ * kernels this library has launched since it was loaded, and the kernels of the most
+ * recent forward call as a comma-separated list (truncated to names_bytes - 1
+ * characters).  Returns the number of kernels in that list.
+ */
+int b200moe_launch_stats(long long *total_launches, char *last_call_names, size_t names_bytes);
+
+/*
+ * Self-test of the device-side time-out path (no counterpart in the reference, which has no
+ * bounded waits).  Launches a one-CTA kernel in which one warp waits, for at most limit_ns
+ * (1 .. 100 000 000), on a barrier nobody arrives on, and a second warp waits on the same
+ * barrier with a limit a thousand times longer.  The first wait must run out, raise the CTA's
+ * abort flag and so release the second; the kernel returns normally and writes the time-out
+ * code 105 into *status (device int32, left alone if already non-zero).  observed (device
+ * int32[3]): [0] = 0 when the short wait ran out, [1] = 0 when the long wait was released by
+ * the flag, [2] = microseconds the second warp waited.  Nothing faults, traps or hangs.
+ */
+int b200moe_selftest_timeout(uint64_t limit_ns, int32_t *status, int32_t *observed, void *stream);
 
 #ifdef __cplusplus
 }

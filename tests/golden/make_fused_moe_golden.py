@@ -7,38 +7,31 @@ anywhere).
 
 Needs a GPU, the unmodified reference installed under baseline/_ref
 (`pip install --no-deps --target baseline/_ref <reference tree>`) and the
-`triton_kernels` package bundled in the installed vllm wheel.
+`triton_kernels` package bundled in the installed vllm wheel (baseline/ref_shim.py).
+From M = 1024 on the file keeps every 16th token row of the output.
 
     python tests/golden/make_fused_moe_golden.py [out.npz]
 """
-import importlib
-import os
 import sys
-import types
 from pathlib import Path
 
 import numpy as np
 
 ROOT = Path(__file__).resolve().parent.parent.parent
-os.environ["DNN_VENDOR"] = "nvidia"
-sys.path.insert(0, str(ROOT / "baseline" / "_ref"))
-import vllm.third_party.triton_kernels as tk  # noqa: E402
+sys.path.insert(0, str(ROOT / "baseline"))
+from ref_shim import load_reference  # noqa: E402
 
-sys.modules["triton_kernels"] = tk
-for sub in ("matmul_ogs", "routing", "numerics", "swiglu"):
-    sys.modules["triton_kernels." + sub] = importlib.import_module("vllm.third_party.triton_kernels." + sub)
-stub = types.ModuleType("sgl_kernel")
-stub.gelu_and_mul = lambda x, out: None
-sys.modules["sgl_kernel"] = stub
+flaggems_sglang, _standard_topk_to_triton_kernels = load_reference()   # the reference, from baseline/_ref
 
 import torch  # noqa: E402
-import flaggems_sglang  # noqa: E402  (the reference, from baseline/_ref)
-from flaggems_sglang.ops.fused_moe import _standard_topk_to_triton_kernels  # noqa: E402
 
-assert "baseline" in flaggems_sglang.__file__, flaggems_sglang.__file__
+# from M = 1024 on only every 16th token row is kept (the whole outputs would add tens of MB)
+ROW_STRIDE_FROM = 1024
+ROW_STRIDE = 16
 
 SHAPES = [(1, 128, 256, 8, 2), (7, 128, 256, 8, 2), (33, 256, 512, 16, 4),
-          (1, 1280, 3072, 64, 8), (4, 1280, 3072, 64, 8), (17, 1280, 3072, 64, 8), (64, 1280, 3072, 64, 8)]
+          (1, 1280, 3072, 64, 8), (4, 1280, 3072, 64, 8), (17, 1280, 3072, 64, 8), (64, 1280, 3072, 64, 8),
+          (1024, 1280, 3072, 64, 8), (2048, 1280, 3072, 64, 8), (4096, 1280, 3072, 64, 8)]
 
 dev = torch.device("cuda:0")
 out = {}
@@ -60,7 +53,10 @@ for shape in SHAPES:
         res = flaggems_sglang.triton_kernel_fused_experts(x.to(dev), w1.to(dev), w2.to(dev), rd, gi, si,
                                                           apply_router_weight_on_input=gate_in)
         torch.cuda.synchronize()
-        out[key + ("/gate_in" if gate_in else "/out")] = res.cpu().view(torch.int16).numpy()
+        if M >= ROW_STRIDE_FROM:
+            out[key + f"/out_rows{ROW_STRIDE}"] = res[::ROW_STRIDE].contiguous().cpu().view(torch.int16).numpy()
+        else:
+            out[key + ("/gate_in" if gate_in else "/out")] = res.cpu().view(torch.int16).numpy()
     print(key, "ok", float(res.float().abs().max()))
 
 dst = Path(sys.argv[1]) if len(sys.argv) > 1 else Path(__file__).resolve().parent / "fused_moe_ref_golden.npz"

@@ -29,7 +29,7 @@ def test_binding_covers_header(built_lib):
     from flaggems_sglang_b200 import _lib
     assert sorted(_lib.SYMBOLS) == _declared_symbols()
     assert built_lib.b200moe_version() == _lib.VERSION
-    assert C.sizeof(_lib.Cfg) == 14 * 4
+    assert C.sizeof(_lib.Cfg) == 15 * 4
 
 
 @pytest.mark.parametrize("p,e,b", [(0, 8, 16), (2, 8, 16), (128, 8, 64), (8192, 8, 256), (2048, 128, 16),

@@ -58,18 +58,29 @@ def test_fused_moe_reference_shapes(cuda_device, shape):
 GOLD = np.load(GOLDEN / "fused_moe_ref_golden.npz")
 
 
+# Fraction of elements that must be bit-identical to the reference's recorded output, per shape
+# (floors a little below what this build measures on a B200; a regression that corrupts a tile
+# of a large tensor shows up here long before it moves the tolerance check).
+BIT_EQUAL_FLOOR = {}
+BIT_EQUAL_DEFAULT = 0.85
+
+
 @pytest.mark.parametrize("key", sorted(GOLD.files))
 def test_against_reference_outputs(cuda_device, key):
     """Outputs of the reference's own Triton op recorded on a B200
-    (tests/golden/make_fused_moe_golden.py), same seeded inputs."""
+    (tests/golden/make_fused_moe_golden.py), same seeded inputs.  From M = 1024 on the file
+    holds every 16th token row."""
     name, which = key.split("/")
     shape = tuple(int(p.lstrip("MKNEtopk")) for p in name.split("_"))
     M, K, N, E, topk = shape
     x, w1, w2, tw, ids = _ref_inputs(*shape, cuda_device)
     out = _run_reference_api(x, w1, w2, tw, ids, E, cuda_device, apply_router_weight_on_input=(which == "gate_in"))
+    if which.startswith("out_rows"):
+        out = out[::int(which[len("out_rows"):])]
     gold = torch.from_numpy(GOLD[key]).view(torch.bfloat16)
-    assert_parity(out, gold, what=key)
-    assert bit_equal_fraction(out, gold) >= 0.85, f"{key}: only {bit_equal_fraction(out, gold):.3f} bit-identical"
+    st = assert_parity(out, gold, what=key)
+    floor = BIT_EQUAL_FLOOR.get(key, BIT_EQUAL_DEFAULT)
+    assert st["bit_equal"] >= floor, f"{key}: only {st['bit_equal']:.4f} bit-identical (floor {floor})"
 
 
 @pytest.mark.parametrize("shape", REF_SMALL, ids=lambda s: "M%d_K%d_N%d_E%d_topk%d" % s)
