@@ -422,10 +422,11 @@ def expert_parallel_leg(args, dev, rank, local_rank, world, dist, barrier):
     _lib.check(lib.b200moe_profile_begin(steps), "profile_begin")
     for _ in range(steps):
         step()
-    g1, g2, tot, calls = C.c_double(), C.c_double(), C.c_double(), C.c_int()
-    _lib.check(lib.b200moe_profile_end(C.byref(g1), C.byref(g2), C.byref(tot), C.byref(calls)), "profile_end")
+    g1, g2, tot, loc, calls = C.c_double(), C.c_double(), C.c_double(), C.c_double(), C.c_int()
+    _lib.check(lib.b200moe_profile_end(C.byref(g1), C.byref(g2), C.byref(tot), C.byref(loc), C.byref(calls)),
+               "profile_end")
     n = max(1, calls.value)
-    local_ms = tot.value / n
+    local_ms = loc.value / n
     if dist:
         t = torch.tensor([local_ms, g1.value / n + g2.value / n], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -493,7 +494,7 @@ def run_ours(args, rank, local_rank, world):
     for _ in range(args.steps):
         step()
     g1, g2, tot, calls = C.c_double(), C.c_double(), C.c_double(), C.c_int()
-    _lib.check(lib.b200moe_profile_end(C.byref(g1), C.byref(g2), C.byref(tot), C.byref(calls)), "profile_end")
+    _lib.check(lib.b200moe_profile_end(C.byref(g1), C.byref(g2), C.byref(tot), None, C.byref(calls)), "profile_end")
     n_calls = max(1, calls.value)
     g1_ms, g2_ms, tot_ms = g1.value / n_calls, g2.value / n_calls, tot.value / n_calls
 

@@ -5,6 +5,7 @@
 #include <vector>
 
 #include "align.cuh"
+#include "ep.cuh"
 #include "gemm.cuh"
 #include "prep.cuh"
 #include "router.cuh"
@@ -80,11 +81,14 @@ struct Profile {
   bool on = false;
   int max_calls = 0, calls = 0;
   std::vector<cudaEvent_t> ev;  // kMarks events per call
+  std::vector<char> local_marked;  // per call: marks 6 and 7 were recorded
 };
 Profile g_prof;
 
-// mark index: 0 = call start, 1 = before GEMM-1, 2 = after GEMM-1, 3 = before GEMM-2, 4 = after GEMM-2, 5 = call end
-constexpr int kMarks = 6;
+// mark index: 0 = call start, 1 = before GEMM-1, 2 = after GEMM-1, 3 = before GEMM-2, 4 = after GEMM-2, 5 = call end,
+// 6 / 7 = start / end of the local operator of an expert-parallel call (after the peers' rows have
+// arrived; after the down projection has completed)
+constexpr int kMarks = 8;
 
 int prof_slot() {
   if (!g_prof.on) return -1;
@@ -92,8 +96,17 @@ int prof_slot() {
   if (!g_prof.on || g_prof.calls >= g_prof.max_calls) return -1;
   return g_prof.calls++;
 }
+// The slot of the call in progress: the later phases of an expert-parallel call that was started
+// by an earlier b200moe_ep_forward(phases = dispatch) continue in the slot that call took.
+int prof_slot_current() {
+  if (!g_prof.on) return -1;
+  std::lock_guard<std::mutex> lk(g_prof.mu);
+  return g_prof.calls > 0 ? g_prof.calls - 1 : -1;
+}
 void prof_mark(int slot, int mark, cudaStream_t st) {
-  if (slot >= 0) cudaEventRecord(g_prof.ev[static_cast<size_t>(slot) * kMarks + mark], st);
+  if (slot < 0) return;
+  cudaEventRecord(g_prof.ev[static_cast<size_t>(slot) * kMarks + mark], st);
+  if (mark == 7) g_prof.local_marked[slot] = 1;
 }
 
 // Launch accounting (see common.cuh: note_launch).
@@ -221,8 +234,10 @@ int make_layout(const b200moe_cfg* c, Layout* L) {
   // to the pairs' validity bytes.  16-bit weights: only where the reference, too, rounds each
   // pair's row to the 16-bit type (or its rounding is not asked for).
   const int sms_l = query_sms(c);
+  // (16-bit: from four waves of tiles on; below that the split reduction, which needs the atomics,
+  // is what keeps the last wave full)
   const bool many_tiles = (static_cast<long long>(L->P) / L->BT) * ((c->H + 255) / 256) >=
-                          (fp8 ? 2LL : 1LL) * sms_l;
+                          (fp8 ? 2LL : 4LL) * sms_l;
   const bool pairs_ok16 = !fp8 && !L->w4p && L->orient == 1 &&
                           (!(c->flags & B200MOE_FLAG_MIMIC_ROUNDING) ||
                            reference_rounds_pairs(L->P, c->E, c->H, c->I, sms_l));
@@ -305,10 +320,21 @@ int align_into_workspace(const b200moe_cfg* c, const Layout& L, uint8_t* ws, con
                             row_gamma, blk_off, meta, st);
 }
 
-// Everything after the internal routing tables exist in the workspace.
+// Expert parallelism: where the down projection's output rows go (the buffers of the ranks that
+// own the tokens) instead of this call's workspace.
+struct PeerOut {
+  int n_peers = 0;
+  int tokens_per_peer = 0;             // m_cap: rows of a rank's fp32 buffer; its pair rows: m_cap * topk
+  void* out32[kMaxPeers] = {};
+  void* pairs[kMaxPeers] = {};
+  uint8_t* pair_valid[kMaxPeers] = {};
+};
+
+// Everything after the internal routing tables exist in the workspace.  With `peers` the results
+// land on their owners and nothing is cleared or converted here.
 int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void* w1, const void* w2,
                 const b200moe_quant* quant, uint8_t* ws, void* out, int32_t* status, cudaStream_t st,
-                int slot) {
+                int slot, const PeerOut* peers = nullptr) {
   const int sms = query_sms(c);
   int* meta = reinterpret_cast<int*>(ws + L.meta);
   int* blk_off = reinterpret_cast<int*>(ws + L.blk_off);
@@ -326,8 +352,9 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
   // cleared alongside the first row mover: the fp32 combine buffer, or the pairs' validity bytes
   // when rows are stored per pair
   void* zero = L.pair_rows ? static_cast<void*>(ws + L.pair_valid) : static_cast<void*>(out32);
-  const size_t zero_bytes = L.pair_rows ? align_up(static_cast<size_t>(L.P), 16)
-                                        : static_cast<size_t>(L.out_rows) * c->H * 4;
+  size_t zero_bytes = L.pair_rows ? align_up(static_cast<size_t>(L.P), 16)
+                                  : static_cast<size_t>(L.out_rows) * c->H * 4;
+  if (peers != nullptr) zero_bytes = 0;   // the owners cleared their buffers before they signalled "ready"
   if (fp8) {
     if (quant == nullptr || quant->w1_scale == nullptr || quant->w2_scale == nullptr) return B200MOE_ERR_BAD_ARG;
     if (c->flags & B200MOE_FLAG_X_FP8) {
@@ -429,6 +456,24 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
     g2.pair_valid = ws + L.pair_valid;
     g2.flags |= B200MOE_FLAG_NO_SPLIT_K;
   }
+  if (peers != nullptr) {
+    if (!fp8 || (c->flags & (B200MOE_FLAG_NO_COMBINE | B200MOE_FLAG_SIMT))) return B200MOE_ERR_UNSUPPORTED;
+    g2.n_peers = peers->n_peers;
+    g2.rows_per_peer = L.pair_rows ? peers->tokens_per_peer * c->topk : peers->tokens_per_peer;
+    for (int r = 0; r < peers->n_peers; ++r) {
+      g2.peer_out[r] = L.pair_rows ? peers->pairs[r] : peers->out32[r];
+      g2.peer_valid[r] = peers->pair_valid[r];
+    }
+    // with a single rank the "peer" is this GPU's own heap: plain local addressing through the same fields
+    if (peers->n_peers == 1) {
+      if (L.pair_rows) {
+        g2.out_pairs = peers->pairs[0];
+        g2.pair_valid = peers->pair_valid[0];
+      } else {
+        g2.out = peers->out32[0];
+      }
+    }
+  }
   if (fp8) {
     g2.w_scale = quant->w2_scale;
     g2.w_scale_rows = (c->H + 127) / 128;
@@ -489,6 +534,7 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
     prof_mark(slot, 4, st);
     if (rc != B200MOE_OK) return rc;
   }
+  if (peers != nullptr) return B200MOE_OK;   // the owners convert what arrived, after the peers' "done" flags
   if (L.pair_rows)
     rc = launch_finalize_pairs(ws + L.pairs, ws + L.pair_valid, out, c->dtype, c->M, c->topk, c->H,
                                c->routed_scaling, sms, st, pdl);
@@ -721,11 +767,191 @@ int b200moe_forward_topk_noalloc(const b200moe_cfg* cfg, const void* x, const vo
                               static_cast<size_t>(B200MOE_NOALLOC_SCRATCH_BYTES), out, status, stream);
 }
 
+// ---------------------------------------------------------------------------------------
+// Expert parallelism over peer-mapped heaps (ep.cuh).
+namespace {
+
+int check_ep(const b200moe_cfg* cfg, const b200moe_ep_cfg* ep) {
+  int rc = check_cfg(cfg);
+  if (rc != B200MOE_OK) return rc;
+  if (ep == nullptr || ep->struct_bytes != static_cast<int32_t>(sizeof(b200moe_ep_cfg))) return B200MOE_ERR_BAD_ARG;
+  if (ep->world < 1 || ep->world > kMaxPeers || ep->rank < 0 || ep->rank >= ep->world) return B200MOE_ERR_BAD_ARG;
+  if (ep->m_cap <= 0 || cfg->M > ep->m_cap || ep->n_global_experts <= 0) return B200MOE_ERR_BAD_ARG;
+  if (cfg->wmode != B200MOE_W_FP8_BLOCK) return B200MOE_ERR_UNSUPPORTED;   // rows travel as e4m3 + 1x128 scales
+  if (cfg->flags & (B200MOE_FLAG_X_FP8 | B200MOE_FLAG_NO_COMBINE | B200MOE_FLAG_SIMT)) return B200MOE_ERR_UNSUPPORTED;
+  if (cfg->topk > 32 || cfg->E > 0xffff) return B200MOE_ERR_UNSUPPORTED;
+  if (static_cast<long long>(ep->world) * ep->m_cap * cfg->topk > (1LL << 24)) return B200MOE_ERR_TOO_LARGE;
+  return B200MOE_OK;
+}
+
+// The local operator's view: every row of every source rank (masked routing entries drop what
+// is not for this rank), activations already quantised.
+b200moe_cfg ep_local_cfg(const b200moe_cfg* cfg, const b200moe_ep_cfg* ep) {
+  b200moe_cfg c = *cfg;
+  // token block from the real load (M_global * topk over all experts), not from the row capacity
+  b200moe_cfg load = *cfg;
+  load.M = ep->m_cap;
+  load.block_tokens = cfg->block_tokens;
+  c.block_tokens = pick_bt(&load);
+  c.M = ep->world * ep->m_cap;
+  c.flags |= B200MOE_FLAG_X_FP8;
+  c.n_global_experts = 0;
+  return c;
+}
+
+}  // namespace
+
+size_t b200moe_ep_heap_bytes(const b200moe_cfg* cfg, const b200moe_ep_cfg* ep) {
+  if (check_ep(cfg, ep) != B200MOE_OK) return 0;
+  return ep_heap_layout(ep->world, ep->m_cap, cfg->H, cfg->topk, true).total;
+}
+
+size_t b200moe_ep_workspace_bytes(const b200moe_cfg* cfg, const b200moe_ep_cfg* ep) {
+  if (check_ep(cfg, ep) != B200MOE_OK) return 0;
+  const b200moe_cfg c = ep_local_cfg(cfg, ep);
+  Layout L;
+  if (make_layout(&c, &L) != B200MOE_OK) return 0;
+  return L.total;
+}
+
+int b200moe_ep_heap_alloc(size_t bytes, void** heap) {
+  if (heap == nullptr || bytes == 0) return B200MOE_ERR_BAD_ARG;
+  void* p = nullptr;
+  if (cudaMalloc(&p, bytes) != cudaSuccess) return B200MOE_ERR_CUDA;
+  if (cudaMemset(p, 0, bytes) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
+    cudaFree(p);
+    return B200MOE_ERR_CUDA;
+  }
+  *heap = p;
+  return B200MOE_OK;
+}
+
+int b200moe_ep_heap_free(void* heap) {
+  if (heap == nullptr) return B200MOE_OK;
+  return cudaFree(heap) == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
+}
+
+int b200moe_ep_ipc_export(void* heap, void* handle64) {
+  if (heap == nullptr || handle64 == nullptr) return B200MOE_ERR_BAD_ARG;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, heap) != cudaSuccess) return B200MOE_ERR_CUDA;
+  memcpy(handle64, &h, sizeof(h));
+  return B200MOE_OK;
+}
+
+int b200moe_ep_ipc_open(const void* handle64, void** peer_heap) {
+  if (handle64 == nullptr || peer_heap == nullptr) return B200MOE_ERR_BAD_ARG;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  void* p = nullptr;
+  if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) return B200MOE_ERR_CUDA;
+  *peer_heap = p;
+  return B200MOE_OK;
+}
+
+int b200moe_ep_ipc_close(void* peer_heap) {
+  if (peer_heap == nullptr) return B200MOE_OK;
+  return cudaIpcCloseMemHandle(peer_heap) == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
+}
+
+int b200moe_ep_forward(const b200moe_cfg* cfg, const b200moe_ep_cfg* ep, void* const* heaps, int phases,
+                       const void* x, const void* w1, const void* w2, const b200moe_quant* quant,
+                       const float* topk_weights, const void* topk_ids, const int32_t* placement,
+                       void* workspace, size_t workspace_bytes, void* out, int32_t* status, void* stream) {
+  int rc = check_ep(cfg, ep);
+  if (rc != B200MOE_OK) return rc;
+  if (!heaps || !w1 || !w2 || !quant || !quant->w1_scale || !quant->w2_scale || !workspace || !status)
+    return B200MOE_ERR_BAD_ARG;
+  if ((phases & ~7) != 0 || phases == 0) return B200MOE_ERR_BAD_ARG;
+  for (int r = 0; r < ep->world; ++r)
+    if (heaps[r] == nullptr || (reinterpret_cast<uintptr_t>(heaps[r]) & 255) != 0) return B200MOE_ERR_BAD_ARG;
+  const b200moe_cfg c = ep_local_cfg(cfg, ep);
+  Layout L;
+  if ((rc = make_layout(&c, &L)) != B200MOE_OK) return rc;
+  if (workspace_bytes < L.total || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0) return B200MOE_ERR_WORKSPACE;
+  const EpHeap H = ep_heap_layout(ep->world, ep->m_cap, cfg->H, cfg->topk, true);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+  uint8_t* me = reinterpret_cast<uint8_t*>(heaps[ep->rank]);
+  const bool pdl = (cfg->flags & B200MOE_FLAG_NO_PDL) == 0;
+  const int sms = query_sms(cfg);
+  const unsigned long long limit_ns = ep->wait_limit_ns > 0 ? ep->wait_limit_ns : kWaitLimitNs;
+  int slot = -1;
+  if (phases & B200MOE_EP_PHASE_DISPATCH) {
+    if (!x || !topk_weights || !topk_ids || !placement) return B200MOE_ERR_BAD_ARG;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) != 0) return B200MOE_ERR_BAD_ARG;
+    launch_log_new_call();
+    slot = prof_slot();
+    prof_mark(slot, 0, st);
+    EpDispatchArgs d = {};
+    d.world = ep->world;
+    d.rank = ep->rank;
+    d.m = cfg->M;
+    d.m_cap = ep->m_cap;
+    d.H = cfg->H;
+    d.topk = cfg->topk;
+    d.n_global_experts = ep->n_global_experts;
+    d.dtype = cfg->dtype;
+    d.fp8_rows = 1;
+    d.ids_i64 = (cfg->flags & B200MOE_FLAG_IDS_I64) ? 1 : 0;
+    d.clear_pairs = L.pair_rows ? 1 : 0;
+    d.x = x;
+    d.topk_weights = topk_weights;
+    d.topk_ids = topk_ids;
+    d.placement = placement;
+    for (int r = 0; r < ep->world; ++r) d.heap[r] = reinterpret_cast<uint8_t*>(heaps[r]);
+    d.L = H;
+    if ((rc = launch_ep_dispatch(d, sms, st, pdl)) != B200MOE_OK) return rc;
+  }
+  if (phases & B200MOE_EP_PHASE_COMPUTE) {
+    if (slot < 0 && (phases & B200MOE_EP_PHASE_DISPATCH) == 0) slot = prof_slot_current();
+    if ((rc = launch_ep_wait(me, H, kEpFlagReady, ep->world, limit_ns, status, st, pdl)) != B200MOE_OK) return rc;
+    prof_mark(slot, 6, st);
+    // alignment over every received row: ids are already local (or -1), weights already masked
+    rc = align_into_workspace(&c, L, ws, me + H.recv_ids, 0, nullptr, reinterpret_cast<const float*>(me + H.recv_w), st);
+    if (rc != B200MOE_OK) return rc;
+    b200moe_quant q = *quant;
+    q.x_scale = reinterpret_cast<const float*>(me + H.recv_xs);
+    PeerOut po;
+    po.n_peers = ep->world;
+    po.tokens_per_peer = ep->m_cap;
+    for (int r = 0; r < ep->world; ++r) {
+      uint8_t* h = reinterpret_cast<uint8_t*>(heaps[r]);
+      po.out32[r] = h + H.out32;
+      po.pairs[r] = h + H.pairs;
+      po.pair_valid[r] = h + H.pair_valid;
+    }
+    if ((rc = run_experts(&c, L, me + H.recv_x, w1, w2, &q, ws, nullptr, status, st, slot, &po)) != B200MOE_OK) return rc;
+    uint8_t* hp[kMaxPeers];
+    for (int r = 0; r < ep->world; ++r) hp[r] = reinterpret_cast<uint8_t*>(heaps[r]);
+    if ((rc = launch_ep_signal(hp, H, kEpFlagDone, ep->world, ep->rank, st, pdl)) != B200MOE_OK) return rc;
+    prof_mark(slot, 7, st);
+  }
+  if (phases & B200MOE_EP_PHASE_COMBINE) {
+    if (!out || (reinterpret_cast<uintptr_t>(out) & 15) != 0) return B200MOE_ERR_BAD_ARG;
+    if (slot < 0 && (phases & B200MOE_EP_PHASE_DISPATCH) == 0) slot = prof_slot_current();
+    if ((rc = launch_ep_wait(me, H, kEpFlagDone, ep->world, limit_ns, status, st, pdl)) != B200MOE_OK) return rc;
+    if (cfg->M > 0) {
+      if (L.pair_rows)
+        rc = launch_finalize_pairs(me + H.pairs, me + H.pair_valid, out, cfg->dtype, cfg->M, cfg->topk, cfg->H,
+                                   cfg->routed_scaling, sms, st, pdl);
+      else
+        rc = launch_finalize(reinterpret_cast<const float*>(me + H.out32), out, cfg->dtype,
+                             static_cast<size_t>(cfg->M) * cfg->H, cfg->routed_scaling, sms, st, pdl);
+      if (rc != B200MOE_OK) return rc;
+    }
+    prof_mark(slot, 5, st);
+  }
+  return B200MOE_OK;
+}
+
 int b200moe_profile_begin(int max_calls) {
   if (max_calls <= 0 || max_calls > 4096) return B200MOE_ERR_BAD_ARG;
   std::lock_guard<std::mutex> lk(g_prof.mu);
   for (cudaEvent_t e : g_prof.ev) cudaEventDestroy(e);
   g_prof.ev.assign(static_cast<size_t>(max_calls) * kMarks, nullptr);
+  g_prof.local_marked.assign(static_cast<size_t>(max_calls), 0);
   for (auto& e : g_prof.ev)
     if (cudaEventCreate(&e) != cudaSuccess) return B200MOE_ERR_CUDA;
   g_prof.max_calls = max_calls;
@@ -734,11 +960,11 @@ int b200moe_profile_begin(int max_calls) {
   return B200MOE_OK;
 }
 
-int b200moe_profile_end(double* gemm1_ms, double* gemm2_ms, double* total_ms, int* calls) {
+int b200moe_profile_end(double* gemm1_ms, double* gemm2_ms, double* total_ms, double* local_ms, int* calls) {
   std::lock_guard<std::mutex> lk(g_prof.mu);
   if (!g_prof.on) return B200MOE_ERR_BAD_ARG;
   g_prof.on = false;
-  double g1 = 0, g2 = 0, tot = 0;
+  double g1 = 0, g2 = 0, tot = 0, loc = 0;
   int rc = B200MOE_OK;
   for (int i = 0; i < g_prof.calls; ++i) {
     cudaEvent_t* e = &g_prof.ev[static_cast<size_t>(i) * kMarks];
@@ -749,7 +975,15 @@ int b200moe_profile_end(double* gemm1_ms, double* gemm2_ms, double* total_ms, in
       break;
     }
     g1 += a; g2 += b; tot += t;
+    // expert-parallel calls also mark their local operator; elsewhere the whole call is local
+    float l = t;
+    if (g_prof.local_marked[i] && cudaEventElapsedTime(&l, e[6], e[7]) != cudaSuccess) {
+      rc = B200MOE_ERR_CUDA;
+      break;
+    }
+    loc += l;
   }
+  if (local_ms) *local_ms = loc;
   if (gemm1_ms) *gemm1_ms = g1;
   if (gemm2_ms) *gemm2_ms = g2;
   if (total_ms) *total_ms = tot;

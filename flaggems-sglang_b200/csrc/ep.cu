@@ -1,0 +1,306 @@
+// Expert parallelism: the kernels that move rows and flags between ranks over peer-mapped memory.
+//
+// A forward call under expert parallelism is, on every rank,
+//   dispatch   this rank's tokens -> the ranks that hold their experts (plain peer stores of the
+//              quantised row, its scales and the masked routing entries), then "ready" flags;
+//   wait       until every peer's ready flag has arrived;
+//   local op   alignment, gather and the two grouped GEMMs over the rows received; the down
+//              projection's epilogue stores each pair's weighted row straight into the buffer of
+//              the rank that owns the token (gemm.cuh: out_row_base), so the combine needs no
+//              collective and overlaps the GEMM;
+//   signal     "done" flags to every peer once the GEMM has completed;
+//   wait       until every peer is done, then the output conversion sums the rows that arrived.
+// Flags are epochs that only grow, so nothing is ever reset while a peer may look at it; each
+// wait has a time limit and ends in the status word.  No load ever has a peer's memory as its
+// source except these flag polls of the rank's OWN heap: data moves by stores only.
+#include "ep.cuh"
+
+namespace b200moe {
+
+namespace {
+
+size_t up256(size_t v) { return (v + 255) / 256 * 256; }
+
+__device__ __forceinline__ void st_release_sys_u64(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_acquire_sys_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+template <typename T>
+__device__ __forceinline__ void load4f(const T* p, float (&v)[4]);
+template <>
+__device__ __forceinline__ void load4f<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[4]) {
+  uint2 raw = *reinterpret_cast<const uint2*>(p);
+  __nv_bfloat162 a = *reinterpret_cast<__nv_bfloat162*>(&raw.x);
+  __nv_bfloat162 b = *reinterpret_cast<__nv_bfloat162*>(&raw.y);
+  v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+}
+template <>
+__device__ __forceinline__ void load4f<__half>(const __half* p, float (&v)[4]) {
+  uint2 raw = *reinterpret_cast<const uint2*>(p);
+  __half2 a = *reinterpret_cast<__half2*>(&raw.x);
+  __half2 b = *reinterpret_cast<__half2*>(&raw.y);
+  v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+}
+
+constexpr int kDispatchWarps = 4;
+// staging of one quantised row: H bytes + H/128 scales, kept 16-byte aligned per warp
+__host__ __device__ inline size_t ep_stage_bytes(int H) { return static_cast<size_t>(H) + (((H >> 7) * 4 + 15) & ~15); }
+
+// One warp per token.  Shared memory per warp (FP8 rows): H bytes of quantised row + H/128 scales.
+template <typename T>
+__global__ void __launch_bounds__(kDispatchWarps * 32)
+ep_dispatch_kernel(const EpDispatchArgs a) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  __shared__ unsigned long long s_epoch;
+  __shared__ int s_last;
+  griddep_wait();
+  griddep_launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint8_t* me = a.heap[a.rank];
+  const int G = a.H >> 7;
+
+  // ---- this rank's result buffer starts empty (peers add to it / mark it only after they have seen
+  // this rank's ready flag, which is raised at the end of this kernel)
+  {
+    uint4* z = reinterpret_cast<uint4*>(me + (a.clear_pairs ? a.L.pair_valid : a.L.out32));
+    const long long n = a.clear_pairs ? (static_cast<long long>(a.m_cap) * a.topk + 15) / 16
+                                      : static_cast<long long>(a.m_cap) * a.H / 4;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+         i += static_cast<long long>(gridDim.x) * blockDim.x)
+      z[i] = make_uint4(0, 0, 0, 0);
+  }
+
+  uint8_t* stage = smem + static_cast<size_t>(warp) * (a.fp8_rows ? ep_stage_bytes(a.H) : 0);
+  float* stage_sc = reinterpret_cast<float*>(stage + a.H);
+  const int total_warps = gridDim.x * kDispatchWarps;
+  for (int i = blockIdx.x * kDispatchWarps + warp; i < a.m_cap; i += total_warps) {
+    // ---- where do this token's experts live?
+    int dr = -1, lid = -1;
+    float w = 0.f;
+    if (i < a.m && lane < a.topk) {
+      const long long gid = a.ids_i64 ? reinterpret_cast<const long long*>(a.topk_ids)[static_cast<size_t>(i) * a.topk + lane]
+                                      : reinterpret_cast<const int*>(a.topk_ids)[static_cast<size_t>(i) * a.topk + lane];
+      if (gid >= 0 && gid < a.n_global_experts) {
+        const int pl = a.placement[gid];
+        if (pl >= 0 && (pl >> 16) < a.world) {
+          dr = pl >> 16;
+          lid = pl & 0xffff;
+          w = a.topk_weights[static_cast<size_t>(i) * a.topk + lane];
+        }
+      }
+    }
+    // ---- routing entries, masked per destination; every rank gets a row for every token so that
+    // it never has to guess which rows arrived
+    unsigned dest_mask = 0;
+    const size_t row = static_cast<size_t>(a.rank) * a.m_cap + i;
+    for (int d = 0; d < a.world; ++d) {
+      const bool mine = dr == d;
+      if (__any_sync(0xffffffffu, mine)) dest_mask |= 1u << d;
+      if (lane < a.topk) {
+        reinterpret_cast<int*>(a.heap[d] + a.L.recv_ids)[row * a.topk + lane] = mine ? lid : -1;
+        reinterpret_cast<float*>(a.heap[d] + a.L.recv_w)[row * a.topk + lane] = mine ? w : 0.f;
+      }
+    }
+    if (dest_mask == 0) continue;
+    const T* xrow = reinterpret_cast<const T*>(a.x) + static_cast<size_t>(i) * a.H;
+    if (a.fp8_rows) {
+      // ---- 1x128 quantisation, the arithmetic of group_quant_fp8_kernel (prep.cu) so that a row
+      // carries the same bits whether it is quantised here or inside a single-GPU call
+      constexpr int RUN = 8;
+      for (int g0 = 0; g0 < G; g0 += RUN) {
+        float v[RUN][4];
+#pragma unroll
+        for (int u = 0; u < RUN; ++u) {
+          v[u][0] = v[u][1] = v[u][2] = v[u][3] = 0.f;
+          if (g0 + u < G) load4f<T>(xrow + (g0 + u) * 128 + lane * 4, v[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < RUN; ++u) {
+          const int g = g0 + u;
+          if (g >= G) break;
+          float amax = fmaxf(fmaxf(fabsf(v[u][0]), fabsf(v[u][1])), fmaxf(fabsf(v[u][2]), fabsf(v[u][3])));
+          amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(amax)));
+          const float s = __fdiv_rn(fmaxf(amax, 1e-10f), 448.0f);
+          uint32_t packed = 0;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            __nv_fp8_storage_t b = __nv_cvt_float_to_fp8(__fdiv_rn(v[u][q], s), __NV_SATFINITE, __NV_E4M3);
+            packed |= static_cast<uint32_t>(b) << (8 * q);
+          }
+          *reinterpret_cast<uint32_t*>(stage + g * 128 + lane * 4) = packed;
+          if (lane == 0) stage_sc[g] = s;
+        }
+      }
+      __syncwarp();
+      for (int d = 0; d < a.world; ++d) {
+        if (!(dest_mask & (1u << d))) continue;
+        uint4* dst = reinterpret_cast<uint4*>(a.heap[d] + a.L.recv_x + row * a.L.x_row_bytes);
+        const uint4* src = reinterpret_cast<const uint4*>(stage);
+        for (int c = lane; c < a.H / 16; c += 32) dst[c] = src[c];
+        float* dsc = reinterpret_cast<float*>(a.heap[d] + a.L.recv_xs) + row * G;
+        for (int g = lane; g < G; g += 32) dsc[g] = stage_sc[g];
+      }
+      __syncwarp();
+    } else {
+      const uint4* src = reinterpret_cast<const uint4*>(xrow);
+      for (int c0 = 0; c0 < a.H / 8; c0 += 32 * 4) {      // four 16-byte chunks per lane in flight
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int c = c0 + u * 32 + lane;
+          v[u] = (c < a.H / 8) ? __ldg(src + c) : make_uint4(0, 0, 0, 0);
+        }
+        for (int d = 0; d < a.world; ++d) {
+          if (!(dest_mask & (1u << d))) continue;
+          uint4* dst = reinterpret_cast<uint4*>(a.heap[d] + a.L.recv_x + row * a.L.x_row_bytes);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int c = c0 + u * 32 + lane;
+            if (c < a.H / 8) dst[c] = v[u];
+          }
+        }
+      }
+    }
+  }
+
+  // ---- the last CTA to get here opens a new epoch and tells every peer that this rank's rows
+  // are in place (each thread's stores are fenced before its CTA is counted)
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned int* cnt = reinterpret_cast<unsigned int*>(me + a.L.flags + kEpFlagCtaCount);
+    const unsigned int prev = atomicAdd(cnt, 1u);
+    s_last = (prev == gridDim.x - 1) ? 1 : 0;
+    if (s_last) {
+      *cnt = 0;
+      unsigned long long* ep = reinterpret_cast<unsigned long long*>(me + a.L.flags + kEpFlagEpoch);
+      s_epoch = *ep + 1;
+      *ep = s_epoch;
+      __threadfence_system();
+    }
+  }
+  __syncthreads();
+  if (s_last && threadIdx.x < a.world)
+    st_release_sys_u64(reinterpret_cast<unsigned long long*>(a.heap[threadIdx.x] + a.L.flags + kEpFlagReady) + a.rank,
+                       s_epoch);
+}
+
+__global__ void __launch_bounds__(32)
+ep_wait_kernel(const unsigned long long* flags, const unsigned long long* epoch_ptr, int world,
+               unsigned long long limit_ns, int* status) {
+  griddep_wait();
+  const unsigned long long want = *reinterpret_cast<const volatile unsigned long long*>(epoch_ptr);
+  if (threadIdx.x < world) {
+    const unsigned long long* f = flags + threadIdx.x;
+    unsigned long long t0 = 0;
+#pragma unroll 1
+    for (unsigned int spin = 0;; ++spin) {
+      if (ld_acquire_sys_u64(f) >= want) break;
+      if ((spin & 0x3f) == 0x3f) {
+        const unsigned long long now = globaltimer_ns();
+        if (t0 == 0) t0 = now;
+        if (now - t0 > limit_ns) {
+          atomicCAS(status, 0, static_cast<int>(DEV_TIMEOUT_PEER));
+          break;
+        }
+      }
+    }
+  }
+  __syncwarp();
+  griddep_launch_dependents();
+}
+
+struct EpSignalArgs {
+  uint8_t* heap[kMaxPeers];
+  size_t flags_off;   // offset of the flag array (ready or done) inside a heap
+  size_t epoch_off;   // offset of the epoch counter inside this rank's heap
+  int world, rank;
+};
+
+__global__ void __launch_bounds__(32)
+ep_signal_kernel(const EpSignalArgs a) {
+  griddep_wait();   // everything launched before in this stream has completed and is visible here
+  const unsigned long long e = *reinterpret_cast<const volatile unsigned long long*>(a.heap[a.rank] + a.epoch_off);
+  __threadfence_system();
+  if (threadIdx.x < a.world)
+    st_release_sys_u64(reinterpret_cast<unsigned long long*>(a.heap[threadIdx.x] + a.flags_off) + a.rank, e);
+  griddep_launch_dependents();
+}
+
+}  // namespace
+
+EpHeap ep_heap_layout(int world, int m_cap, int H, int topk, bool fp8_rows) {
+  EpHeap L;
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    size_t o = off;
+    off = up256(off + bytes);
+    return o;
+  };
+  const size_t rows = static_cast<size_t>(world) * m_cap;
+  L.x_row_bytes = fp8_rows ? H : 2 * H;
+  L.flags = take(256);
+  L.recv_ids = take(rows * topk * 4);
+  L.recv_w = take(rows * topk * 4);
+  L.recv_x = take(rows * L.x_row_bytes);
+  L.recv_xs = take(rows * ((H + 127) / 128) * 4);
+  L.pairs = take(static_cast<size_t>(m_cap) * topk * H * 2);
+  L.pair_valid = take((static_cast<size_t>(m_cap) * topk + 15) / 16 * 16);
+  L.out32 = take(static_cast<size_t>(m_cap) * H * 4);
+  L.total = off;
+  return L;
+}
+
+int launch_ep_dispatch(const EpDispatchArgs& a, int num_sms, cudaStream_t stream, bool pdl) {
+  if (a.world < 1 || a.world > kMaxPeers || a.rank < 0 || a.rank >= a.world || a.topk > 32) return B200MOE_ERR_BAD_ARG;
+  if (a.m < 0 || a.m > a.m_cap || a.H % 8 != 0 || (a.fp8_rows && a.H % 128 != 0)) return B200MOE_ERR_BAD_ARG;
+  const size_t smem = a.fp8_rows ? static_cast<size_t>(kDispatchWarps) * ep_stage_bytes(a.H) : 0;
+  if (smem > 200 * 1024) return B200MOE_ERR_TOO_LARGE;
+  int ctas = (a.m_cap + kDispatchWarps - 1) / kDispatchWarps;
+  if (ctas > num_sms * 4) ctas = num_sms * 4;
+  if (ctas < 1) ctas = 1;
+  cudaError_t err;
+  note_launch("ep_dispatch_kernel");
+  if (a.dtype == B200MOE_DTYPE_BF16) {
+    if (cudaFuncSetAttribute(ep_dispatch_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
+      return B200MOE_ERR_CUDA;
+    err = launch_kernel(ep_dispatch_kernel<__nv_bfloat16>, dim3(ctas), dim3(kDispatchWarps * 32), smem, stream, pdl, a);
+  } else {
+    if (cudaFuncSetAttribute(ep_dispatch_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem)) != cudaSuccess)
+      return B200MOE_ERR_CUDA;
+    err = launch_kernel(ep_dispatch_kernel<__half>, dim3(ctas), dim3(kDispatchWarps * 32), smem, stream, pdl, a);
+  }
+  return err == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
+}
+
+int launch_ep_wait(uint8_t* my_heap, const EpHeap& L, size_t flag_off, int world, unsigned long long limit_ns,
+                   int* status, cudaStream_t stream, bool pdl) {
+  note_launch("ep_wait_kernel");
+  cudaError_t err = launch_kernel(ep_wait_kernel, dim3(1), dim3(32), 0, stream, pdl,
+                                  reinterpret_cast<const unsigned long long*>(my_heap + L.flags + flag_off),
+                                  reinterpret_cast<const unsigned long long*>(my_heap + L.flags + kEpFlagEpoch), world,
+                                  limit_ns, status);
+  return err == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
+}
+
+int launch_ep_signal(uint8_t* const* heaps, const EpHeap& L, size_t flag_off, int world, int rank,
+                     cudaStream_t stream, bool pdl) {
+  EpSignalArgs a = {};
+  for (int r = 0; r < world; ++r) a.heap[r] = heaps[r];
+  a.flags_off = L.flags + flag_off;
+  a.epoch_off = L.flags + kEpFlagEpoch;
+  a.world = world;
+  a.rank = rank;
+  note_launch("ep_signal_kernel");
+  cudaError_t err = launch_kernel(ep_signal_kernel, dim3(1), dim3(32), 0, stream, pdl, a);
+  return err == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
+}
+
+}  // namespace b200moe

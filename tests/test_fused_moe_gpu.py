@@ -61,8 +61,14 @@ GOLD = np.load(GOLDEN / "fused_moe_ref_golden.npz")
 # Fraction of elements that must be bit-identical to the reference's recorded output, per shape
 # (floors a little below what this build measures on a B200; a regression that corrupts a tile
 # of a large tensor shows up here long before it moves the tolerance check).
-BIT_EQUAL_FLOOR = {}
-BIT_EQUAL_DEFAULT = 0.85
+BIT_EQUAL_FLOOR = {
+    "M1_K1280_N3072_E64_topk8/gate_in": 0.93,      # measured 0.953
+    "M1_K1280_N3072_E64_topk8/out": 0.995,         # measured 0.9992
+    "M4_K1280_N3072_E64_topk8/out": 0.99,          # measured 0.9986
+    "M33_K256_N512_E16_topk4/gate_in": 0.995,      # measured 0.9998
+    "M33_K256_N512_E16_topk4/out": 0.995,          # measured 0.9999
+}
+BIT_EQUAL_DEFAULT = 0.999                          # every other recorded shape: measured 1.0 (M = 17 ... 4096)
 
 
 @pytest.mark.parametrize("key", sorted(GOLD.files))
@@ -78,7 +84,7 @@ def test_against_reference_outputs(cuda_device, key):
     if which.startswith("out_rows"):
         out = out[::int(which[len("out_rows"):])]
     gold = torch.from_numpy(GOLD[key]).view(torch.bfloat16)
-    st = assert_parity(out, gold, what=key)
+    st = assert_parity(out, gold, what=key, strict=True)      # every element within rtol = atol = 1e-2
     floor = BIT_EQUAL_FLOOR.get(key, BIT_EQUAL_DEFAULT)
     assert st["bit_equal"] >= floor, f"{key}: only {st['bit_equal']:.4f} bit-identical (floor {floor})"
 
