@@ -97,10 +97,18 @@ class Layer:
         self.world = world
         self.ep_collective = None
         e_ids = range(self.e)
+        self.placement = None
         if self.ep:
+            # Load-balanced expert placement from the layer's own traffic statistics: a calibration batch
+            # (other tokens, same router bias) counts the tokens per expert, the experts are dealt out heaviest
+            # first to the least loaded rank.  The timed batch is not the calibration batch.
+            from flaggems_sglang_b200 import ep
+            from flaggems_sglang_b200.testing import make_tokens
             assert self.e % world == 0
-            e_loc = self.e // world
-            e_ids = range(rank * e_loc, (rank + 1) * e_loc)
+            _, _, cal_ids = make_tokens(8192, 64, self.e, self.k, seed=1234, skew=True, bias_seed=0)
+            load = torch.bincount(cal_ids.flatten().long(), minlength=self.e).tolist()
+            self.placement = ep.plan_placement(self.e, world, load if not os.environ.get("B200MOE_EP_CONTIGUOUS") else None)
+            e_ids = ep.local_experts(self.placement, rank)
         if self.fp8:
             from flaggems_sglang_b200.quant import quantize_fp8_block
             qs = [[], [], [], []]
@@ -112,6 +120,10 @@ class Layer:
                     lst.append(t)
             self.w13, self.s13, self.w2, self.s2 = (torch.cat(l, dim=0).contiguous() for l in qs)
             self.kw = dict(use_fp8_w8a8=True, w13_scale=self.s13, w2_scale=self.s2)
+            if self.ep:
+                self.kw.update(placement=self.placement, mode=os.environ.get("B200MOE_EP_MODE") or None)
+                if self.kw["mode"] in ("allgather", "alltoall"):
+                    self.kw["placement"] = None
             self.bytes_w = 1
         elif self.int4:
             from flaggems_sglang_b200.quant import quantize_awq, repack_awq_for_kernel
@@ -132,7 +144,8 @@ class Layer:
 
     def tokens(self, m, dev, seed):
         from flaggems_sglang_b200.testing import make_tokens
-        return make_tokens(m, self.h, self.e, self.k, dtype=self.act_dtype, device=dev, seed=seed, skew=self.fp8)
+        return make_tokens(m, self.h, self.e, self.k, dtype=self.act_dtype, device=dev, seed=seed, skew=self.fp8,
+                           bias_seed=0 if self.fp8 else None)
 
     def forward(self, x, tw, ids):
         if self.ep:
@@ -413,9 +426,16 @@ def expert_parallel_leg(args, dev, rank, local_rank, world, dist, barrier):
     del gx, gtw
     step = lambda: layer.forward(x, tw, ids)
     steps = max(5, min(args.steps, 20))
+    out_first = step()
+    torch.cuda.synchronize()
+    _ep_check_status(F)                       # a broken exchange shows here, after one call, not after a timed region
     with ClockSampler(physical_index(local_rank)) as clocks:
         regions = time_regions(step, steps, 3, barrier, dist, dev, clocks, min_total_s=0.5)
-    F.check_status()
+    _ep_check_status(F)
+    # this rank's rows of the result against the one-GPU operator's bits are checked in tests; here: finite and repeatable
+    again = step()
+    torch.cuda.synchronize()
+    repeatable = bool(torch.equal(out_first, again)) and bool(torch.isfinite(again.float()).all())
     med = statistics.median(r["ms"] for r in regions)
     # time inside this package's local operator (alignment to output conversion), from events the library records
     lib = _lib.lib()
@@ -437,7 +457,14 @@ def expert_parallel_leg(args, dev, rank, local_rank, world, dist, barrier):
     hit = int(torch.unique(gids).numel())
     b, f = algorithmic_work(h, i, k, m_global, hit, 1)
     ms_step = med / steps
-    res = {"workload": f"{name} H{h} I{i} E{e} top{k}, FP8 e4m3 128x128 block scales, zipf(1.1) routing skew, "
+    per_rank_pairs = None
+    if layer.placement is not None:
+        dest = (layer.placement.to(gids.device).long()[gids.long()] >> 16)
+        per_rank_pairs = torch.bincount(dest.flatten(), minlength=world).tolist()
+    res = {"placement": ("contiguous" if os.environ.get("B200MOE_EP_CONTIGUOUS") else
+                         "load-balanced from a calibration batch (8192 other tokens, same router bias)") if world > 1 else None,
+           "pairs_per_rank": per_rank_pairs, "repeatable_bits": repeatable,
+           "workload": f"{name} H{h} I{i} E{e} top{k}, FP8 e4m3 128x128 block scales, zipf(1.1) routing skew, "
                        f"global M {m_global} (seed 0), {e // world} experts and {m} tokens per rank",
            "collective": layer.ep_collective if world > 1 else "none (one GPU)",
            "ms_per_step": ms_step, "tokens_per_s": m_global / (ms_step / 1e3), "steps": steps,
@@ -449,6 +476,13 @@ def expert_parallel_leg(args, dev, rank, local_rank, world, dist, barrier):
     del layer
     torch.cuda.empty_cache()
     return res
+
+
+def _ep_check_status(F):
+    F.check_status()
+    from flaggems_sglang_b200 import ep
+    for ctx in ep._contexts.values():
+        ctx.check_status()
 
 
 def run_ours(args, rank, local_rank, world):
@@ -466,6 +500,16 @@ def run_ours(args, rank, local_rank, world):
         dist = dist_
         dist.init_process_group("nccl", device_id=dev)
     barrier = (lambda: dist.barrier()) if dist else None
+
+    if args.ep_only:
+        leg = expert_parallel_leg(args, dev, rank, local_rank, world, dist, barrier)
+        if rank == 0:
+            print(json.dumps({"ep_only": True, "n_gpus": world, "expert_parallel": leg}), flush=True)
+        if dist:
+            from flaggems_sglang_b200 import ep
+            ep.close_contexts()
+            dist.destroy_process_group()
+        return
 
     layer = Layer(args.workload, dev, rank, world)
     # expert parallelism: M is the global batch, split evenly; otherwise every rank has its own M tokens
@@ -693,6 +737,8 @@ def run_ours(args, rank, local_rank, world):
         }
         print(json.dumps(line), flush=True)
     if dist:
+        from flaggems_sglang_b200 import ep
+        ep.close_contexts()
         dist.destroy_process_group()
 
 
@@ -711,6 +757,7 @@ def main():
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-ep-leg", action="store_true", help="skip the expert-parallel DeepSeek-V3 leg")
+    ap.add_argument("--ep-only", action="store_true", help="development: run only the expert-parallel leg")
     ap.add_argument("--min-seconds", type=float, default=1.0, help="device time to accumulate over timed regions")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

@@ -917,7 +917,7 @@ int b200moe_ep_forward(const b200moe_cfg* cfg, const b200moe_ep_cfg* ep, void* c
     po.n_peers = ep->world;
     po.tokens_per_peer = ep->m_cap;
     for (int r = 0; r < ep->world; ++r) {
-      uint8_t* h = reinterpret_cast<uint8_t*>(heaps[r]);
+      uint8_t* h = reinterpret_cast<uint8_t*>(heaps[(cfg->flags & B200MOE_FLAG_EP_DIAG_LOCAL_COMBINE) ? ep->rank : r]);
       po.out32[r] = h + H.out32;
       po.pairs[r] = h + H.pairs;
       po.pair_valid[r] = h + H.pair_valid;

@@ -22,6 +22,7 @@ NOALLOC_SCRATCH_BYTES = 16 * 1024 * 1024
 FLAG_WEIGHT_ON_INPUT, FLAG_MIMIC_ROUNDING, FLAG_SIMT, FLAG_IDS_I64, FLAG_NO_SPLIT_K, \
     FLAG_NO_GRID_BALANCE, FLAG_NO_PDL, FLAG_W4_SMEM_OPERANDS, FLAG_NO_COMBINE, FLAG_ALIGN_ONE_CTA, FLAG_X_FP8 = \
     1, 2, 4, 8, 16, 32, 64, 128, 256, 512, 1024
+FLAG_EP_DIAG_LOCAL_COMBINE = 2048
 
 
 class Cfg(C.Structure):

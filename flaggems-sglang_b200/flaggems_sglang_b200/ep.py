@@ -303,8 +303,11 @@ def peer_context(group, m_cap, h, i, topk, n_local, n_global, device, dtype) -> 
     key = (id(group), m_cap, h, i, topk, n_local, n_global, str(device), dtype)
     ctx = _contexts.get(key)
     if ctx is None:
+        import os
+        from . import _lib
+        flags = _lib.FLAG_EP_DIAG_LOCAL_COMBINE if os.environ.get("B200MOE_EP_DIAG_LOCAL_COMBINE") == "1" else 0
         ctx = EpContext(dist.get_rank(group), dist.get_world_size(group), m_cap, h, i, topk, n_local, n_global,
-                        device, dtype=dtype, group=group)
+                        device, dtype=dtype, group=group, flags=flags)
         _contexts[key] = ctx
     return ctx
 

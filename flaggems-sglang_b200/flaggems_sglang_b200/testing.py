@@ -61,11 +61,15 @@ def make_weights(h: int, i: int, e: int, dtype=torch.bfloat16, device="cpu", sca
     return w13, w2
 
 
-def make_tokens(m: int, h: int, e: int, topk: int, dtype=torch.bfloat16, device="cpu", seed=0, skew=False):
+def make_tokens(m: int, h: int, e: int, topk: int, dtype=torch.bfloat16, device="cpu", seed=0, skew=False,
+                bias_seed=None):
+    """Tokens and their routing.  ``skew``: the router's logits carry the layer's zipf bias, drawn from
+    ``bias_seed`` (default: ``seed``) -- two batches with different ``seed`` and the same ``bias_seed``
+    are different traffic through the same layer."""
     g = torch.Generator(device=device).manual_seed(seed + 1)
     x = torch.randn(m, h, generator=g, device=device, dtype=torch.float32).to(dtype)
     logits = torch.randn(m, e, generator=g, device=device, dtype=torch.float32)
     if skew:
-        logits = logits + zipf_bias(e, 1.1, seed).to(device)
+        logits = logits + zipf_bias(e, 1.1, seed if bias_seed is None else bias_seed).to(device)
     w, ids = route(logits, topk)
     return x, w, ids

@@ -63,6 +63,8 @@ extern "C" {
                                            1 x 128 group with scales quant->x_scale [M, H/128] (what
                                            b200moe_per_token_group_quant_fp8 writes); cfg->dtype still
                                            names the 16-bit type of the intermediate and the output   */
+#define B200MOE_FLAG_EP_DIAG_LOCAL_COMBINE 2048 /* tuning aid, expert parallelism: the down projection's rows stay on
+                                           this GPU (WRONG results; isolates the cost of the peer stores)      */
 #define B200MOE_FLAG_ALIGN_ONE_CTA 512  /* tuning aid: single-CTA alignment however many slots           */
 #define B200MOE_FLAG_NO_COMBINE 256     /* out is [M*topk, H]: row t*topk+j holds pair j of token t,
                                            routing weight applied, nothing summed, routed_scaling ignored

@@ -36,7 +36,8 @@ def _case(h, i, e, k, m, seed, skew=True):
     return x, tw, ids, w13q, s13, w2q, s2
 
 
-def _run_emulated(d, world, placement, x, tw, ids, w13q, s13, w2q, s2, m_cap=None, **kw):
+def _run_emulated(d, world, placement, x, tw, ids, w13q, s13, w2q, s2, m_cap=None, held=None, **kw):
+    """`held`: the placement that says which experts each rank's weight shard holds (default: `placement`)."""
     from flaggems_sglang_b200 import ep
     m_all, h = x.shape
     e, i = w13q.shape[0], w2q.shape[2]
@@ -47,7 +48,7 @@ def _run_emulated(d, world, placement, x, tw, ids, w13q, s13, w2q, s2, m_cap=Non
     try:
         shards, toks = [], []
         for r in range(world):
-            mine = ep.local_experts(placement, r)
+            mine = ep.local_experts(placement if held is None else held, r)
             shards.append(tuple(t[mine].contiguous().to(d) for t in (w13q, s13, w2q, s2)))
             toks.append(tuple(t[r * m:(r + 1) * m].contiguous().to(d) for t in (x, tw, ids)))
         outs = [torch.empty(m, h, dtype=x.dtype, device=d) for _ in range(world)]
@@ -71,7 +72,7 @@ def test_emulated_ranks_match_single_gpu(cuda_device, world, shape, balanced):
     import flaggems_sglang_b200 as F
     from flaggems_sglang_b200 import ep
     h, i, e, k, m = shape
-    x, tw, ids, w13q, s13, w2q, s2 = _case(h, i, e, k, m, seed=h + world)
+    x, tw, ids, w13q, s13, w2q, s2 = _case(h, i, e, k, m, seed=77)
     d = cuda_device
     load = torch.bincount(ids.flatten().long(), minlength=e).tolist() if balanced else None
     placement = ep.plan_placement(e, world, load)
@@ -92,9 +93,10 @@ def test_emulated_partial_batch_and_dropped_expert(cuda_device):
     from flaggems_sglang_b200 import ep
     h, i, e, k, m = 512, 256, 8, 2, 40
     x, tw, ids, w13q, s13, w2q, s2 = _case(h, i, e, k, m, seed=3)
-    placement = ep.plan_placement(e, 2)
+    held = ep.plan_placement(e, 2)
+    placement = held.clone()
     placement[5] = -1
-    out = _run_emulated(cuda_device, 2, placement, x, tw, ids, w13q, s13, w2q, s2, m_cap=32)
+    out = _run_emulated(cuda_device, 2, placement, x, tw, ids, w13q, s13, w2q, s2, m_cap=32, held=held)
     tw_ref = torch.where(ids == 5, torch.zeros_like(tw), tw)
     ref = OM.fused_experts_fp8(x, w13q, w2q, s13, s2, tw_ref, ids)
     assert_parity(out, ref, what="ep emulated, capacity 32 > 20 tokens per rank, expert 5 nowhere")
