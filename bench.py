@@ -436,6 +436,16 @@ def expert_parallel_leg(args, dev, rank, local_rank, world, dist, barrier):
     again = step()
     torch.cuda.synchronize()
     repeatable = bool(torch.equal(out_first, again)) and bool(torch.isfinite(again.float()).all())
+    # the global batch's output, rank-major = token order: expert parallelism stores the same pair rows and sums
+    # them in the same order as one GPU does, so this digest must be the same at every N
+    if dist:
+        parts = [torch.empty_like(again) for _ in range(world)]
+        dist.all_gather(parts, again.contiguous())
+        whole = torch.cat(parts)
+    else:
+        whole = again
+    import hashlib
+    digest = hashlib.sha256(whole.contiguous().view(torch.int16).cpu().numpy().tobytes()).hexdigest()[:16]
     med = statistics.median(r["ms"] for r in regions)
     # time inside this package's local operator (alignment to output conversion), from events the library records
     lib = _lib.lib()
@@ -463,7 +473,7 @@ def expert_parallel_leg(args, dev, rank, local_rank, world, dist, barrier):
         per_rank_pairs = torch.bincount(dest.flatten(), minlength=world).tolist()
     res = {"placement": ("contiguous" if os.environ.get("B200MOE_EP_CONTIGUOUS") else
                          "load-balanced from a calibration batch (8192 other tokens, same router bias)") if world > 1 else None,
-           "pairs_per_rank": per_rank_pairs, "repeatable_bits": repeatable,
+           "pairs_per_rank": per_rank_pairs, "repeatable_bits": repeatable, "output_sha256_16": digest,
            "workload": f"{name} H{h} I{i} E{e} top{k}, FP8 e4m3 128x128 block scales, zipf(1.1) routing skew, "
                        f"global M {m_global} (seed 0), {e // world} experts and {m} tokens per rank",
            "collective": layer.ep_collective if world > 1 else "none (one GPU)",

@@ -165,8 +165,11 @@ __device__ __forceinline__ void group_by_expert(const void* ids, int is64, const
 __global__ void __launch_bounds__(kAlignThreads)
 align_block_kernel(const void* ids, int is64, const int* map, int map_len, const float* weights, int P, int E,
                    int block, int cap, int nwarps, int* sorted_ids, int* expert_ids, int* num_post_pad,
-                   float* row_gamma, int* blk_off, int* meta) {
+                   float* row_gamma, int* blk_off, int* meta, const FlagWait fw) {
   extern __shared__ int smem[];
+  griddep_wait();             // the tables written below may still be read by the kernels of the previous call
+  griddep_launch_dependents();
+  wait_for_peers(fw);
   int* s_cnt = smem;                    // nwarps * E
   int* s_base = s_cnt + nwarps * E;     // E + 1
   int* s_hist = s_base + (E + 1);       // E
@@ -204,12 +207,13 @@ align_block_kernel(const void* ids, int is64, const int* map, int map_len, const
 }
 
 // ---------------------------------------------------------------------------------------------
-// The same grouping spread over kAlignCtas CTAs in three launches, for tens of thousands of slots
+// The same grouping spread over kAlignCtas CTAs in two launches, for tens of thousands of slots
 // (one CTA pushes every store through one SM's memory pipe: 77 us at 32 k slots).  CTA c owns the
 // contiguous slots [c * per, (c + 1) * per); stability follows from ordering by (CTA, warp, lane).
 //   count  per-CTA slots per expert -> cnt[c][e]; all CTAs share the filling of the defaults
-//   scan   one CTA: padded expert starts, per-CTA bases base[c][e], block tables
-//   place  each CTA recounts its chunk (cheaper than keeping the per-warp counts) and writes
+//   place  each CTA derives the padded expert starts and its own first rows from cnt (CTA 0 also
+//          writes the block tables), recounts its chunk (cheaper than keeping the per-warp counts)
+//          and writes
 constexpr int kAlignCtas = 32;
 
 // warp-private counts of the chunk [begin, end): s_cnt[w][e]
@@ -243,9 +247,12 @@ __device__ __forceinline__ void count_chunk(const void* ids, int is64, const int
 
 __global__ void __launch_bounds__(kAlignThreads)
 align_count_kernel(const void* ids, int is64, const int* map, int map_len, int P, int E, int block, int cap, int per, int nwarps,
-                   int* sorted_ids, int* expert_ids, float* row_gamma, int* cnt) {
+                   int* sorted_ids, int* expert_ids, float* row_gamma, int* cnt, const FlagWait fw) {
   extern __shared__ int smem[];
   int* s_cnt = smem;
+  griddep_wait();
+  griddep_launch_dependents();
+  wait_for_peers(fw);
   const int nblk_cap = (cap + block - 1) / block;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < cap; i += gridDim.x * blockDim.x) {
     sorted_ids[i] = P;
@@ -263,61 +270,63 @@ align_count_kernel(const void* ids, int is64, const int* map, int map_len, int P
 }
 
 __global__ void __launch_bounds__(kAlignThreads)
-align_scan_kernel(const int* cnt, int E, int block, int nctas, int* base, int* expert_ids, int* num_post_pad,
-                  int* blk_off, int* meta) {
+align_place_kernel(const void* ids, int is64, const int* map, int map_len, const float* weights, int P, int E,
+                   int block, int per, int nwarps, const int* cnt, int* sorted_ids, float* row_gamma, int* expert_ids,
+                   int* num_post_pad, int* blk_off, int* meta) {
   extern __shared__ int smem[];
-  int* s_base = smem;            // E + 1 padded starts
-  int* s_hist = s_base + (E + 1);
-  int* s_scan = s_hist + E;      // 33
-  for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    int run = 0;
-    for (int c = 0; c < nctas; ++c) {
-      const int t = cnt[c * E + e];
-      base[c * E + e] = run;     // slots of this expert in earlier CTAs
-      run += t;
-    }
-    s_hist[e] = run;
-  }
-  __syncthreads();
+  int* s_cnt = smem;                      // nwarps * E
+  int* s_base = s_cnt + nwarps * E;       // E + 1 padded expert starts
+  int* s_mine = s_base + (E + 1);         // E: first row of this CTA's slots of each expert
+  int* s_scan = s_mine + E;               // 33
+  griddep_wait();
+  griddep_launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nctas = gridDim.x;
+  // Every CTA derives the padded expert starts from the per-CTA counts by itself (a few thousand
+  // integers out of L2), which saves a single-CTA launch between counting and placing.
   int carry = 0;
   for (int e0 = 0; e0 < E; e0 += blockDim.x) {
     const int e = e0 + threadIdx.x;
-    int padded = 0;
-    if (e < E) padded = (s_hist[e] + block - 1) / block * block;
+    int total_e = 0, before = 0;
+    if (e < E) {
+      for (int c = 0; c < nctas; ++c) {
+        const int t = cnt[c * E + e];
+        if (c < static_cast<int>(blockIdx.x)) before += t;
+        total_e += t;
+      }
+    }
+    const int padded = (total_e + block - 1) / block * block;
     int total;
     const int ex = block_exclusive_scan(padded, s_scan, &total);
-    if (e < E) s_base[e] = carry + ex;
+    if (e < E) {
+      s_base[e] = carry + ex;
+      s_mine[e] = carry + ex + before;
+    }
     carry += total;
   }
   if (threadIdx.x == 0) s_base[E] = carry;
   __syncthreads();
-  for (int i = threadIdx.x; i < nctas * E; i += blockDim.x) base[i] += s_base[i % E];
-  const int rows = s_base[E];
-  const int nblk = rows / block;
-  for (int b = threadIdx.x; b < nblk; b += blockDim.x) expert_ids[b] = upper_expert(s_base, E + 1, b * block);
-  if (blk_off != nullptr)
-    for (int e = threadIdx.x; e <= E; e += blockDim.x) blk_off[e] = s_base[e] / block;
-  if (threadIdx.x == 0) {
-    num_post_pad[0] = rows;
-    if (meta != nullptr) {
-      meta[0] = nblk;
-      meta[1] = rows;
+  if (blockIdx.x == 0) {
+    // the block tables, once
+    const int rows = s_base[E];
+    const int nblk = rows / block;
+    for (int b = threadIdx.x; b < nblk; b += blockDim.x) expert_ids[b] = upper_expert(s_base, E + 1, b * block);
+    if (blk_off != nullptr)
+      for (int e = threadIdx.x; e <= E; e += blockDim.x) blk_off[e] = s_base[e] / block;
+    if (threadIdx.x == 0) {
+      num_post_pad[0] = rows;
+      if (meta != nullptr) {
+        meta[0] = nblk;
+        meta[1] = rows;
+      }
     }
   }
-}
-
-__global__ void __launch_bounds__(kAlignThreads)
-align_place_kernel(const void* ids, int is64, const int* map, int map_len, const float* weights, int P, int E, int per, int nwarps,
-                   const int* base, int* sorted_ids, float* row_gamma) {
-  extern __shared__ int smem[];
-  int* s_cnt = smem;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int begin = min(P, static_cast<int>(blockIdx.x) * per), end = min(P, begin + per);
   int sb, se;
   count_chunk(ids, is64, map, map_len, begin, end, E, s_cnt, nwarps, &sb, &se);
-  // start of (warp, expert) = this CTA's base + the counts of the warps before it
+  // start of (warp, expert) = this CTA's first row of the expert + the counts of the warps before it
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    int run = base[blockIdx.x * E + e];
+    int run = s_mine[e];
     for (int w = 0; w < nwarps; ++w) {
       const int t = s_cnt[w * E + e];
       s_cnt[w * E + e] = run;
@@ -499,42 +508,46 @@ int routing_max_tiles(int n_slots, int n_experts) {
 
 int launch_align_block(const void* ids, int is64, const int* map, int map_len, const float* weights, int P, int E,
                        int block, int cap, int* sorted_ids, int* expert_ids, int* num_post_pad,
-                       float* row_gamma, int* blk_off, int* meta, cudaStream_t stream) {
+                       float* row_gamma, int* blk_off, int* meta, cudaStream_t stream, bool pdl, const FlagWait* wait) {
   if (P < 0 || E <= 0 || block <= 0 || cap < 0) return B200MOE_ERR_BAD_ARG;
   int nw = pick_warps(E);
   size_t smem = (static_cast<size_t>(nw) * E + (E + 1) + E + 40) * sizeof(int);
   if (smem > 48 * 1024) return B200MOE_ERR_TOO_LARGE;
   note_launch("align_block_kernel");
-  align_block_kernel<<<1, kAlignThreads, smem, stream>>>(ids, is64, map, map_len, weights, P, E, block, cap, nw,
-                                                         sorted_ids, expert_ids, num_post_pad,
-                                                         row_gamma, blk_off, meta);
-  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
+  FlagWait fw = {};
+  if (wait != nullptr) fw = *wait;
+  cudaError_t err = launch_kernel(align_block_kernel, dim3(1), dim3(kAlignThreads), smem, stream, pdl, ids, is64, map,
+                                  map_len, weights, P, E, block, cap, nw, sorted_ids, expert_ids, num_post_pad,
+                                  row_gamma, blk_off, meta, fw);
+  return err == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
 }
 
-size_t align_multi_tmp_bytes(int E) { return 2 * static_cast<size_t>(kAlignCtas) * E * sizeof(int); }
+size_t align_multi_tmp_bytes(int E) { return static_cast<size_t>(kAlignCtas) * E * sizeof(int); }
 
 int launch_align_block_multi(const void* ids, int is64, const int* map, int map_len, const float* weights, int P, int E,
                              int block, int cap, int* sorted_ids, int* expert_ids, int* num_post_pad,
-                             float* row_gamma, int* blk_off, int* meta, int* tmp, cudaStream_t stream) {
+                             float* row_gamma, int* blk_off, int* meta, int* tmp, cudaStream_t stream, bool pdl,
+                             const FlagWait* wait) {
   if (P < 0 || E <= 0 || block <= 0 || cap < 0 || tmp == nullptr) return B200MOE_ERR_BAD_ARG;
   const int nw = pick_warps(E);
   const size_t smem = (static_cast<size_t>(nw) * E + 40) * sizeof(int);
-  const size_t smem_scan = (2 * static_cast<size_t>(E) + 1 + 40) * sizeof(int);
-  if (smem > 48 * 1024 || smem_scan > 48 * 1024) return B200MOE_ERR_TOO_LARGE;
+  const size_t smem_place = (static_cast<size_t>(nw) * E + 2 * static_cast<size_t>(E) + 1 + 40) * sizeof(int);
+  if (smem_place > 48 * 1024) return B200MOE_ERR_TOO_LARGE;
   int per = (P + kAlignCtas - 1) / kAlignCtas;
   per = (per + 31) & ~31;
   int* cnt = tmp;
-  int* base = tmp + static_cast<size_t>(kAlignCtas) * E;
+  FlagWait fw = {};
+  if (wait != nullptr) fw = *wait;
   note_launch("align_count_kernel");
-  note_launch("align_scan_kernel");
+  cudaError_t err = launch_kernel(align_count_kernel, dim3(kAlignCtas), dim3(kAlignThreads), smem, stream, pdl, ids,
+                                  is64, map, map_len, P, E, block, cap, per, nw, sorted_ids, expert_ids, row_gamma, cnt,
+                                  fw);
+  if (err != cudaSuccess) return B200MOE_ERR_CUDA;
   note_launch("align_place_kernel");
-  align_count_kernel<<<kAlignCtas, kAlignThreads, smem, stream>>>(ids, is64, map, map_len, P, E, block, cap, per, nw,
-                                                                  sorted_ids, expert_ids, row_gamma, cnt);
-  align_scan_kernel<<<1, kAlignThreads, smem_scan, stream>>>(cnt, E, block, kAlignCtas, base, expert_ids,
-                                                             num_post_pad, blk_off, meta);
-  align_place_kernel<<<kAlignCtas, kAlignThreads, smem, stream>>>(ids, is64, map, map_len, weights, P, E, per, nw, base,
-                                                                  sorted_ids, row_gamma);
-  return cudaGetLastError() == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
+  err = launch_kernel(align_place_kernel, dim3(kAlignCtas), dim3(kAlignThreads), smem_place, stream, pdl, ids, is64, map,
+                      map_len, weights, P, E, block, per, nw, static_cast<const int*>(cnt), sorted_ids, row_gamma,
+                      expert_ids, num_post_pad, blk_off, meta);
+  return err == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
 }
 
 int launch_align_from_routing(const int* hist, const int* topk_indx, const float* gate_scal, int P,

@@ -417,6 +417,48 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// ---------------------------------------------------------------- flags raised by other ranks
+// Expert parallelism: a kernel that consumes what the peers wrote first waits until every peer's
+// epoch flag (in THIS rank's memory, written by the peers with release stores) has reached this
+// rank's own epoch.  world == 0: nothing to wait for.  The wait is bounded; when it runs out the
+// status word receives DEV_TIMEOUT_PEER and the kernel goes on (its output is then meaningless,
+// the context stays usable).
+struct FlagWait {
+  const unsigned long long* flags;   // [world]
+  const unsigned long long* epoch;   // this rank's epoch counter
+  int world;
+  unsigned long long limit_ns;
+  int* status;
+};
+__device__ __forceinline__ unsigned long long ld_acquire_sys_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+// Called by every thread of a CTA (after griddep_wait); contains a __syncthreads.
+__device__ __forceinline__ void wait_for_peers(const FlagWait& w) {
+  if (w.world <= 0) return;
+  // a wait that already ran out in this call (another CTA, an earlier kernel) is not repeated
+  if (static_cast<int>(threadIdx.x) < w.world && *reinterpret_cast<const volatile int*>(w.status) == 0) {
+    const unsigned long long want = *reinterpret_cast<const volatile unsigned long long*>(w.epoch);
+    const unsigned long long* f = w.flags + threadIdx.x;
+    unsigned long long t0 = 0;
+#pragma unroll 1
+    for (unsigned int spin = 0;; ++spin) {
+      if (ld_acquire_sys_u64(f) >= want) break;
+      if ((spin & 0x3f) == 0x3f) {
+        const unsigned long long now = globaltimer_ns();
+        if (t0 == 0) t0 = now;
+        if (now - t0 > w.limit_ns) {
+          atomicCAS(w.status, 0, static_cast<int>(DEV_TIMEOUT_PEER));
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+}
+
 // ---------------------------------------------------------------- host: launch accounting
 // Every launcher names the kernel it starts; the C ABI reports the total and the kernels of the
 // most recent forward call (b200moe_launch_stats), so that benchmarks count launches instead of

@@ -24,11 +24,6 @@ size_t up256(size_t v) { return (v + 255) / 256 * 256; }
 __device__ __forceinline__ void st_release_sys_u64(unsigned long long* p, unsigned long long v) {
   asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
-__device__ __forceinline__ unsigned long long ld_acquire_sys_u64(const unsigned long long* p) {
-  unsigned long long v;
-  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-  return v;
-}
 
 template <typename T>
 __device__ __forceinline__ void load4f(const T* p, float (&v)[4]);
@@ -48,10 +43,12 @@ __device__ __forceinline__ void load4f<__half>(const __half* p, float (&v)[4]) {
 }
 
 constexpr int kDispatchWarps = 4;
-// staging of one quantised row: H bytes + H/128 scales, kept 16-byte aligned per warp
+// staging of one quantised row: H bytes + H/128 scales
 __host__ __device__ inline size_t ep_stage_bytes(int H) { return static_cast<size_t>(H) + (((H >> 7) * 4 + 15) & ~15); }
 
-// One warp per token.  Shared memory per warp (FP8 rows): H bytes of quantised row + H/128 scales.
+// One CTA (four warps) per token: the warps share the token's 128-wide groups, so that even a few
+// hundred tokens put enough loads in flight, and then copy the staged row to every destination
+// together.  Shared memory (FP8 rows): H bytes of quantised row + H/128 scales.
 template <typename T>
 __global__ void __launch_bounds__(kDispatchWarps * 32)
 ep_dispatch_kernel(const EpDispatchArgs a) {
@@ -75,11 +72,10 @@ ep_dispatch_kernel(const EpDispatchArgs a) {
       z[i] = make_uint4(0, 0, 0, 0);
   }
 
-  uint8_t* stage = smem + static_cast<size_t>(warp) * (a.fp8_rows ? ep_stage_bytes(a.H) : 0);
+  uint8_t* stage = smem;
   float* stage_sc = reinterpret_cast<float*>(stage + a.H);
-  const int total_warps = gridDim.x * kDispatchWarps;
-  for (int i = blockIdx.x * kDispatchWarps + warp; i < a.m_cap; i += total_warps) {
-    // ---- where do this token's experts live?
+  for (int i = blockIdx.x; i < a.m_cap; i += gridDim.x) {
+    // ---- where do this token's experts live?  (every warp looks for itself: 32 bytes of ids)
     int dr = -1, lid = -1;
     float w = 0.f;
     if (i < a.m && lane < a.topk) {
@@ -101,18 +97,18 @@ ep_dispatch_kernel(const EpDispatchArgs a) {
     for (int d = 0; d < a.world; ++d) {
       const bool mine = dr == d;
       if (__any_sync(0xffffffffu, mine)) dest_mask |= 1u << d;
-      if (lane < a.topk) {
+      if (warp == 0 && lane < a.topk) {
         reinterpret_cast<int*>(a.heap[d] + a.L.recv_ids)[row * a.topk + lane] = mine ? lid : -1;
         reinterpret_cast<float*>(a.heap[d] + a.L.recv_w)[row * a.topk + lane] = mine ? w : 0.f;
       }
     }
-    if (dest_mask == 0) continue;
+    if (dest_mask == 0) continue;     // the same in every warp of the CTA
     const T* xrow = reinterpret_cast<const T*>(a.x) + static_cast<size_t>(i) * a.H;
     if (a.fp8_rows) {
       // ---- 1x128 quantisation, the arithmetic of group_quant_fp8_kernel (prep.cu) so that a row
       // carries the same bits whether it is quantised here or inside a single-GPU call
       constexpr int RUN = 8;
-      for (int g0 = 0; g0 < G; g0 += RUN) {
+      for (int g0 = warp * RUN; g0 < G; g0 += kDispatchWarps * RUN) {
         float v[RUN][4];
 #pragma unroll
         for (int u = 0; u < RUN; ++u) {
@@ -136,34 +132,23 @@ ep_dispatch_kernel(const EpDispatchArgs a) {
           if (lane == 0) stage_sc[g] = s;
         }
       }
-      __syncwarp();
+      __syncthreads();
       for (int d = 0; d < a.world; ++d) {
         if (!(dest_mask & (1u << d))) continue;
         uint4* dst = reinterpret_cast<uint4*>(a.heap[d] + a.L.recv_x + row * a.L.x_row_bytes);
         const uint4* src = reinterpret_cast<const uint4*>(stage);
-        for (int c = lane; c < a.H / 16; c += 32) dst[c] = src[c];
+        for (int c = threadIdx.x; c < a.H / 16; c += blockDim.x) dst[c] = src[c];
         float* dsc = reinterpret_cast<float*>(a.heap[d] + a.L.recv_xs) + row * G;
-        for (int g = lane; g < G; g += 32) dsc[g] = stage_sc[g];
+        for (int g = threadIdx.x; g < G; g += blockDim.x) dsc[g] = stage_sc[g];
       }
-      __syncwarp();
+      __syncthreads();     // the staging row is reused by the CTA's next token
     } else {
       const uint4* src = reinterpret_cast<const uint4*>(xrow);
-      for (int c0 = 0; c0 < a.H / 8; c0 += 32 * 4) {      // four 16-byte chunks per lane in flight
-        uint4 v[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int c = c0 + u * 32 + lane;
-          v[u] = (c < a.H / 8) ? __ldg(src + c) : make_uint4(0, 0, 0, 0);
-        }
-        for (int d = 0; d < a.world; ++d) {
-          if (!(dest_mask & (1u << d))) continue;
-          uint4* dst = reinterpret_cast<uint4*>(a.heap[d] + a.L.recv_x + row * a.L.x_row_bytes);
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int c = c0 + u * 32 + lane;
-            if (c < a.H / 8) dst[c] = v[u];
-          }
-        }
+      for (int c = threadIdx.x; c < a.H / 8; c += blockDim.x) {
+        const uint4 v = __ldg(src + c);
+        for (int d = 0; d < a.world; ++d)
+          if (dest_mask & (1u << d))
+            reinterpret_cast<uint4*>(a.heap[d] + a.L.recv_x + row * a.L.x_row_bytes)[c] = v;
       }
     }
   }
@@ -191,27 +176,9 @@ ep_dispatch_kernel(const EpDispatchArgs a) {
 }
 
 __global__ void __launch_bounds__(32)
-ep_wait_kernel(const unsigned long long* flags, const unsigned long long* epoch_ptr, int world,
-               unsigned long long limit_ns, int* status) {
+ep_wait_kernel(const FlagWait w) {
   griddep_wait();
-  const unsigned long long want = *reinterpret_cast<const volatile unsigned long long*>(epoch_ptr);
-  if (threadIdx.x < world) {
-    const unsigned long long* f = flags + threadIdx.x;
-    unsigned long long t0 = 0;
-#pragma unroll 1
-    for (unsigned int spin = 0;; ++spin) {
-      if (ld_acquire_sys_u64(f) >= want) break;
-      if ((spin & 0x3f) == 0x3f) {
-        const unsigned long long now = globaltimer_ns();
-        if (t0 == 0) t0 = now;
-        if (now - t0 > limit_ns) {
-          atomicCAS(status, 0, static_cast<int>(DEV_TIMEOUT_PEER));
-          break;
-        }
-      }
-    }
-  }
-  __syncwarp();
+  wait_for_peers(w);
   griddep_launch_dependents();
 }
 
@@ -259,10 +226,10 @@ EpHeap ep_heap_layout(int world, int m_cap, int H, int topk, bool fp8_rows) {
 int launch_ep_dispatch(const EpDispatchArgs& a, int num_sms, cudaStream_t stream, bool pdl) {
   if (a.world < 1 || a.world > kMaxPeers || a.rank < 0 || a.rank >= a.world || a.topk > 32) return B200MOE_ERR_BAD_ARG;
   if (a.m < 0 || a.m > a.m_cap || a.H % 8 != 0 || (a.fp8_rows && a.H % 128 != 0)) return B200MOE_ERR_BAD_ARG;
-  const size_t smem = a.fp8_rows ? static_cast<size_t>(kDispatchWarps) * ep_stage_bytes(a.H) : 0;
+  const size_t smem = a.fp8_rows ? ep_stage_bytes(a.H) : 0;
   if (smem > 200 * 1024) return B200MOE_ERR_TOO_LARGE;
-  int ctas = (a.m_cap + kDispatchWarps - 1) / kDispatchWarps;
-  if (ctas > num_sms * 4) ctas = num_sms * 4;
+  int ctas = a.m_cap;
+  if (ctas > num_sms * 8) ctas = num_sms * 8;
   if (ctas < 1) ctas = 1;
   cudaError_t err;
   note_launch("ep_dispatch_kernel");
@@ -280,13 +247,20 @@ int launch_ep_dispatch(const EpDispatchArgs& a, int num_sms, cudaStream_t stream
   return err == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
 }
 
-int launch_ep_wait(uint8_t* my_heap, const EpHeap& L, size_t flag_off, int world, unsigned long long limit_ns,
-                   int* status, cudaStream_t stream, bool pdl) {
+FlagWait ep_flag_wait(uint8_t* my_heap, const EpHeap& L, size_t flag_off, int world, unsigned long long limit_ns,
+                      int* status) {
+  FlagWait w;
+  w.flags = reinterpret_cast<const unsigned long long*>(my_heap + L.flags + flag_off);
+  w.epoch = reinterpret_cast<const unsigned long long*>(my_heap + L.flags + kEpFlagEpoch);
+  w.world = world;
+  w.limit_ns = limit_ns;
+  w.status = status;
+  return w;
+}
+
+int launch_ep_wait(const FlagWait& w, cudaStream_t stream, bool pdl) {
   note_launch("ep_wait_kernel");
-  cudaError_t err = launch_kernel(ep_wait_kernel, dim3(1), dim3(32), 0, stream, pdl,
-                                  reinterpret_cast<const unsigned long long*>(my_heap + L.flags + flag_off),
-                                  reinterpret_cast<const unsigned long long*>(my_heap + L.flags + kEpFlagEpoch), world,
-                                  limit_ns, status);
+  cudaError_t err = launch_kernel(ep_wait_kernel, dim3(1), dim3(32), 0, stream, pdl, w);
   return err == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
 }
 

@@ -43,10 +43,11 @@ struct EpDispatchArgs {
 
 int launch_ep_dispatch(const EpDispatchArgs& a, int num_sms, cudaStream_t stream, bool pdl);
 
-// One warp waits (at most limit_ns) until every peer's flag in this rank's heap has reached this
-// rank's epoch; on a time-out DEV_TIMEOUT_PEER goes to the status word and the kernel returns.
-int launch_ep_wait(uint8_t* my_heap, const EpHeap& L, size_t flag_off, int world, unsigned long long limit_ns,
-                   int* status, cudaStream_t stream, bool pdl);
+// Waiting for the peers' flags (common.cuh: FlagWait): as a kernel of its own, or handed to the kernel
+// that consumes what the peers wrote (alignment, output conversion), which then waits in its prologue.
+FlagWait ep_flag_wait(uint8_t* my_heap, const EpHeap& L, size_t flag_off, int world, unsigned long long limit_ns,
+                      int* status);
+int launch_ep_wait(const FlagWait& w, cudaStream_t stream, bool pdl);
 
 // After everything before it in the stream has completed: this rank's epoch goes into its slot of
 // the flag array (at flag_off) of every peer.

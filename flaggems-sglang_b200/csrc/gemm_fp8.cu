@@ -286,9 +286,18 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         // warp maxima by redux on the bit patterns (non-negative floats order like integers),
         // one thread per token turns the four warp maxima into the scale and its reciprocal.
         float* red = s_red + (buf * 2 + grp) * 4 * 64;
+        // per-expert bias of this thread's gate row and up / linear row, and the clamped swiglu: the
+        // rarer tail, kept out of the plain one
+        const bool ext = a.bias != nullptr || a.activation == B200MOE_ACT_SWIGLU_OAI;
+        float bg = 0.f, bu = 0.f;
+        if (a.bias != nullptr && n < a.N) {
+          bg = __ldg(a.bias + static_cast<size_t>(t.e) * 2 * a.N + n);
+          bu = __ldg(a.bias + static_cast<size_t>(t.e) * 2 * a.N + a.N + n);
+        }
 #pragma unroll
         for (int i = 0; i < CPT; ++i) {
-          float av = act_mul<__nv_bfloat16>(acc0[i], acc1[i], w_on_input, col_gam[i], false, act_params(a));
+          float av = ext ? act_mul<__nv_bfloat16, true>(acc0[i] + bg, acc1[i] + bu, w_on_input, col_gam[i], false, act_params(a))
+                         : act_mul<__nv_bfloat16>(acc0[i], acc1[i], w_on_input, col_gam[i], false, act_params(a));
           av = (a.dtype == B200MOE_DTYPE_BF16) ? __bfloat162float(__float2bfloat16_rn(av))
                                                : __half2float(__float2half_rn(av));
           acc0[i] = av;
@@ -312,14 +321,19 @@ moe_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       } else {
         const unsigned long long* col_ptr = s_col_ptr + buf * 128 + cb;
         const bool second = n + kTileRows < a.N;
+        float b0 = 0.f, b1 = 0.f;      // bias of the two output columns; the first reduction split carries it
+        if (a.bias != nullptr && t.kb0 == 0) {
+          if (n < a.N) b0 = __ldg(a.bias + static_cast<size_t>(t.e) * a.N + n);
+          if (second) b1 = __ldg(a.bias + static_cast<size_t>(t.e) * a.N + n + kTileRows);
+        }
 #pragma unroll
         for (int i = 0; i < CPT; ++i) {
           const int orow = col_row[i];
           if (orow >= 0) {
             const float gam = w_on_input ? 1.0f : col_gam[i];
             float* out = reinterpret_cast<float*>(col_ptr[i]) + n;   // the token's row, here or on its owner
-            atomicAdd(out, acc0[i] * gam);
-            if (second) atomicAdd(out + kTileRows, acc1[i] * gam);
+            atomicAdd(out, (acc0[i] + b0) * gam);
+            if (second) atomicAdd(out + kTileRows, (acc1[i] + b1) * gam);
           }
         }
       }
@@ -614,13 +628,34 @@ moe_gemm_fp8_tokm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
       if (!ok) break;
       const long long tail_t0 = clock64();
 
+      if (MODE == 1 && a.bias != nullptr && t.kb0 == 0) {
+        // bias of columns n0 + 128 grp + [0, 128): accA holds the first 64, accB the next 64
+        const float* bo = a.bias + static_cast<size_t>(t.e) * a.N + t.n0 + 128 * grp;
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          accA[i] += (t.n0 + 128 * grp + i < a.N) ? __ldg(bo + i) : 0.f;
+          accB[i] += (t.n0 + 128 * grp + 64 + i < a.N) ? __ldg(bo + 64 + i) : 0.f;
+        }
+      }
       if (MODE == 0) {
         // 64 activations of this token; the other 64 of its quantisation group live in the
         // same lane of the other promotion group
         float amax = 0.f;
+        const bool ext = a.bias != nullptr || a.activation == B200MOE_ACT_SWIGLU_OAI;
+        if (a.bias != nullptr) {
+          // gate columns n0 + 64 grp + i and the matching up / linear columns of the same expert
+          const float* bgp = a.bias + static_cast<size_t>(t.e) * 2 * a.N + t.n0 + 64 * grp;
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            const bool in = t.n0 + 64 * grp + i < a.N;
+            accA[i] += in ? __ldg(bgp + i) : 0.f;
+            accB[i] += in ? __ldg(bgp + a.N + i) : 0.f;
+          }
+        }
 #pragma unroll
         for (int i = 0; i < 64; ++i) {
-          float av = act_mul<__nv_bfloat16>(accA[i], accB[i], w_on_input, gam, false, act_params(a));
+          float av = ext ? act_mul<__nv_bfloat16, true>(accA[i], accB[i], w_on_input, gam, false, act_params(a))
+                         : act_mul<__nv_bfloat16>(accA[i], accB[i], w_on_input, gam, false, act_params(a));
           av = (a.dtype == B200MOE_DTYPE_BF16) ? __bfloat162float(__float2bfloat16_rn(av))
                                                : __half2float(__float2half_rn(av));
           accA[i] = av;

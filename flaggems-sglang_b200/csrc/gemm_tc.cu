@@ -551,9 +551,17 @@ int launch_gemm_tc(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmA
   if (a.orient == 1 && a.BT > 128) return B200MOE_ERR_BAD_ARG;
   if (a.wmode == B200MOE_W_INT4_AWQ) {
     if (a.dtype != B200MOE_DTYPE_FP16 || a.w_sz == nullptr) return B200MOE_ERR_UNSUPPORTED;
-    if (a.orient == 1)
+    const bool ext4 = a.bias != nullptr || a.activation == B200MOE_ACT_SWIGLU_OAI;
+    if (a.orient == 1) {
+      if (ext4)
+        return a.mode == 0 ? launch_one<0, __half, 1, true, true>(tm_w, tm_x, a, num_sms, stream)
+                           : launch_one<1, __half, 1, true, true>(tm_w, tm_x, a, num_sms, stream);
       return a.mode == 0 ? launch_one<0, __half, 1, true>(tm_w, tm_x, a, num_sms, stream)
                          : launch_one<1, __half, 1, true>(tm_w, tm_x, a, num_sms, stream);
+    }
+    if (ext4)
+      return a.mode == 0 ? launch_one<0, __half, 0, true, true>(tm_w, tm_x, a, num_sms, stream)
+                         : launch_one<1, __half, 0, true, true>(tm_w, tm_x, a, num_sms, stream);
     return a.mode == 0 ? launch_one<0, __half, 0, true>(tm_w, tm_x, a, num_sms, stream)
                        : launch_one<1, __half, 0, true>(tm_w, tm_x, a, num_sms, stream);
   }

@@ -451,9 +451,17 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         const bool n_ok = n < a.N;
         unsigned int* amax = s_amax + buf * 32 + tk0;
         int* osum = s_osum + buf * 32 + tk0;
+        // per-expert bias of this thread's gate row and up / linear row, and the clamped swiglu
+        const bool ext = a.bias != nullptr || a.activation == B200MOE_ACT_SWIGLU_OAI;
+        float bg = 0.f, bu = 0.f;
+        if (a.bias != nullptr && n_ok) {
+          bg = __ldg(a.bias + static_cast<size_t>(t.e) * 2 * a.N + n);
+          bu = __ldg(a.bias + static_cast<size_t>(t.e) * 2 * a.N + a.N + n);
+        }
 #pragma unroll
         for (int i = 0; i < HT; ++i) {
-          float av = act_mul<__half>(acc0[i], acc1[i], w_on_input, col_gam[i], mimic, act_params(a));
+          float av = ext ? act_mul<__half, true>(acc0[i] + bg, acc1[i] + bu, w_on_input, col_gam[i], mimic, act_params(a))
+                         : act_mul<__half>(acc0[i], acc1[i], w_on_input, col_gam[i], mimic, act_params(a));
           av = n_ok ? __half2float(__float2half_rn(av)) : 0.f;
           acc0[i] = av;
           const unsigned int m = __reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(av)));
@@ -502,12 +510,17 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       } else {
         float* out = reinterpret_cast<float*>(a.out) + n;
         const bool first = n < a.N, second = n + kTileRows < a.N;
+        float b0 = 0.f, b1 = 0.f;      // the first reduction split carries the bias
+        if (a.bias != nullptr && t.kb0 == 0) {
+          if (first) b0 = __ldg(a.bias + static_cast<size_t>(t.e) * a.N + n);
+          if (second) b1 = __ldg(a.bias + static_cast<size_t>(t.e) * a.N + n + kTileRows);
+        }
 #pragma unroll
         for (int i = 0; i < HT; ++i) {
           const int orow = col_row[i];
           if (orow >= 0) {
             const float gam = w_on_input ? 1.0f : col_gam[i];
-            float y0 = acc0[i] * gam, y1 = acc1[i] * gam;
+            float y0 = (acc0[i] + b0) * gam, y1 = (acc1[i] + b1) * gam;
             if (round_pair) {
               y0 = __half2float(__float2half_rn(y0));
               y1 = __half2float(__float2half_rn(y1));

@@ -208,9 +208,10 @@ group_split_i8_kernel(const __half* __restrict__ x, uint8_t* __restrict__ planes
 
 template <typename T>
 __global__ void __launch_bounds__(256)
-finalize_kernel(const float4* __restrict__ acc, T* __restrict__ out, size_t n4, float scale) {
+finalize_kernel(const float4* __restrict__ acc, T* __restrict__ out, size_t n4, float scale, const FlagWait fw) {
   griddep_wait();
   griddep_launch_dependents();
+  wait_for_peers(fw);
   for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4;
        i += static_cast<size_t>(gridDim.x) * blockDim.x) {
     float4 v = acc[i];
@@ -224,9 +225,10 @@ finalize_kernel(const float4* __restrict__ acc, T* __restrict__ out, size_t n4, 
 template <typename T>
 __global__ void __launch_bounds__(256)
 finalize_pairs_kernel(const uint4* __restrict__ pairs, const uint8_t* __restrict__ pair_valid, uint4* __restrict__ out,
-                      int M, int topk, int chunks_per_row, float scale) {
+                      int M, int topk, int chunks_per_row, float scale, const FlagWait fw) {
   griddep_wait();
   griddep_launch_dependents();
+  wait_for_peers(fw);
   const long long total = static_cast<long long>(M) * chunks_per_row;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -265,7 +267,9 @@ finalize_pairs_kernel(const uint4* __restrict__ pairs, const uint8_t* __restrict
 }  // namespace
 
 int launch_finalize_pairs(const void* pairs, const uint8_t* pair_valid, void* out, int dtype, int M, int topk,
-                          int H, float scale, int num_sms, cudaStream_t stream, bool pdl) {
+                          int H, float scale, int num_sms, cudaStream_t stream, bool pdl, const FlagWait* wait) {
+  FlagWait fw = {};
+  if (wait != nullptr) fw = *wait;
   if (H % 8 != 0) return B200MOE_ERR_UNSUPPORTED;
   const long long total = static_cast<long long>(M) * (H / 8);
   long long ctas = (total + 255) / 256;
@@ -276,11 +280,11 @@ int launch_finalize_pairs(const void* pairs, const uint8_t* pair_valid, void* ou
   if (dtype == B200MOE_DTYPE_BF16)
     err = launch_kernel(finalize_pairs_kernel<__nv_bfloat16>, dim3(static_cast<unsigned>(ctas)), dim3(256), 0, stream,
                         pdl, reinterpret_cast<const uint4*>(pairs), pair_valid, reinterpret_cast<uint4*>(out), M, topk,
-                        H / 8, scale);
+                        H / 8, scale, fw);
   else
     err = launch_kernel(finalize_pairs_kernel<__half>, dim3(static_cast<unsigned>(ctas)), dim3(256), 0, stream, pdl,
                         reinterpret_cast<const uint4*>(pairs), pair_valid, reinterpret_cast<uint4*>(out), M, topk, H / 8,
-                        scale);
+                        scale, fw);
   return err == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
 }
 
@@ -339,7 +343,9 @@ int launch_group_split_i8(const void* x, uint8_t* planes, float* scales, int* su
 }
 
 int launch_finalize(const float* acc, void* out, int dtype, size_t n, float scale, int num_sms,
-                    cudaStream_t stream, bool pdl) {
+                    cudaStream_t stream, bool pdl, const FlagWait* wait) {
+  FlagWait fw = {};
+  if (wait != nullptr) fw = *wait;
   if (n % 4 != 0) return B200MOE_ERR_UNSUPPORTED;
   size_t n4 = n / 4;
   size_t ctas = (n4 + 255) / 256;
@@ -349,10 +355,10 @@ int launch_finalize(const float* acc, void* out, int dtype, size_t n, float scal
   note_launch("finalize_kernel");
   if (dtype == B200MOE_DTYPE_BF16)
     err = launch_kernel(finalize_kernel<__nv_bfloat16>, dim3(static_cast<unsigned>(ctas)), dim3(256), 0, stream, pdl,
-                        reinterpret_cast<const float4*>(acc), reinterpret_cast<__nv_bfloat16*>(out), n4, scale);
+                        reinterpret_cast<const float4*>(acc), reinterpret_cast<__nv_bfloat16*>(out), n4, scale, fw);
   else
     err = launch_kernel(finalize_kernel<__half>, dim3(static_cast<unsigned>(ctas)), dim3(256), 0, stream, pdl,
-                        reinterpret_cast<const float4*>(acc), reinterpret_cast<__half*>(out), n4, scale);
+                        reinterpret_cast<const float4*>(acc), reinterpret_cast<__half*>(out), n4, scale, fw);
   return err == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
 }
 

@@ -29,12 +29,14 @@ int launch_group_split_i8(const void* x, uint8_t* planes, float* scales, int* su
                           size_t zero_bytes, int num_sms, cudaStream_t stream, bool pdl);
 
 // out[i] = cast(acc[i] * scale)
+// `wait` (expert parallelism): every CTA first waits for the peers' flags (common.cuh: FlagWait).
 int launch_finalize(const float* acc, void* out, int dtype, size_t n, float scale, int num_sms,
-                    cudaStream_t stream, bool pdl);
+                    cudaStream_t stream, bool pdl, const FlagWait* wait = nullptr);
 
 // out[t][c] = cast(scale * sum_j pairs[t * topk + j][c]) over the pairs marked valid.
 int launch_finalize_pairs(const void* pairs, const uint8_t* pair_valid, void* out, int dtype, int M, int topk,
-                          int H, float scale, int num_sms, cudaStream_t stream, bool pdl);
+                          int H, float scale, int num_sms, cudaStream_t stream, bool pdl,
+                          const FlagWait* wait = nullptr);
 
 // Provokes a device-side time-out on purpose (see selftest.cu): observed[0] = 0 when the short wait
 // ran out, observed[1] = 0 when the sibling wait was released by the abort flag, observed[2] = the

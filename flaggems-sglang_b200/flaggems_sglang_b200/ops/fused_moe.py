@@ -189,7 +189,7 @@ def fused_experts(
     pair instead of their sum; ``routed_scaling_factor`` is not applied (the reference's
     adapter skips it too, src/flaggems_sglang/ops/fused_moe.py:399-404).
 
-    ``b13 [E, 2I]`` / ``b2 [E, H]`` (16-bit weights only): per-expert biases added to
+    ``b13 [E, 2I]`` / ``b2 [E, H]`` (any weight mode): per-expert biases added to
     the two projections.  ``activation="swiglu_oai"``: ``s = g * sigmoid(alpha * g)``,
     ``out = s * (linear + 1)`` with the gate clamped from above and the linear half
     clamped to ``[-limit, limit]`` when ``swiglu_limit`` is given.
@@ -235,12 +235,14 @@ def fused_experts(
 
     quant = None
     wmode = _lib.W_16BIT
+    keep = []                    # converted tensors whose storage the call reads
     if use_fp8_w8a8:
         wmode = _lib.W_FP8_BLOCK
         assert w13.dtype == torch.float8_e4m3fn and w2.dtype == torch.float8_e4m3fn, "FP8 weights must be float8_e4m3fn"
         assert w13_scale is not None and w2_scale is not None, "block scales are required"
         s1 = w13_scale.to(torch.float32).contiguous()
         s2 = w2_scale.to(torch.float32).contiguous()
+        keep += [s1, s2]
         quant = _lib.Quant(s1.data_ptr(), s2.data_ptr(), None, None)
         if xs_keep is not None:
             quant.x_scale = xs_keep.data_ptr()
@@ -252,23 +254,25 @@ def fused_experts(
         assert w13_sz.dtype == torch.int32 and w13_sz.shape == (e, h // 128, 2 * i), "w13_sz must be [E, H/128, 2I] int32"
         assert w2_sz.dtype == torch.int32 and w2_sz.shape == (e, i // 128, h), "w2_sz must be [E, I/128, H] int32"
         z1, z2 = w13_sz.contiguous(), w2_sz.contiguous()
+        keep += [z1, z2]
         quant = _lib.Quant(None, None, z1.data_ptr(), z2.data_ptr())
     else:
         assert w13.dtype == x.dtype and w2.dtype == x.dtype, "weights must have the activation dtype"
-        if b13 is not None or b2 is not None or activation == "swiglu_oai":
-            bias1 = b13.to(torch.float32).contiguous() if b13 is not None else None
-            bias2 = b2.to(torch.float32).contiguous() if b2 is not None else None
-            if bias1 is not None:
-                assert bias1.shape == (e, 2 * i), "b13 must be [E, 2I]"
-            if bias2 is not None:
-                assert bias2.shape == (e, h), "b2 must be [E, H]"
-            quant = _lib.Quant(None, None, None, None,
-                               bias1.data_ptr() if bias1 is not None else None,
-                               bias2.data_ptr() if bias2 is not None else None,
-                               float(swiglu_alpha), float(swiglu_limit) if swiglu_limit else 0.0)
-    if quant is None or wmode != _lib.W_16BIT:
-        assert b13 is None and b2 is None and activation != "swiglu_oai", \
-            "biases and the clamped swiglu are available with 16-bit weights only"
+    if b13 is not None or b2 is not None or activation == "swiglu_oai":
+        # per-expert biases and the clamped swiglu, for every weight mode
+        bias1 = b13.to(torch.float32).contiguous() if b13 is not None else None
+        bias2 = b2.to(torch.float32).contiguous() if b2 is not None else None
+        if bias1 is not None:
+            assert bias1.shape == (e, 2 * i), "b13 must be [E, 2I]"
+        if bias2 is not None:
+            assert bias2.shape == (e, h), "b2 must be [E, H]"
+        keep += [bias1, bias2]
+        if quant is None:
+            quant = _lib.Quant(None, None, None, None)
+        quant.b1 = bias1.data_ptr() if bias1 is not None else None
+        quant.b2 = bias2.data_ptr() if bias2 is not None else None
+        quant.swiglu_alpha = float(swiglu_alpha)
+        quant.swiglu_limit = float(swiglu_limit) if swiglu_limit else 0.0
 
     lib = _lib.lib()
     if router is not None:

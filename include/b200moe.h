@@ -100,7 +100,7 @@ typedef struct b200moe_quant {
    * flaggems_sglang_b200.quant.repack_awq_for_kernel builds both from AWQ checkpoint tensors. */
   const void *w1_sz;
   const void *w2_sz;
-  /* 16-bit weights only: per-expert biases, fp32.  b1 [E, 2I] (gate rows, then up / linear
+  /* per-expert biases (every weight mode), fp32.  b1 [E, 2I] (gate rows, then up / linear
    * rows, matching w1's row order), b2 [E, H]; added to the GEMM outputs before activation /
    * routing weight, as triton_kernel_fused_experts_with_bias does
    * (src/flaggems_sglang/ops/fused_moe.py:285-308). */

@@ -139,3 +139,30 @@ def test_fp8_prequantised_activations(cuda_device, h, i, e, k, m):
     torch.testing.assert_close(pre.float(), plain.float(), rtol=1e-2, atol=1e-3)
     ref = OM.fused_experts_fp8(x, w13q, w2q, s13, s2, tw, ids)
     assert_parity(pre, ref, what=f"fp8 prequantised {(h, i, e, k, m)}")
+
+
+@pytest.mark.parametrize("h,i,e,k,m,bt", [(512, 384, 8, 2, 100, 0), (512, 256, 4, 2, 150, 16), (512, 256, 4, 2, 150, 64),
+                                           (2048, 256, 16, 8, 640, 0), (1024, 512, 8, 2, 300, 128)])
+@pytest.mark.parametrize("alpha,limit", [(1.702, 7.0), (None, None)])
+def test_fp8_bias_and_clamped_swiglu(cuda_device, h, i, e, k, m, bt, alpha, limit):
+    """Per-expert biases and the bias variant's activation (reference: fused_moe.py:219-309, bf16 only
+    there) on the FP8 kernels: weights-on-M blocks, 128-token blocks with atomics and with pair rows."""
+    import flaggems_sglang_b200 as F
+    x, tw, ids, w13q, s13, w2q, s2 = _fp8_case(h, i, e, k, m, seed=h + m + bt)
+    g = torch.Generator().manual_seed(bt + m)
+    b13 = (torch.randn(e, 2 * i, generator=g) * 0.5).to(torch.bfloat16)
+    b2 = (torch.randn(e, h, generator=g) * 0.5).to(torch.bfloat16)
+    d = cuda_device
+    out = F.fused_experts(x.to(d), w13q.to(d), w2q.to(d), tw.to(d), ids.to(d), use_fp8_w8a8=True, w13_scale=s13.to(d),
+                          w2_scale=s2.to(d), activation="swiglu_oai", b13=b13.to(d), b2=b2.to(d),
+                          swiglu_alpha=1.0 if alpha is None else alpha, swiglu_limit=limit, block_tokens=bt)
+    F.check_status()
+    ref = OM.fused_experts_fp8(x, w13q, w2q, s13, s2, tw, ids, activation="swiglu_oai", b1=b13, b2=b2,
+                               swiglu_alpha=1.0 if alpha is None else alpha, swiglu_limit=limit)
+    assert_parity(out, ref, what=f"fp8 bias {(h, i, e, k, m, bt)}")
+    # biases with the plain activation
+    out2 = F.fused_experts(x.to(d), w13q.to(d), w2q.to(d), tw.to(d), ids.to(d), use_fp8_w8a8=True, w13_scale=s13.to(d),
+                           w2_scale=s2.to(d), b13=b13.to(d), b2=b2.to(d), block_tokens=bt)
+    F.check_status()
+    ref2 = OM.fused_experts_fp8(x, w13q, w2q, s13, s2, tw, ids, b1=b13, b2=b2)
+    assert_parity(out2, ref2, what=f"fp8 bias + silu {(h, i, e, k, m, bt)}")

@@ -66,3 +66,26 @@ def test_int4_through_reference_signature(cuda_device):
     flaggems_sglang.check_status()
     ref = OM.fused_experts_awq(x, *q1, *q2, tw, ids)
     assert_parity(out, ref, rtol=2e-2, atol=2e-2, what="int4 reference signature")
+
+
+@pytest.mark.parametrize("m,bt", [(20, 16), (60, 32), (300, 64), (300, 128)])
+def test_int4_bias_and_clamped_swiglu(cuda_device, m, bt):
+    """Per-expert biases and the bias variant's activation on both int4 kernels (integer MMAs for
+    blocks of 16 / 32 tokens, fp16 operands above)."""
+    import flaggems_sglang_b200 as F
+    from flaggems_sglang_b200.quant import repack_awq_for_kernel
+    h, i, e, k = 512, 256, 4, 2
+    x, tw, ids, q1, q2 = _case(h, i, e, k, m, seed=m + bt)
+    g = torch.Generator().manual_seed(m)
+    b13 = (torch.randn(e, 2 * i, generator=g) * 0.5).to(torch.float16)
+    b2 = (torch.randn(e, h, generator=g) * 0.5).to(torch.float16)
+    d = cuda_device
+    p1, z1 = repack_awq_for_kernel(*[t.to(d) for t in q1])
+    p2, z2 = repack_awq_for_kernel(*[t.to(d) for t in q2])
+    out = F.fused_experts(x.to(d), p1, p2, tw.to(d), ids.to(d), use_int4_w4a16=True, w13_sz=z1, w2_sz=z2,
+                          activation="swiglu_oai", b13=b13.to(d), b2=b2.to(d), swiglu_alpha=1.702, swiglu_limit=7.0,
+                          block_tokens=bt)
+    F.check_status()
+    ref = OM.fused_experts_awq(x, *q1, *q2, tw, ids, activation="swiglu_oai", b1=b13, b2=b2, swiglu_alpha=1.702,
+                               swiglu_limit=7.0)
+    assert_parity(out, ref, rtol=2e-2, atol=2e-2, what=f"int4 bias M={m} BT={bt}")
