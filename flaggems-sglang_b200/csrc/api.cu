@@ -140,9 +140,10 @@ int pick_bt(const b200moe_cfg* c) {
   if (c->wmode == B200MOE_W_FP8_BLOCK) {
     // many-expert FP8 layers route unevenly: hot experts hold several times the average, and every
     // extra block of an expert streams its weights once more from L2, so lean towards larger blocks
+    // (measured on the 256-expert zipf-skewed layer: M = 64 -> 16 is best; M = 512, average 16 ->
+    // tokens-on-M blocks of 128 beat 64-token blocks by 11 %, 32-token blocks lose 38 %)
     if (avg <= 4) return 16;
     if (avg <= 12) return 32;
-    if (avg < 24) return 64;
     return 128;  // tokens-on-M kernels
   }
   if (avg <= 10) return 16;
@@ -492,6 +493,13 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
     g2.out_sum = nullptr;
   }
   if (fp8) gemm_plan_fp8(&g2); else if (w4p) gemm_plan_w4(&g2); else gemm_plan(&g2);
+  // CTA pairs for the 16-bit prefill GEMMs (each GEMM by itself: the down projection only when its
+  // reduction is in one piece)
+  const bool pair_flag = (c->flags & B200MOE_FLAG_CTA_PAIR) != 0 && !(c->flags & B200MOE_FLAG_SIMT) && sms >= 2;
+  const bool pair1 = pair_flag && gemm_tc2_ok(g1);
+  const bool pair2 = pair_flag && gemm_tc2_ok(g2);
+  if (pair1) gemm_plan_tc2(&g1);
+  if (pair2) gemm_plan_tc2(&g2);
 
   if (c->flags & B200MOE_FLAG_SIMT) {
     rc = launch_gemm_simt(w1, xs, g1, st, L.cap);
@@ -517,7 +525,7 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
         return rc;
     } else {
       if ((rc = make_tmap_3d(&tm_w1, dt, eb, w1, c->H, 2ull * c->I, c->E, kbox, 128)) != B200MOE_OK) return rc;
-      if ((rc = make_tmap_3d(&tm_w2, dt, eb, w2, c->I, c->H, c->E, kbox, (L.orient == 1 && !fp8) ? 256 : 128)) != B200MOE_OK)
+      if ((rc = make_tmap_3d(&tm_w2, dt, eb, w2, c->I, c->H, c->E, kbox, (L.orient == 1 && !fp8 && !pair2) ? 256 : 128)) != B200MOE_OK)
         return rc;
     }
     // int4 decode: a token block is 3 * BT consecutive rows (its three byte planes)
@@ -527,12 +535,14 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
     if ((rc = make_tmap_2d(&tm_a2, dt, eb, a2, c->I, xrows, kbox, xbox)) != B200MOE_OK) return rc;
     prof_mark(slot, 1, st);
     rc = fp8 ? launch_gemm_fp8(tm_w1, tm_x, g1, sms, st)
-             : (w4p ? launch_gemm_w4(tm_w1, tm_x, g1, sms, st) : launch_gemm_tc(tm_w1, tm_x, g1, sms, st));
+             : (w4p ? launch_gemm_w4(tm_w1, tm_x, g1, sms, st)
+                    : (pair1 ? launch_gemm_tc2(tm_w1, tm_x, g1, sms, st) : launch_gemm_tc(tm_w1, tm_x, g1, sms, st)));
     prof_mark(slot, 2, st);
     if (rc != B200MOE_OK) return rc;
     prof_mark(slot, 3, st);
     rc = fp8 ? launch_gemm_fp8(tm_w2, tm_a2, g2, sms, st)
-             : (w4p ? launch_gemm_w4(tm_w2, tm_a2, g2, sms, st) : launch_gemm_tc(tm_w2, tm_a2, g2, sms, st));
+             : (w4p ? launch_gemm_w4(tm_w2, tm_a2, g2, sms, st)
+                    : (pair2 ? launch_gemm_tc2(tm_w2, tm_a2, g2, sms, st) : launch_gemm_tc(tm_w2, tm_a2, g2, sms, st)));
     prof_mark(slot, 4, st);
     if (rc != B200MOE_OK) return rc;
   }
@@ -1013,6 +1023,8 @@ int b200moe_per_token_group_quant_fp8(const void* x, int dtype, int rows, int K,
   return launch_group_quant_fp8(x, dtype, q, scales, nullptr, nullptr, 0, 1, rows, K, 0, 0, nullptr, 0,
                                 query_sms(nullptr), static_cast<cudaStream_t>(stream), false);
 }
+
+int b200moe_debug_resident_cta_pairs(void) { return gemm_tc2_resident_pairs(); }
 
 int b200moe_launch_stats(long long* total_launches, char* last_call_names, size_t names_bytes) {
   std::lock_guard<std::mutex> lk(g_launches.mu);

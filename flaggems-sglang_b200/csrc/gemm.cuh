@@ -99,6 +99,12 @@ int launch_gemm_fp8(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const Gemm
 void gemm_plan_w4(GemmArgs* a);
 int launch_gemm_w4(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmArgs& a, int num_sms,
                    cudaStream_t stream);
+// 16-bit, 128-token blocks, on CTA pairs (tcgen05.mma.cta_group::2): see gemm_tc2.cu
+bool gemm_tc2_ok(const GemmArgs& a);
+int gemm_tc2_resident_pairs();   // CTA pairs the device kept resident for the last such launch (0: none yet)
+void gemm_plan_tc2(GemmArgs* a);
+int launch_gemm_tc2(const CUtensorMap& tm_w, const CUtensorMap& tm_x, const GemmArgs& a, int num_sms,
+                    cudaStream_t stream);
 int launch_gemm_simt(const void* w, const void* x, const GemmArgs& a, cudaStream_t stream, int cap);
 
 }  // namespace b200moe

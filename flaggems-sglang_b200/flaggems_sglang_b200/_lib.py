@@ -23,6 +23,7 @@ FLAG_WEIGHT_ON_INPUT, FLAG_MIMIC_ROUNDING, FLAG_SIMT, FLAG_IDS_I64, FLAG_NO_SPLI
     FLAG_NO_GRID_BALANCE, FLAG_NO_PDL, FLAG_W4_SMEM_OPERANDS, FLAG_NO_COMBINE, FLAG_ALIGN_ONE_CTA, FLAG_X_FP8 = \
     1, 2, 4, 8, 16, 32, 64, 128, 256, 512, 1024
 FLAG_EP_DIAG_LOCAL_COMBINE = 2048
+FLAG_CTA_PAIR = 4096
 
 
 class Cfg(C.Structure):
@@ -96,6 +97,7 @@ SYMBOLS = {
     "b200moe_ep_forward": (C.c_int, [C.POINTER(Cfg), C.POINTER(EpCfg), C.POINTER(C.c_void_p), C.c_int, C.c_void_p,
                                      C.c_void_p, C.c_void_p, C.POINTER(Quant), C.c_void_p, C.c_void_p, C.c_void_p,
                                      C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "b200moe_debug_resident_cta_pairs": (C.c_int, []),
     "b200moe_launch_stats": (C.c_int, [C.POINTER(C.c_longlong), C.c_char_p, C.c_size_t]),
     "b200moe_selftest_timeout": (C.c_int, [C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p]),
     "b200moe_per_token_group_quant_fp8": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p,

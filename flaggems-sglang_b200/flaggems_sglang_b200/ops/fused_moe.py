@@ -139,6 +139,8 @@ def _env_flags() -> int:
         f |= _lib.FLAG_NO_PDL
     if os.environ.get("B200MOE_W4_SMEM_OPERANDS", "0") == "1":
         f |= _lib.FLAG_W4_SMEM_OPERANDS
+    if os.environ.get("B200MOE_CTA_PAIR", "0") == "1":
+        f |= _lib.FLAG_CTA_PAIR
     return f
 
 

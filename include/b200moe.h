@@ -65,6 +65,8 @@ extern "C" {
                                            names the 16-bit type of the intermediate and the output   */
 #define B200MOE_FLAG_EP_DIAG_LOCAL_COMBINE 2048 /* tuning aid, expert parallelism: the down projection's rows stay on
                                            this GPU (WRONG results; isolates the cost of the peer stores)      */
+#define B200MOE_FLAG_CTA_PAIR 4096      /* 16-bit prefill (128-token blocks): run the grouped GEMMs on CTA pairs
+                                           (tcgen05.mma.cta_group::2) where the shape allows                   */
 #define B200MOE_FLAG_ALIGN_ONE_CTA 512  /* tuning aid: single-CTA alignment however many slots           */
 #define B200MOE_FLAG_NO_COMBINE 256     /* out is [M*topk, H]: row t*topk+j holds pair j of token t,
                                            routing weight applied, nothing summed, routed_scaling ignored
@@ -355,6 +357,9 @@ int b200moe_profile_end(double *gemm1_ms, double *gemm2_ms, double *total_ms, do
  * characters).  Returns the number of kernels in that list.
  */
 int b200moe_launch_stats(long long *total_launches, char *last_call_names, size_t names_bytes);
+/* CTA pairs the device kept resident for the last grouped GEMM launched on CTA pairs
+ * (B200MOE_FLAG_CTA_PAIR); 0 before the first such launch.  Diagnostics. */
+int b200moe_debug_resident_cta_pairs(void);
 
 /*
  * Self-test of the device-side time-out path (no counterpart in the reference, which has no
