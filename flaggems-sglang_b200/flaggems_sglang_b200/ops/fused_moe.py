@@ -73,6 +73,36 @@ def _status_word(dev: torch.device) -> torch.Tensor:
     return st
 
 
+_status_host: dict = {}    # device index -> pinned int32[1] that trails the device word
+_status_calls: dict = {}
+STATUS_COPY_EVERY = 16     # calls between two asynchronous copies of the status word to the host
+
+
+def _deferred_status_check(dev: torch.device, status: torch.Tensor) -> None:
+    """Catches a device-side time-out without ever synchronising: after every
+    ``STATUS_COPY_EVERY``-th call the status word is copied (asynchronously, four bytes) to pinned
+    host memory, and every call looks at the host copy first.  A time-out therefore surfaces a
+    few calls after the kernels that hit it have finished, even in a host that never calls
+    ``check_status()``.  ``B200MOE_DEFERRED_STATUS=0`` switches it off."""
+    if os.environ.get("B200MOE_DEFERRED_STATUS", "1") == "0":
+        return
+    host = _status_host.get(dev.index)
+    if host is None:
+        host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        _status_host[dev.index] = host
+        _status_calls[dev.index] = 0
+    elif not torch.cuda.is_current_stream_capturing():
+        code = int(host[0])          # plain host read: whatever an earlier copy has delivered
+        if code != 0:
+            host.zero_()
+            status.zero_()
+            raise RuntimeError(f"b200moe: a device-side wait timed out (code {code}) in an earlier call on "
+                               f"cuda:{dev.index}; that call's output is invalid")
+    _status_calls[dev.index] += 1
+    if _status_calls[dev.index] % STATUS_COPY_EVERY == 1 and not torch.cuda.is_current_stream_capturing():
+        host.copy_(status, non_blocking=True)
+
+
 def check_status(device=None) -> None:
     """Synchronise and raise if a kernel reported a device-side time-out since
     the last check.  Never called on the hot path."""
@@ -84,6 +114,8 @@ def check_status(device=None) -> None:
         code = int(st.item())
         if code != 0:
             st.zero_()
+            if idx in _status_host:
+                _status_host[idx].zero_()
             raise RuntimeError(f"b200moe: device-side wait timed out (code {code}) on cuda:{idx}")
 
 
@@ -338,6 +370,7 @@ def fused_experts(
                 topk_indx.data_ptr(), gate_scal.data_ptr(), base, avail, out.data_ptr(),
                 status.data_ptr(), stream)
     _lib.check(rc, "fused_experts")
+    _deferred_status_check(dev, status)
     if os.environ.get("B200MOE_CHECK_STATUS", "0") == "1":
         check_status(dev)
     return out

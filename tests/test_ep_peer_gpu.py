@@ -214,3 +214,45 @@ def test_peer_mode_two_gpus(shape, balanced):
             assert frac >= 0.99 and max_err <= 1e-2 * max(1.0, scale) + 1e-2 * scale, (r, ret[r])
             if shape[4] * shape[3] >= 4096:
                 assert same_bits, f"rank {r}: pair rows must reproduce the single-GPU bits"
+
+
+def test_emulated_call_replays_from_a_cuda_graph(cuda_device):
+    """Nothing in the expert-parallel call reads device data on the host and the epoch lives in
+    device memory, so the whole call -- all phases of all (emulated) ranks -- can be captured once
+    and replayed; every replay opens a new epoch and gives the same bits."""
+    from flaggems_sglang_b200 import ep
+    h, i, e, k, m = 512, 256, 8, 2, 64
+    x, tw, ids, w13q, s13, w2q, s2 = _case(h, i, e, k, m, seed=21)
+    d = cuda_device
+    world, mr = 2, m // 2
+    placement = ep.plan_placement(e, world)
+    ctxs = ep.EpContext.emulate(world, mr, h, i, k, e // world, e, d)
+    try:
+        shards = [tuple(t[ep.local_experts(placement, r)].contiguous().to(d) for t in (w13q, s13, w2q, s2))
+                  for r in range(world)]
+        toks = [tuple(t[r * mr:(r + 1) * mr].contiguous().to(d) for t in (x, tw, ids)) for r in range(world)]
+        outs = [torch.empty(mr, h, dtype=x.dtype, device=d) for _ in range(world)]
+
+        def call():
+            for phase in (1, 2, 4):
+                for r in range(world):
+                    (a13, as13, a2, as2), (xr, twr, idr) = shards[r], toks[r]
+                    ctxs[r].forward(xr, a13, a2, as13, as2, twr, idr, placement, phases=phase, out=outs[r])
+
+        call()                                        # outside capture first (placement upload, lazy set-up)
+        torch.cuda.synchronize()
+        eager = torch.cat(outs).clone()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            call()
+        for _ in range(3):
+            for o in outs:
+                o.zero_()
+            g.replay()
+            torch.cuda.synchronize()
+            for c in ctxs:
+                c.check_status()
+            assert torch.equal(torch.cat(outs), eager)
+        assert_parity(eager, OM.fused_experts_fp8(x, w13q, w2q, s13, s2, tw, ids), what="ep graph replay")
+    finally:
+        ep.EpContext.close_emulated(ctxs)

@@ -328,3 +328,46 @@ def test_no_combine_quantised(cuda_device, mode):
         whole = fused_experts(x.to(d), k13, k2, tw.to(d), ids.to(d), use_int4_w4a16=True, w13_sz=z13, w2_sz=z2)
     assert pairs.shape == (M, topk, H)
     _assert_close(pairs.float().sum(1).to(whole.dtype), whole, rtol=2e-2, atol=2e-2, what=f"no_combine {mode}")
+
+
+def test_adapters_twice_with_the_same_weight_objects(cuda_device):
+    """A serving step passes the same weight tensors every time: the second call of every entry
+    point must succeed and reuse the cached re-layout (nothing is re-laid out per call)."""
+    import importlib
+    import flaggems_sglang
+    fm = importlib.import_module("flaggems_sglang_b200.ops.fused_moe")
+    d = cuda_device
+    M, K, N, E, topk = 21, 256, 256, 8, 2
+    x, w1, w2, tw, ids = _ref_inputs(M, K, N, E, topk, d)
+    w1d, w2d = w1.to(d), w2.to(d)                                  # op layout [E, K, 2N] / [E, N, K]
+    rd, gi, si = flaggems_sglang.topk_to_routing(tw.to(d), ids.to(d), E)
+    a = flaggems_sglang.triton_kernel_fused_experts(x.to(d), w1d, w2d, rd, gi, si)
+    ptr1 = fm._layer_layout(w1d).data_ptr()
+    b = flaggems_sglang.triton_kernel_fused_experts(x.to(d), w1d, w2d, rd, gi, si)
+    assert fm._layer_layout(w1d).data_ptr() == ptr1 and torch.equal(a, b)
+    # bias variant: interleaved columns split once per weight object
+    _, w1b, w2b, b1, b2, _, _ = _bias_inputs(M, K, N, E, topk, seed=3)
+    w1bd, w2bd, b1d, b2d = w1b.to(d), w2b.to(d), b1.to(d), b2.to(d)
+    f = flaggems_sglang.triton_kernel_fused_experts_with_bias
+    c1 = f(x.to(d), w1bd, None, b1d, w2bd, None, b2d, rd, gi, si)
+    split_ptr = fm._deinterleaved(w1bd, b1d)[0].data_ptr()
+    c2 = f(x.to(d), w1bd, None, b1d, w2bd, None, b2d, rd, gi, si)
+    assert fm._deinterleaved(w1bd, b1d)[0].data_ptr() == split_ptr and torch.equal(c1, c2)
+    # the serving hook on a biased layer, twice
+    obj, layer, disp = _adapter_objects(x, w1b.transpose(1, 2).contiguous(), w2b.transpose(1, 2).contiguous(), tw, ids, d, E,
+                                        b13=b1, b2=b2)
+    h1 = flaggems_sglang.fused_moe_flagos(obj, layer, disp).hidden_states
+    h2 = flaggems_sglang.fused_moe_flagos(obj, layer, disp).hidden_states
+    flaggems_sglang.check_status()
+    assert torch.equal(h1, h2)
+    # int4 adapter: AWQ tensors repacked once per qweight object
+    from flaggems_sglang_b200.quant import quantize_awq
+    xh = x.to(torch.float16).to(d)
+    q1 = [t.to(d) for t in quantize_awq((w1.float() * 0.2).to(torch.float16))]
+    q2 = [t.to(d) for t in quantize_awq((w2.float() * 0.2).to(torch.float16))]
+    kw = dict(w1_scale=q1[1], w2_scale=q2[1], use_int4_w4a16=True, w1_zp=q1[2], w2_zp=q2[2])
+    i1 = flaggems_sglang.triton_kernel_fused_experts(xh, q1[0], q2[0], rd, gi, si, **kw)
+    rp = fm._awq_repacked(q1[0], q1[1], q1[2])[0].data_ptr()
+    i2 = flaggems_sglang.triton_kernel_fused_experts(xh, q1[0], q2[0], rd, gi, si, **kw)
+    flaggems_sglang.check_status()
+    assert fm._awq_repacked(q1[0], q1[1], q1[2])[0].data_ptr() == rp and torch.equal(i1, i2)

@@ -49,6 +49,40 @@ def test_wait_runs_out_sets_status_and_context_survives(cuda_device):
     assert_parity(out, OM.fused_experts(x, w13, w2, tw, ids), what="call after a provoked time-out")
 
 
+def test_timeout_surfaces_without_anyone_calling_check_status(cuda_device):
+    """A serving host never calls check_status(): the operator itself notices, a few calls later
+    and without synchronising, through the host copy of the status word."""
+    import importlib
+    import flaggems_sglang_b200 as F
+    from flaggems_sglang_b200 import _lib
+    fm = importlib.import_module("flaggems_sglang_b200.ops.fused_moe")
+    from flaggems_sglang_b200.testing import make_tokens, make_weights
+    lib = _lib.lib()
+    d = cuda_device
+    torch.cuda.set_device(d)
+    F.check_status()
+    h, i, e, k, m = 512, 256, 8, 2, 40
+    w13, w2 = make_weights(h, i, e, seed=1, scale=0.05)
+    x, tw, ids = make_tokens(m, h, e, k, seed=1)
+    args = (x.to(d), w13.to(d), w2.to(d), tw.to(d), ids.to(d))
+    F.fused_experts(*args)                                     # makes sure the host copy exists
+    observed = torch.zeros(3, dtype=torch.int32, device=d)
+    assert lib.b200moe_selftest_timeout(1_000_000, fm._status_word(d).data_ptr(), observed.data_ptr(),
+                                        torch.cuda.current_stream().cuda_stream) == _lib.OK
+    raised = 0
+    for _ in range(2 * fm.STATUS_COPY_EVERY + 2):
+        try:
+            F.fused_experts(*args)
+        except RuntimeError as ex:
+            assert "timed out" in str(ex)
+            raised += 1
+        torch.cuda.synchronize()
+    assert raised == 1, f"the provoked time-out surfaced {raised} times"
+    out = F.fused_experts(*args)
+    F.check_status()
+    assert_parity(out, OM.fused_experts(x, w13, w2, tw, ids), what="after the deferred status report")
+
+
 def test_selftest_argument_checks(cuda_device):
     from flaggems_sglang_b200 import _lib
     lib = _lib.lib()
