@@ -140,10 +140,11 @@ int pick_bt(const b200moe_cfg* c) {
   if (c->wmode == B200MOE_W_FP8_BLOCK) {
     // many-expert FP8 layers route unevenly: hot experts hold several times the average, and every
     // extra block of an expert streams its weights once more from L2, so lean towards larger blocks
-    // (measured on the 256-expert zipf-skewed layer: M = 64 -> 16 is best; M = 512, average 16 ->
-    // tokens-on-M blocks of 128 beat 64-token blocks by 11 %, 32-token blocks lose 38 %)
+    // (measured on the 256-expert zipf-skewed layer: average 2 (M = 64) -> 16 is best; average 4: 16 / 32 /
+    // 64 within 4 %; average 8 (M = 256): tokens-on-M blocks of 128 and 64-token blocks beat 32-token blocks
+    // by 10 %; average 12 / 16: blocks of 128 win by 20 % / 11 %)
     if (avg <= 4) return 16;
-    if (avg <= 12) return 32;
+    if (avg < 8) return 32;
     return 128;  // tokens-on-M kernels
   }
   if (avg <= 10) return 16;
@@ -331,6 +332,7 @@ struct PeerOut {
   void* out32[kMaxPeers] = {};
   void* pairs[kMaxPeers] = {};
   uint8_t* pair_valid[kMaxPeers] = {};
+  const FlagWait* rows_wait = nullptr;   // the gather waits for the peers' "rows" flags in its prologue
 };
 
 // Everything after the internal routing tables exist in the workspace.  With `peers` the results
@@ -364,7 +366,8 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
       // rows arrive quantised (e.g. from an expert-parallel dispatch that sends bytes): gather only
       if (quant->x_scale == nullptr) return B200MOE_ERR_BAD_ARG;
       rc = launch_gather_rows(x, xs, sorted_ids, meta, L.P, c->topk, c->H, L.cap, zero, zero_bytes, sms, st, pdl,
-                              quant->x_scale, reinterpret_cast<float*>(ws + L.xs_scale), c->H / 128, L.cap);
+                              quant->x_scale, reinterpret_cast<float*>(ws + L.xs_scale), c->H / 128, L.cap,
+                              peers != nullptr ? peers->rows_wait : nullptr);
     } else if (L.quant_once) {
       float* tok_scale = reinterpret_cast<float*>(ws + L.xq_scale);
       rc = launch_group_quant_fp8(x, c->dtype, ws + L.xq_tok, tok_scale, nullptr, nullptr, L.P, c->topk, c->M, c->H, 0,
@@ -918,11 +921,14 @@ int b200moe_ep_forward(const b200moe_cfg* cfg, const b200moe_ep_cfg* ep, void* c
   }
   if (phases & B200MOE_EP_PHASE_COMPUTE) {
     if (slot < 0 && (phases & B200MOE_EP_PHASE_DISPATCH) == 0) slot = prof_slot_current();
-    // The wait for the peers' rows sits in the prologue of the first alignment kernel; only while a
-    // benchmark is timing the local operator it is a kernel of its own, so that the span can start after it.
+    // Two flags per peer: "ready" (its routing entries are in place) is what the first alignment kernel
+    // waits for in its prologue, "rows" (its token rows are in place, raised later) what the gather waits
+    // for, so the alignment overlaps the tail of the peers' dispatch.  Only while a benchmark is timing
+    // the local operator the wait is a kernel of its own, so that the span can start after it.
     const FlagWait ready = ep_flag_wait(me, H, kEpFlagReady, ep->world, limit_ns, status);
+    const FlagWait rows = ep_flag_wait(me, H, kEpFlagRows, ep->world, limit_ns, status);
     if (slot >= 0) {
-      if ((rc = launch_ep_wait(ready, st, pdl)) != B200MOE_OK) return rc;
+      if ((rc = launch_ep_wait(rows, st, pdl)) != B200MOE_OK) return rc;    // "rows" is raised after "ready"
       prof_mark(slot, 6, st);
     }
     // alignment over every received row: ids are already local (or -1), weights already masked
@@ -934,6 +940,7 @@ int b200moe_ep_forward(const b200moe_cfg* cfg, const b200moe_ep_cfg* ep, void* c
     PeerOut po;
     po.n_peers = ep->world;
     po.tokens_per_peer = ep->m_cap;
+    po.rows_wait = slot >= 0 ? nullptr : &rows;
     for (int r = 0; r < ep->world; ++r) {
       uint8_t* h = reinterpret_cast<uint8_t*>(heaps[(cfg->flags & B200MOE_FLAG_EP_DIAG_LOCAL_COMBINE) ? ep->rank : r]);
       po.out32[r] = h + H.out32;

@@ -46,6 +46,26 @@ constexpr int kDispatchWarps = 4;
 // staging of one quantised row: H bytes + H/128 scales
 __host__ __device__ inline size_t ep_stage_bytes(int H) { return static_cast<size_t>(H) + (((H >> 7) * 4 + 15) & ~15); }
 
+// Where does expert choice `lane` of token i live?  (dr = rank, lid = local expert, w = routing weight;
+// dr = -1: not a choice of this token, or an expert held nowhere)
+__device__ __forceinline__ void ep_route(const EpDispatchArgs& a, int i, int lane, int& dr, int& lid, float& w) {
+  dr = -1;
+  lid = -1;
+  w = 0.f;
+  if (i < a.m && lane < a.topk) {
+    const long long gid = a.ids_i64 ? reinterpret_cast<const long long*>(a.topk_ids)[static_cast<size_t>(i) * a.topk + lane]
+                                    : reinterpret_cast<const int*>(a.topk_ids)[static_cast<size_t>(i) * a.topk + lane];
+    if (gid >= 0 && gid < a.n_global_experts) {
+      const int pl = a.placement[gid];
+      if (pl >= 0 && (pl >> 16) < a.world) {
+        dr = pl >> 16;
+        lid = pl & 0xffff;
+        w = a.topk_weights[static_cast<size_t>(i) * a.topk + lane];
+      }
+    }
+  }
+}
+
 // One CTA (four warps) per token: the warps share the token's 128-wide groups, so that even a few
 // hundred tokens put enough loads in flight, and then copy the staged row to every destination
 // together.  Shared memory (FP8 rows): H bytes of quantised row + H/128 scales.
@@ -61,8 +81,47 @@ ep_dispatch_kernel(const EpDispatchArgs a) {
   uint8_t* me = a.heap[a.rank];
   const int G = a.H >> 7;
 
+  // ---- pass 1: the routing entries of every token, masked per destination.  Every rank gets a row for
+  // every token, so that it never has to guess which rows arrived; they go first and get a flag of
+  // their own, so that the receivers' alignment runs while the token rows are still travelling.
+  for (int i = blockIdx.x; i < a.m_cap; i += gridDim.x) {
+    if (warp != 0) break;
+    int dr = -1, lid = -1;
+    float w = 0.f;
+    ep_route(a, i, lane, dr, lid, w);
+    const size_t row = static_cast<size_t>(a.rank) * a.m_cap + i;
+    if (lane < a.topk) {
+      for (int d = 0; d < a.world; ++d) {
+        const bool mine = dr == d;
+        reinterpret_cast<int*>(a.heap[d] + a.L.recv_ids)[row * a.topk + lane] = mine ? lid : -1;
+        reinterpret_cast<float*>(a.heap[d] + a.L.recv_w)[row * a.topk + lane] = mine ? w : 0.f;
+      }
+    }
+  }
+  // the last CTA to get here opens a new epoch and raises "ready" on every peer (each thread's
+  // stores are fenced before its CTA is counted)
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned int* cnt = reinterpret_cast<unsigned int*>(me + a.L.flags + kEpFlagCtaCount);
+    const unsigned int prev = atomicAdd(cnt, 1u);
+    s_last = (prev == gridDim.x - 1) ? 1 : 0;
+    if (s_last) {
+      *cnt = 0;
+      unsigned long long* ep = reinterpret_cast<unsigned long long*>(me + a.L.flags + kEpFlagEpoch);
+      s_epoch = *ep + 1;
+      *ep = s_epoch;
+      __threadfence_system();
+    }
+  }
+  __syncthreads();
+  if (s_last && threadIdx.x < a.world)
+    st_release_sys_u64(reinterpret_cast<unsigned long long*>(a.heap[threadIdx.x] + a.L.flags + kEpFlagReady) + a.rank,
+                       s_epoch);
+  __syncthreads();
+
   // ---- this rank's result buffer starts empty (peers add to it / mark it only after they have seen
-  // this rank's ready flag, which is raised at the end of this kernel)
+  // this rank's "rows" flag, which is raised at the end of this kernel)
   {
     uint4* z = reinterpret_cast<uint4*>(me + (a.clear_pairs ? a.L.pair_valid : a.L.out32));
     const long long n = a.clear_pairs ? (static_cast<long long>(a.m_cap) * a.topk + 15) / 16
@@ -72,40 +131,21 @@ ep_dispatch_kernel(const EpDispatchArgs a) {
       z[i] = make_uint4(0, 0, 0, 0);
   }
 
+  // ---- pass 2: the token rows, only to the ranks that hold one of the token's experts
   uint8_t* stage = smem;
   float* stage_sc = reinterpret_cast<float*>(stage + a.H);
-  for (int i = blockIdx.x; i < a.m_cap; i += gridDim.x) {
-    // ---- where do this token's experts live?  (every warp looks for itself: 32 bytes of ids)
+  for (int i = blockIdx.x; i < a.m; i += gridDim.x) {
     int dr = -1, lid = -1;
     float w = 0.f;
-    if (i < a.m && lane < a.topk) {
-      const long long gid = a.ids_i64 ? reinterpret_cast<const long long*>(a.topk_ids)[static_cast<size_t>(i) * a.topk + lane]
-                                      : reinterpret_cast<const int*>(a.topk_ids)[static_cast<size_t>(i) * a.topk + lane];
-      if (gid >= 0 && gid < a.n_global_experts) {
-        const int pl = a.placement[gid];
-        if (pl >= 0 && (pl >> 16) < a.world) {
-          dr = pl >> 16;
-          lid = pl & 0xffff;
-          w = a.topk_weights[static_cast<size_t>(i) * a.topk + lane];
-        }
-      }
-    }
-    // ---- routing entries, masked per destination; every rank gets a row for every token so that
-    // it never has to guess which rows arrived
+    ep_route(a, i, lane, dr, lid, w);      // every warp looks for itself: 32 bytes of ids
     unsigned dest_mask = 0;
-    const size_t row = static_cast<size_t>(a.rank) * a.m_cap + i;
-    for (int d = 0; d < a.world; ++d) {
-      const bool mine = dr == d;
-      if (__any_sync(0xffffffffu, mine)) dest_mask |= 1u << d;
-      if (warp == 0 && lane < a.topk) {
-        reinterpret_cast<int*>(a.heap[d] + a.L.recv_ids)[row * a.topk + lane] = mine ? lid : -1;
-        reinterpret_cast<float*>(a.heap[d] + a.L.recv_w)[row * a.topk + lane] = mine ? w : 0.f;
-      }
-    }
+    for (int d = 0; d < a.world; ++d)
+      if (__any_sync(0xffffffffu, dr == d)) dest_mask |= 1u << d;
     if (dest_mask == 0) continue;     // the same in every warp of the CTA
+    const size_t row = static_cast<size_t>(a.rank) * a.m_cap + i;
     const T* xrow = reinterpret_cast<const T*>(a.x) + static_cast<size_t>(i) * a.H;
     if (a.fp8_rows) {
-      // ---- 1x128 quantisation, the arithmetic of group_quant_fp8_kernel (prep.cu) so that a row
+      // 1x128 quantisation, the arithmetic of group_quant_fp8_kernel (prep.cu) so that a row
       // carries the same bits whether it is quantised here or inside a single-GPU call
       constexpr int RUN = 8;
       for (int g0 = warp * RUN; g0 < G; g0 += kDispatchWarps * RUN) {
@@ -153,25 +193,22 @@ ep_dispatch_kernel(const EpDispatchArgs a) {
     }
   }
 
-  // ---- the last CTA to get here opens a new epoch and tells every peer that this rank's rows
-  // are in place (each thread's stores are fenced before its CTA is counted)
+  // ---- the last CTA to get here tells every peer that this rank's rows are in place
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
-    unsigned int* cnt = reinterpret_cast<unsigned int*>(me + a.L.flags + kEpFlagCtaCount);
+    unsigned int* cnt = reinterpret_cast<unsigned int*>(me + a.L.flags + kEpFlagCtaCount2);
     const unsigned int prev = atomicAdd(cnt, 1u);
     s_last = (prev == gridDim.x - 1) ? 1 : 0;
     if (s_last) {
       *cnt = 0;
-      unsigned long long* ep = reinterpret_cast<unsigned long long*>(me + a.L.flags + kEpFlagEpoch);
-      s_epoch = *ep + 1;
-      *ep = s_epoch;
+      s_epoch = *reinterpret_cast<volatile unsigned long long*>(me + a.L.flags + kEpFlagEpoch);
       __threadfence_system();
     }
   }
   __syncthreads();
   if (s_last && threadIdx.x < a.world)
-    st_release_sys_u64(reinterpret_cast<unsigned long long*>(a.heap[threadIdx.x] + a.L.flags + kEpFlagReady) + a.rank,
+    st_release_sys_u64(reinterpret_cast<unsigned long long*>(a.heap[threadIdx.x] + a.L.flags + kEpFlagRows) + a.rank,
                        s_epoch);
 }
 

@@ -5,8 +5,8 @@
 namespace b200moe {
 
 // Every rank owns one "heap" of this layout and maps the heaps of all other ranks (CUDA IPC).
-//   flags       ready[kMaxPeers], done[kMaxPeers] (uint64 epochs written by the peers), then this
-//               rank's own epoch counter and a CTA counter
+//   flags       ready[kMaxPeers], done[kMaxPeers], rows[kMaxPeers] (uint64 epochs written by the
+//               peers), this rank's own epoch counter and two CTA counters
 //   recv_*      what the peers dispatch to this rank: for source rank r and its token i the row
 //               r * m_cap + i holds the token's activations (FP8 + 1x128 scales, or 16-bit), its
 //               top-k expert ids translated to this rank's local experts (-1 = held elsewhere) and
@@ -20,10 +20,12 @@ struct EpHeap {
   size_t flags, recv_ids, recv_w, recv_x, recv_xs, pairs, pair_valid, out32, total;
   int x_row_bytes;
 };
-constexpr size_t kEpFlagReady = 0;                          // byte offsets inside the flags block
-constexpr size_t kEpFlagDone = kMaxPeers * 8;
-constexpr size_t kEpFlagEpoch = 2 * kMaxPeers * 8;
-constexpr size_t kEpFlagCtaCount = 2 * kMaxPeers * 8 + 8;
+constexpr size_t kEpFlagReady = 0;                          // byte offsets inside the flags block (256 bytes)
+constexpr size_t kEpFlagDone = kMaxPeers * 8;               //   ready: the peers' routing entries are in place
+constexpr size_t kEpFlagEpoch = 2 * kMaxPeers * 8;          //   rows:  the peers' token rows are in place (raised later)
+constexpr size_t kEpFlagCtaCount = 2 * kMaxPeers * 8 + 8;   //   done:  the peers' down projections have completed
+constexpr size_t kEpFlagCtaCount2 = 2 * kMaxPeers * 8 + 12;
+constexpr size_t kEpFlagRows = 3 * kMaxPeers * 8;
 
 EpHeap ep_heap_layout(int world, int m_cap, int H, int topk, bool fp8_rows);
 

@@ -16,9 +16,10 @@ __global__ void __launch_bounds__(256)
 gather_rows_kernel(const uint4* __restrict__ x, uint4* __restrict__ xs, const int* __restrict__ sorted_ids,
                    const int* __restrict__ meta, int P, int topk, int chunks_per_row, int cap,
                    uint4* __restrict__ zero, long long zero_chunks, const float* __restrict__ sc_src,
-                   float* __restrict__ sc_dst, int G, int ld) {
+                   float* __restrict__ sc_dst, int G, int ld, const FlagWait fw) {
   griddep_wait();
   griddep_launch_dependents();
+  wait_for_peers(fw);     // expert parallelism: the rows come from the peers
   const int rows = min(meta[1], cap);
   const long long n_copy = static_cast<long long>(rows) * chunks_per_row;
   const long long total = n_copy + zero_chunks;
@@ -290,7 +291,10 @@ int launch_finalize_pairs(const void* pairs, const uint8_t* pair_valid, void* ou
 
 int launch_gather_rows(const void* x, void* xs, const int* sorted_ids, const int* meta, int P, int topk,
                        int row_bytes, int cap, void* zero, size_t zero_bytes, int num_sms,
-                       cudaStream_t stream, bool pdl, const float* sc_src, float* sc_dst, int G, int ld) {
+                       cudaStream_t stream, bool pdl, const float* sc_src, float* sc_dst, int G, int ld,
+                       const FlagWait* wait) {
+  FlagWait fw = {};
+  if (wait != nullptr) fw = *wait;
   if (row_bytes % 16 != 0 || zero_bytes % 16 != 0) return B200MOE_ERR_UNSUPPORTED;
   const long long work = static_cast<long long>(cap) * (row_bytes / 16) + static_cast<long long>(zero_bytes / 16);
   long long ctas = (work + 255) / 256;
@@ -300,7 +304,7 @@ int launch_gather_rows(const void* x, void* xs, const int* sorted_ids, const int
   cudaError_t err = launch_kernel(gather_rows_kernel, dim3(static_cast<unsigned>(ctas)), dim3(256), 0, stream, pdl,
                                   reinterpret_cast<const uint4*>(x), reinterpret_cast<uint4*>(xs), sorted_ids, meta,
                                   P, topk, row_bytes / 16, cap, reinterpret_cast<uint4*>(zero),
-                                  static_cast<long long>(zero_bytes / 16), sc_src, sc_dst, G, ld);
+                                  static_cast<long long>(zero_bytes / 16), sc_src, sc_dst, G, ld, fw);
   return err == cudaSuccess ? B200MOE_OK : B200MOE_ERR_CUDA;
 }
 

@@ -7,11 +7,12 @@ namespace b200moe {
 // xs[r] = x[sorted_ids[r] / topk] for r < meta[1]; padding rows zero-filled.  Also clears
 // `zero_bytes` bytes at `zero` (the fp32 combine buffer) in the same launch.  With sc_src
 // ([tokens][G] group scales of already quantised rows) the scales follow their rows into the
-// group-major table sc_dst [G][ld].
+// group-major table sc_dst [G][ld].  `wait` (expert parallelism): every CTA first waits for the
+// peers' flags (common.cuh: FlagWait).
 int launch_gather_rows(const void* x, void* xs, const int* sorted_ids, const int* meta, int P, int topk,
                        int row_bytes, int cap, void* zero, size_t zero_bytes, int num_sms,
                        cudaStream_t stream, bool pdl, const float* sc_src = nullptr, float* sc_dst = nullptr,
-                       int G = 0, int ld = 0);
+                       int G = 0, int ld = 0, const FlagWait* wait = nullptr);
 
 // Per-token-group (1x128) FP8 quantisation, optionally gathering rows through
 // sorted_ids like launch_gather_rows.  scale_t: store scales group-major.
