@@ -7,6 +7,7 @@
 #include "align.cuh"
 #include "ep.cuh"
 #include "gemm.cuh"
+#include "gemv.cuh"
 #include "prep.cuh"
 #include "router.cuh"
 
@@ -560,6 +561,65 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
   return rc;
 }
 
+// A handful of (token, choice) pairs: two matrix-vector launches straight from the routing input
+// instead of alignment, gather, grouped GEMMs and output conversion (gemv.cuh).  Returns
+// B200MOE_ERR_UNSUPPORTED when the call does not qualify; the caller then takes the usual path.
+// A caller that fixes the token block (cfg.block_tokens) asks for the grouped GEMMs.
+int run_gemv(const b200moe_cfg* c, const Layout& L, const void* x, const void* w1, const void* w2,
+             const b200moe_quant* quant, const float* topk_weights, const void* topk_ids,
+             const int32_t* expert_map, const int32_t* hist, const int32_t* topk_indx, const float* gate_scal,
+             uint8_t* ws, void* out, cudaStream_t st, int slot) {
+  // 16-bit weights only: FP8 and int4 rows need their conversions on the CUDA cores, which costs
+  // more than the launches saved (measured: a 32-expert FP8 layer at M = 1 took 152 us this way, 97 us
+  // on the grouped tensor-core path)
+  if (L.P <= 0 || L.P > kGemvMaxPairs || c->block_tokens != 0) return B200MOE_ERR_UNSUPPORTED;
+  if (c->wmode != B200MOE_W_16BIT || (c->flags & B200MOE_FLAG_SIMT)) return B200MOE_ERR_UNSUPPORTED;
+  const int sms = query_sms(c);
+  GemvArgs g = {};
+  g.x = x;
+  g.w1 = w1;
+  g.w2 = w2;
+  g.topk_w = topk_weights;
+  g.topk_ids = topk_ids;
+  g.expert_map = expert_map;
+  g.hist = hist;
+  g.topk_indx = topk_indx;
+  g.gate_scal = gate_scal;
+  g.ids_i64 = (c->flags & B200MOE_FLAG_IDS_I64) ? 1 : 0;
+  g.n_global = c->n_global_experts;
+  g.M = c->M;
+  g.H = c->H;
+  g.I = c->I;
+  g.E = c->E;
+  g.topk = c->topk;
+  g.dtype = c->dtype;
+  g.activation = c->activation;
+  g.flags = c->flags;
+  g.round_pair =
+      ((c->flags & B200MOE_FLAG_MIMIC_ROUNDING) && reference_rounds_pairs(L.P, c->E, c->H, c->I, sms)) ? 1 : 0;
+  g.alpha = 1.0f;
+  g.routed_scaling = c->routed_scaling;
+  if (quant != nullptr) {
+    g.alpha = quant->swiglu_alpha;
+    g.limit = quant->swiglu_limit;
+    g.b1 = quant->b1;
+    g.b2 = quant->b2;
+  }
+  g.act = ws + L.a2;   // the pairs' activations go where the grouped path keeps GEMM-1's output (cap >= P rows)
+  g.out = out;
+  if (!gemv_fits(g)) return B200MOE_ERR_UNSUPPORTED;
+  const bool pdl = (c->flags & B200MOE_FLAG_NO_PDL) == 0;
+  prof_mark(slot, 1, st);
+  int rc = launch_gemv_up(g, sms, st, pdl);
+  prof_mark(slot, 2, st);
+  if (rc != B200MOE_OK) return rc;
+  prof_mark(slot, 3, st);
+  rc = launch_gemv_down(g, sms, st, pdl);
+  prof_mark(slot, 4, st);
+  prof_mark(slot, 5, st);
+  return rc;
+}
+
 }  // namespace
 
 namespace b200moe {
@@ -672,6 +732,9 @@ int b200moe_forward_topk(const b200moe_cfg* cfg, const void* x, const void* w1, 
   launch_log_new_call();
   const int slot = prof_slot();
   prof_mark(slot, 0, st);
+  rc = run_gemv(cfg, L, x, w1, w2, quant, topk_weights, topk_ids, expert_map, nullptr, nullptr, nullptr, ws, out, st,
+                slot);
+  if (rc != B200MOE_ERR_UNSUPPORTED) return rc;
   rc = align_into_workspace(cfg, L, ws, topk_ids, (cfg->flags & B200MOE_FLAG_IDS_I64) ? 1 : 0, expert_map,
                             topk_weights, st);
   if (rc != B200MOE_OK) return rc;
@@ -707,6 +770,8 @@ int b200moe_forward_logits(const b200moe_cfg* cfg, const b200moe_router* router,
   prof_mark(slot, 0, st);
   rc = launch_route_topk(router, logits, cfg->M, cfg->E, cfg->topk, tw, ids, query_sms(cfg), st);
   if (rc != B200MOE_OK) return rc;
+  rc = run_gemv(cfg, L, x, w1, w2, quant, tw, ids, expert_map, nullptr, nullptr, nullptr, ws, out, st, slot);
+  if (rc != B200MOE_ERR_UNSUPPORTED) return rc;
   rc = align_into_workspace(cfg, L, ws, ids, 0, expert_map, tw, st);
   if (rc != B200MOE_OK) return rc;
   return run_experts(cfg, L, x, w1, w2, quant, ws, out, status, st, slot);
@@ -726,6 +791,8 @@ int b200moe_forward_routed(const b200moe_cfg* cfg, const void* x, const void* w1
   launch_log_new_call();
   const int slot = prof_slot();
   prof_mark(slot, 0, st);
+  rc = run_gemv(cfg, L, x, w1, w2, quant, nullptr, nullptr, nullptr, hist, topk_indx, gate_scal, ws, out, st, slot);
+  if (rc != B200MOE_ERR_UNSUPPORTED) return rc;
   rc = launch_align_from_routing(hist, topk_indx, gate_scal, L.P, cfg->E, L.BT, L.cap,
                                  reinterpret_cast<int*>(ws + L.sorted_ids),
                                  reinterpret_cast<float*>(ws + L.row_gamma),

@@ -321,6 +321,20 @@ __device__ __forceinline__ void tmem_ld16x2_wait(uint32_t taddr0, uint32_t taddr
   }
 }
 
+// Raw 32-bit words of two 16-column reads (for packed f32x2 arithmetic on register pairs).
+__device__ __forceinline__ void tmem_ld16x2_wait_u32(uint32_t taddr0, uint32_t taddr1, uint32_t (&r0)[16],
+                                                     uint32_t (&r1)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, "
+      "%13, %14, %15}, [%32];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, "
+      "%27, %28, %29, %30, %31}, [%33];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : B200MOE_R16(r0, 0), B200MOE_R16(r1, 0)
+      : "r"(taddr0), "r"(taddr1)
+      : "memory");
+}
+
 #define B200MOE_R32(r, o) B200MOE_R16(r, o), B200MOE_R16(r, o + 16)
 // 32 consecutive fp32 columns of the thread's TMEM lane (load + wait in one statement).
 __device__ __forceinline__ void tmem_ld32_wait(uint32_t taddr, float (&v)[32]) {
@@ -393,16 +407,23 @@ __host__ __device__ __forceinline__ uint32_t make_idesc_i8(bool a_signed, bool b
   return d;
 }
 
-// Two fp32 fused multiply-adds in one instruction (packed f32x2, sm_100): c += a * s.
-__device__ __forceinline__ void ffma2(float& c0, float& c1, float a0, float a1, float s) {
-  asm("{\n\t.reg .b64 ra, rc, rs;\n\t"
-      "mov.b64 ra, {%2, %3};\n\t"
-      "mov.b64 rc, {%0, %1};\n\t"
-      "mov.b64 rs, {%4, %4};\n\t"
-      "fma.rn.f32x2 rc, ra, rs, rc;\n\t"
-      "mov.b64 {%0, %1}, rc;\n\t}"
-      : "+f"(c0), "+f"(c1)
-      : "f"(a0), "f"(a1), "f"(s));
+// Two fp32 fused multiply-adds in one instruction (packed f32x2, sm_100) on accumulators that stay
+// packed, two fp32 to a 64-bit register, across a whole reduction loop, so that no pack / unpack
+// moves surround the instruction: c += {a0, a1} * s2.
+__device__ __forceinline__ unsigned long long pack_f32x2(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(unsigned long long v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ void ffma2_packed(unsigned long long& c, uint32_t a0, uint32_t a1, unsigned long long s2) {
+  asm("{\n\t.reg .b64 ra;\n\t"
+      "mov.b64 ra, {%1, %2};\n\t"
+      "fma.rn.f32x2 %0, ra, %3, %0;\n\t}"
+      : "+l"(c)
+      : "r"(a0), "r"(a1), "l"(s2));
 }
 
 // Programmatic dependent launch: a kernel launched with the stream-serialisation attribute may

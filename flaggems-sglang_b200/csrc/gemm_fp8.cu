@@ -591,11 +591,12 @@ moe_gemm_fp8_tokm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
       const int orow = s_col_row[buf * 128 + lrow];
       const float gam = s_col_gam[buf * 128 + lrow];
 
-      float accA[64], accB[64];
+      // running sums stay packed two to a 64-bit register for the whole reduction
+      unsigned long long pA[32], pB[32];
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        accA[i] = 0.f;
-        accB[i] = 0.f;
+      for (int i = 0; i < 32; ++i) {
+        pA[i] = 0ull;
+        pB[i] = 0ull;
       }
       for (int kb = t.kb0; kb < t.kb1; ++kb, ++j) {
         const float sx = xs_t[(kb - t.kb0) * BT + lrow];
@@ -610,15 +611,17 @@ moe_gemm_fp8_tokm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
         }
         tc_fence_after();
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + pb * PCOLS;
+        // packed f32x2 FMAs on register pairs (one instruction per two accumulators), 16 columns of
+        // each half at a time to stay inside the register budget
+        const unsigned long long fA2 = pack_f32x2(fA, fA), fB2 = pack_f32x2(fB, fB);
 #pragma unroll
-        for (int c0 = 0; c0 < 64; c0 += 32) {
-          float g[32], u[32];
-          tmem_ld32x2_wait(taddr + colA + c0, taddr + colB + c0, g, u);
-          // packed f32x2 FMAs: the promotion is bound by instruction issue
+        for (int c0 = 0; c0 < 64; c0 += 16) {
+          uint32_t g[16], u[16];
+          tmem_ld16x2_wait_u32(taddr + colA + c0, taddr + colB + c0, g, u);
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            ffma2(accA[c0 + i], accA[c0 + i + 1], g[i], g[i + 1], fA);
-            ffma2(accB[c0 + i], accB[c0 + i + 1], u[i], u[i + 1], fB);
+          for (int i = 0; i < 8; ++i) {
+            ffma2_packed(pA[c0 / 2 + i], g[2 * i], g[2 * i + 1], fA2);
+            ffma2_packed(pB[c0 / 2 + i], u[2 * i], u[2 * i + 1], fB2);
           }
         }
         tc_fence_before();
@@ -627,6 +630,12 @@ moe_gemm_fp8_tokm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
       }
       if (!ok) break;
       const long long tail_t0 = clock64();
+      float accA[64], accB[64];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        unpack_f32x2(pA[i], accA[2 * i], accA[2 * i + 1]);
+        unpack_f32x2(pB[i], accB[2 * i], accB[2 * i + 1]);
+      }
 
       if (MODE == 1 && a.bias != nullptr && t.kb0 == 0) {
         // bias of columns n0 + 128 grp + [0, 128): accA holds the first 64, accB the next 64

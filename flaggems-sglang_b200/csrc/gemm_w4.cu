@@ -99,6 +99,7 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   uint64_t* bar_zempty = bar_zfull + kSzSlots; // [kSzSlots] scale words read by every promotion warp
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_zempty + kSzSlots);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* s_nvalid = reinterpret_cast<int*>(tmem_slot + 2);            // [2] columns up to the last valid token
   int* s_col_row = reinterpret_cast<int*>(tmem_slot + 4);           // [2][32]
   float* s_col_gam = reinterpret_cast<float*>(s_col_row + 2 * 32);  // [2][32]
   unsigned int* s_amax = reinterpret_cast<unsigned int*>(s_col_gam + 2 * 32);   // [2][32] tail: group maxima
@@ -274,6 +275,16 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       }
       s_amax[buf * 32 + lane] = 0u;
       s_osum[buf * 32 + lane] = 0;
+      {
+        // columns past the last valid token carry zeros: the promotion warps skip them
+        int slot_ok = 0;
+        if (lane < BT) {
+          const int slot = a.sorted_ids[t.row0 + lane];
+          slot_ok = slot >= 0 && slot < a.P;
+        }
+        const unsigned int m = __ballot_sync(0xffffffffu, slot_ok);
+        if (lane == 0) s_nvalid[buf] = 32 - __clz(m);
+      }
       __syncwarp();
       const int nkb = t.kb1 - t.kb0;
       const uint32_t sfull = smem_u32(&bar_sfull[buf]);
@@ -373,6 +384,10 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       if (!mbar_wait_t(smem_u32(&bar_sfull[buf]), (iter >> 1) & 1, abort_flag, DEV_TIMEOUT_EPILOGUE, w_sfull)) break;
       const float* xf_t = s_xf + buf * nkb_max * BT + tk0;
       const int* xs_t = s_xsum + buf * nkb_max * BT + tk0;
+      // valid columns of this thread's half (the same for the whole warp): with 16-token blocks the
+      // arithmetic runs in chunks of four columns and skips the chunks that hold padding only; with
+      // 32-token blocks a half that holds padding only is skipped
+      const int nv = s_nvalid[buf] - tk0;
 
       float acc0[HT], acc1[HT];
 #pragma unroll
@@ -398,6 +413,14 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         int xsv[HT];
 #pragma unroll
         for (int q = 0; q < HT / 4; ++q) {
+          if (nv <= (HT == 8 ? 4 * q : 0)) {   // 32-token blocks skip by halves only (register budget)
+#pragma unroll
+            for (int i = 4 * q; i < 4 * q + 4; ++i) {
+              xfv[i] = 0.f;
+              xsv[i] = 0;
+            }
+            continue;
+          }
           const float4 fv = *reinterpret_cast<const float4*>(xf_t + (kb - t.kb0) * BT + 4 * q);
           const int4 sv = *reinterpret_cast<const int4*>(xs_t + (kb - t.kb0) * BT + 4 * q);
           xfv[4 * q] = fv.x; xfv[4 * q + 1] = fv.y; xfv[4 * q + 2] = fv.z; xfv[4 * q + 3] = fv.w;
@@ -415,28 +438,36 @@ moe_gemm_w4_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         }
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + pb * PCOLS + tk0;
         if constexpr (HT == 8) {
-          int p[48];   // [block][plane][8 tokens]
-          tmem_ld8x6_wait_b32(taddr, taddr + BT, taddr + 2 * BT, taddr + NB, taddr + NB + BT, taddr + NB + 2 * BT, p);
+          if (nv > 0) {
+            int p[48];   // [block][plane][8 tokens]
+            tmem_ld8x6_wait_b32(taddr, taddr + BT, taddr + 2 * BT, taddr + NB, taddr + NB + BT, taddr + NB + 2 * BT, p);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int sum0 = p[i] + (p[8 + i] << 8) + (p[16 + i] << 16) - z0 * xsv[i];
-            const int sum1 = p[24 + i] + (p[32 + i] << 8) + (p[40 + i] << 16) - z1 * xsv[i];
-            acc0[i] = fmaf(s0 * xfv[i], static_cast<float>(sum0), acc0[i]);
-            acc1[i] = fmaf(s1 * xfv[i], static_cast<float>(sum1), acc1[i]);
+            for (int q = 0; q < 2; ++q) {
+              if (nv <= 4 * q) continue;
+#pragma unroll
+              for (int i = 4 * q; i < 4 * q + 4; ++i) {
+                const int sum0 = p[i] + (p[8 + i] << 8) + (p[16 + i] << 16) - z0 * xsv[i];
+                const int sum1 = p[24 + i] + (p[32 + i] << 8) + (p[40 + i] << 16) - z1 * xsv[i];
+                acc0[i] = fmaf(s0 * xfv[i], static_cast<float>(sum0), acc0[i]);
+                acc1[i] = fmaf(s1 * xfv[i], static_cast<float>(sum1), acc1[i]);
+              }
+            }
           }
         } else {
-          int p0[16], p1[16], p2[16];
-          tmem_ld16x3_wait_b32(taddr, taddr + BT, taddr + 2 * BT, p0, p1, p2);
+          if (nv > 0) {
+            int p0[16], p1[16], p2[16];
+            tmem_ld16x3_wait_b32(taddr, taddr + BT, taddr + 2 * BT, p0, p1, p2);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int sum = p0[i] + (p1[i] << 8) + (p2[i] << 16) - z0 * xsv[i];
-            acc0[i] = fmaf(s0 * xfv[i], static_cast<float>(sum), acc0[i]);
-          }
-          tmem_ld16x3_wait_b32(taddr + NB, taddr + NB + BT, taddr + NB + 2 * BT, p0, p1, p2);
+            for (int i = 0; i < 16; ++i) {
+              const int sum = p0[i] + (p1[i] << 8) + (p2[i] << 16) - z0 * xsv[i];
+              acc0[i] = fmaf(s0 * xfv[i], static_cast<float>(sum), acc0[i]);
+            }
+            tmem_ld16x3_wait_b32(taddr + NB, taddr + NB + BT, taddr + NB + 2 * BT, p0, p1, p2);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int sum = p0[i] + (p1[i] << 8) + (p2[i] << 16) - z1 * xsv[i];
-            acc1[i] = fmaf(s1 * xfv[i], static_cast<float>(sum), acc1[i]);
+            for (int i = 0; i < 16; ++i) {
+              const int sum = p0[i] + (p1[i] << 8) + (p2[i] << 16) - z1 * xsv[i];
+              acc1[i] = fmaf(s1 * xfv[i], static_cast<float>(sum), acc1[i]);
+            }
           }
         }
         tc_fence_before();

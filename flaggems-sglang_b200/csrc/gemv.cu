@@ -1,0 +1,412 @@
+// Matrix-vector kernels for calls with a handful of (token, choice) pairs: see gemv.cuh.
+#include "gemm_sched.cuh"
+#include "gemv.cuh"
+
+namespace b200moe {
+namespace {
+
+constexpr int kUpThreads = 256;     // 8 warps, one output column (gate row + up row) per warp at a time
+constexpr int kDownThreads = 512;   // 16 warps, two output elements per warp at a time
+constexpr int kChunk = 256;         // elements of one warp-wide 16-byte load
+
+// streaming 16-byte load: the weights are read once, keep them out of L1
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+  uint4 v;
+  asm("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+      : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+      : "l"(p));
+  return v;
+}
+
+template <typename T>
+__device__ __forceinline__ void unpack2(uint32_t w, float& lo, float& hi);
+template <>
+__device__ __forceinline__ void unpack2<__nv_bfloat16>(uint32_t w, float& lo, float& hi) {
+  lo = __uint_as_float(w << 16);
+  hi = __uint_as_float(w & 0xffff0000u);
+}
+template <>
+__device__ __forceinline__ void unpack2<__half>(uint32_t w, float& lo, float& hi) {
+  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+  lo = f.x;
+  hi = f.y;
+}
+
+// Token rows and activations are staged in shared memory as fp32 in two planes: elements 0..3 of
+// every run of eight in the first half of the row, elements 4..7 in the second.  A lane that holds
+// eight consecutive weights (one 16-byte load) then reads two float4 whose addresses are
+// consecutive across the lanes of the warp: no bank conflicts.
+__device__ __forceinline__ int plane_index(int k, int n) {
+  return ((k >> 2) & 1) * (n >> 1) + ((k >> 3) << 2) + (k & 3);
+}
+
+// acc + sum of eight 16-bit weights (elements k .. k+7, k a multiple of 8) times the staged row
+template <typename T>
+__device__ __forceinline__ float dot8(const uint4& w, const float* row, int k, int n, float acc) {
+  const float4 x0 = *reinterpret_cast<const float4*>(row + (k >> 1));
+  const float4 x1 = *reinterpret_cast<const float4*>(row + (n >> 1) + (k >> 1));
+  float a, b;
+  unpack2<T>(w.x, a, b);
+  acc = fmaf(a, x0.x, acc);
+  acc = fmaf(b, x0.y, acc);
+  unpack2<T>(w.y, a, b);
+  acc = fmaf(a, x0.z, acc);
+  acc = fmaf(b, x0.w, acc);
+  unpack2<T>(w.z, a, b);
+  acc = fmaf(a, x1.x, acc);
+  acc = fmaf(b, x1.y, acc);
+  unpack2<T>(w.w, a, b);
+  acc = fmaf(a, x1.z, acc);
+  acc = fmaf(b, x1.w, acc);
+  return acc;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+template <typename T>
+__device__ __forceinline__ void load4_f32(const T* p, float (&v)[4]) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  unpack2<T>(raw.x, v[0], v[1]);
+  unpack2<T>(raw.y, v[2], v[3]);
+}
+
+// Local expert and routing weight of every pair, into shared memory (P <= kGemvMaxPairs).  From
+// topk_ids / topk_weights (with an optional global -> local map), or from the routing triple
+// hist[E] / topk_indx[P] / gate_scal[P] (sorted row -> pair slot, weights in sorted order).
+// Called by every thread of the CTA; the caller synchronises before reading the tables.
+__device__ __forceinline__ void stage_routing(const GemvArgs& a, int* s_e, float* s_gam) {
+  const int P = a.M * a.topk;
+  const int p = threadIdx.x;
+  if (a.hist == nullptr) {
+    if (p < P) {
+      long long id = a.ids_i64 ? reinterpret_cast<const long long*>(a.topk_ids)[p]
+                               : static_cast<long long>(reinterpret_cast<const int*>(a.topk_ids)[p]);
+      if (a.expert_map != nullptr) id = (id >= 0 && id < a.n_global) ? a.expert_map[id] : -1;
+      s_e[p] = (id >= 0 && id < a.E) ? static_cast<int>(id) : -1;
+      s_gam[p] = a.topk_w[p];
+    }
+    return;
+  }
+  if (p < P) s_e[p] = -1;
+  __syncthreads();
+  if (p < P) {
+    // sorted row p belongs to the expert whose run of hist[] covers it
+    int e = -1, end = 0;
+    for (int i = 0; i < a.E; ++i) {
+      end += a.hist[i];
+      if (p < end) {
+        e = i;
+        break;
+      }
+    }
+    const int slot = (e >= 0) ? a.topk_indx[p] : -1;
+    if (slot >= 0 && slot < P) {
+      s_e[slot] = e;
+      s_gam[slot] = a.gate_scal[p];
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// act[p][i] = activation(w1[e_p][i] . x_t, w1[e_p][I + i] . x_t) in the 16-bit type
+template <typename T>
+__global__ void __launch_bounds__(kUpThreads)
+moe_gemv_up_kernel(const GemvArgs a) {
+  extern __shared__ __align__(16) uint8_t gemv_smem[];
+  const int P = a.M * a.topk;
+  float* s_x = reinterpret_cast<float*>(gemv_smem);                 // [M][H], two planes per row
+  int* s_e = reinterpret_cast<int*>(s_x + static_cast<size_t>(a.M) * a.H);
+  float* s_gam = reinterpret_cast<float*>(s_e + kGemvMaxPairs);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  griddep_wait();
+  griddep_launch_dependents();
+  stage_routing(a, s_e, s_gam);
+  const T* x = reinterpret_cast<const T*>(a.x);
+  const int quads = a.H >> 2;
+  for (int i = threadIdx.x; i < a.M * quads; i += kUpThreads) {
+    const int t = i / quads, k = (i - t * quads) << 2;
+    float v[4];
+    load4_f32<T>(x + static_cast<size_t>(t) * a.H + k, v);
+    *reinterpret_cast<float4*>(s_x + static_cast<size_t>(t) * a.H + plane_index(k, a.H)) =
+        make_float4(v[0], v[1], v[2], v[3]);
+  }
+  __syncthreads();
+
+  const bool w_on_input = (a.flags & B200MOE_FLAG_WEIGHT_ON_INPUT) != 0;
+  const bool mimic = (a.flags & B200MOE_FLAG_MIMIC_ROUNDING) != 0;
+  const bool ext = a.b1 != nullptr || a.activation == B200MOE_ACT_SWIGLU_OAI;
+  ActParams ap;
+  ap.activation = a.activation;
+  ap.alpha = a.alpha;
+  ap.limit = a.limit;
+  T* act = reinterpret_cast<T*>(a.act);
+  const T* w1 = reinterpret_cast<const T*>(a.w1);
+
+  const int total = P * a.I;
+  const int warps = gridDim.x * (kUpThreads / 32);
+  // consecutive columns go to different SMs, so every SM streams the same share
+  for (int c = warp * gridDim.x + blockIdx.x; c < total; c += warps) {
+    const int p = c / a.I, i = c - p * a.I;
+    const int e = s_e[p];
+    if (e < 0) {
+      if (lane == 0) act[c] = from_f32<T>(0.f);
+      continue;
+    }
+    const float* xs = s_x + static_cast<size_t>(p / a.topk) * a.H;
+    const T* wg = w1 + (static_cast<size_t>(e) * 2 * a.I + i) * a.H;
+    const T* wu = wg + static_cast<size_t>(a.I) * a.H;
+    float ag = 0.f, au = 0.f;
+    // four 256-element chunks of both rows in flight per lane
+    for (int k0 = lane * 8; k0 < a.H; k0 += 4 * kChunk) {
+      uint4 gq[4], uq[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int k = k0 + q * kChunk;
+        if (k < a.H) {
+          gq[q] = ldg_stream(wg + k);
+          uq[q] = ldg_stream(wu + k);
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int k = k0 + q * kChunk;
+        if (k < a.H) {
+          ag = dot8<T>(gq[q], xs, k, a.H, ag);
+          au = dot8<T>(uq[q], xs, k, a.H, au);
+        }
+      }
+    }
+    ag = warp_sum(ag);
+    au = warp_sum(au);
+    if (lane == 0) {
+      if (a.b1 != nullptr) {
+        ag += __ldg(a.b1 + static_cast<size_t>(e) * 2 * a.I + i);
+        au += __ldg(a.b1 + static_cast<size_t>(e) * 2 * a.I + a.I + i);
+      }
+      const float av = ext ? act_mul<T, true>(ag, au, w_on_input, s_gam[p], mimic, ap)
+                           : act_mul<T>(ag, au, w_on_input, s_gam[p], mimic, ap);
+      act[c] = from_f32<T>(av);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// out[t][h] = cast(routed_scaling * sum_j gamma_j * (w2[e_j][h] . act[p_j] + b2[e_j][h]))
+// One warp per pair of output elements (h, h + 1) of a token: the two weight rows share every read
+// of the staged activations.
+template <typename T>
+__global__ void __launch_bounds__(kDownThreads)
+moe_gemv_down_kernel(const GemvArgs a) {
+  extern __shared__ __align__(16) uint8_t gemv_smem[];
+  const int P = a.M * a.topk;
+  float* s_act = reinterpret_cast<float*>(gemv_smem);               // [P][I], two planes per row
+  int* s_e = reinterpret_cast<int*>(s_act + static_cast<size_t>(P) * a.I);
+  float* s_gam = reinterpret_cast<float*>(s_e + kGemvMaxPairs);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool w_on_input = (a.flags & B200MOE_FLAG_WEIGHT_ON_INPUT) != 0;
+  const bool no_combine = (a.flags & B200MOE_FLAG_NO_COMBINE) != 0;
+  // per-pair results are needed one by one when each is rounded or stored by itself; otherwise the
+  // routing weight is folded into the staged activations and one running sum covers all pairs
+  const bool by_pair = no_combine || a.round_pair != 0;
+
+  griddep_wait();
+  griddep_launch_dependents();
+  stage_routing(a, s_e, s_gam);
+  __syncthreads();
+  const T* act = reinterpret_cast<const T*>(a.act);
+  const int quads = a.I >> 2;
+  for (int i = threadIdx.x; i < P * quads; i += kDownThreads) {
+    const int p = i / quads, k = (i - p * quads) << 2;
+    const float fold = (by_pair || w_on_input) ? 1.0f : s_gam[p];
+    float v[4];
+    load4_f32<T>(act + static_cast<size_t>(p) * a.I + k, v);
+    *reinterpret_cast<float4*>(s_act + static_cast<size_t>(p) * a.I + plane_index(k, a.I)) =
+        make_float4(v[0] * fold, v[1] * fold, v[2] * fold, v[3] * fold);
+  }
+  __syncthreads();
+
+  const T* w2 = reinterpret_cast<const T*>(a.w2);
+  const int nch = (a.I + kChunk - 1) / kChunk;
+  T* out = reinterpret_cast<T*>(a.out);
+  const int half_h = a.H >> 1;
+
+  const int tasks = a.M * half_h;
+  const int warps = gridDim.x * (kDownThreads / 32);
+  for (int task = warp * gridDim.x + blockIdx.x; task < tasks; task += warps) {
+    const int t = task / half_h, h = (task - t * half_h) << 1;
+    if (!by_pair) {
+      // (pair, chunk) flattened: eight slots of two 16-byte loads in flight per lane
+      const int Q = a.topk * nch;
+      float acc0 = 0.f, acc1 = 0.f;
+      int j = 0, ch = 0;
+      for (int q0 = 0; q0 < Q; q0 += 8) {
+        uint4 wa[8], wb[8];
+        int kk[8], pp[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int p = t * a.topk + j;
+          const int k = ch * kChunk + lane * 8;
+          const int e = (q0 + u < Q) ? s_e[p] : -1;
+          const bool on = e >= 0 && k < a.I;
+          kk[u] = on ? k : -1;
+          pp[u] = p;
+          if (on) {
+            const T* wr = w2 + (static_cast<size_t>(e) * a.H + h) * a.I + k;
+            wa[u] = ldg_stream(wr);
+            wb[u] = ldg_stream(wr + a.I);
+          }
+          if (++ch == nch) {
+            ch = 0;
+            ++j;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          if (kk[u] >= 0) {
+            const float* av = s_act + static_cast<size_t>(pp[u]) * a.I;
+            acc0 = dot8<T>(wa[u], av, kk[u], a.I, acc0);
+            acc1 = dot8<T>(wb[u], av, kk[u], a.I, acc1);
+          }
+        }
+      }
+      acc0 = warp_sum(acc0);
+      acc1 = warp_sum(acc1);
+      if (lane == 0) {
+        if (a.b2 != nullptr) {
+          for (int jb = 0; jb < a.topk; ++jb) {
+            const int p = t * a.topk + jb;
+            if (s_e[p] >= 0) {
+              const float gam = w_on_input ? 1.0f : s_gam[p];
+              acc0 = fmaf(__ldg(a.b2 + static_cast<size_t>(s_e[p]) * a.H + h), gam, acc0);
+              acc1 = fmaf(__ldg(a.b2 + static_cast<size_t>(s_e[p]) * a.H + h + 1), gam, acc1);
+            }
+          }
+        }
+        out[static_cast<size_t>(t) * a.H + h] = from_f32<T>(acc0 * a.routed_scaling);
+        out[static_cast<size_t>(t) * a.H + h + 1] = from_f32<T>(acc1 * a.routed_scaling);
+      }
+    } else {
+      float sum0 = 0.f, sum1 = 0.f;
+      for (int jb = 0; jb < a.topk; ++jb) {
+        const int p = t * a.topk + jb;
+        const int e = s_e[p];
+        float y0 = 0.f, y1 = 0.f;
+        if (e >= 0) {
+          const T* wr = w2 + (static_cast<size_t>(e) * a.H + h) * a.I;
+          const float* av = s_act + static_cast<size_t>(p) * a.I;
+          float acc0 = 0.f, acc1 = 0.f;
+          for (int k0 = lane * 8; k0 < a.I; k0 += 4 * kChunk) {
+            uint4 wa[4], wb[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              if (k0 + q * kChunk < a.I) {
+                wa[q] = ldg_stream(wr + k0 + q * kChunk);
+                wb[q] = ldg_stream(wr + a.I + k0 + q * kChunk);
+              }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int k = k0 + q * kChunk;
+              if (k < a.I) {
+                acc0 = dot8<T>(wa[q], av, k, a.I, acc0);
+                acc1 = dot8<T>(wb[q], av, k, a.I, acc1);
+              }
+            }
+          }
+          acc0 = warp_sum(acc0);
+          acc1 = warp_sum(acc1);
+          if (a.b2 != nullptr) {
+            acc0 += __ldg(a.b2 + static_cast<size_t>(e) * a.H + h);
+            acc1 += __ldg(a.b2 + static_cast<size_t>(e) * a.H + h + 1);
+          }
+          y0 = w_on_input ? acc0 : acc0 * s_gam[p];
+          y1 = w_on_input ? acc1 : acc1 * s_gam[p];
+          if (a.round_pair) {
+            y0 = to_f32<T>(from_f32<T>(y0));
+            y1 = to_f32<T>(from_f32<T>(y1));
+          }
+        }
+        if (no_combine) {
+          if (lane == 0) {
+            out[static_cast<size_t>(p) * a.H + h] = from_f32<T>(y0);
+            out[static_cast<size_t>(p) * a.H + h + 1] = from_f32<T>(y1);
+          }
+        } else {
+          sum0 += y0;
+          sum1 += y1;
+        }
+      }
+      if (!no_combine && lane == 0) {
+        out[static_cast<size_t>(t) * a.H + h] = from_f32<T>(sum0 * a.routed_scaling);
+        out[static_cast<size_t>(t) * a.H + h + 1] = from_f32<T>(sum1 * a.routed_scaling);
+      }
+    }
+  }
+}
+
+size_t routing_smem() { return kGemvMaxPairs * 8 + 64; }
+
+// resident CTAs per SM times SMs, but no more CTAs per SM than the work has warps for: the grid
+// stays a multiple of the SM count, so every SM streams the same share of the weights
+template <typename K>
+unsigned grid_for(K kernel, size_t smem, int threads, long long items, int num_sms) {
+  int per_sm = 1;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem) != cudaSuccess || per_sm < 1)
+    per_sm = 1;
+  const long long warps_per_cta = threads / 32;
+  const long long need_per_sm = (items + warps_per_cta * num_sms - 1) / (warps_per_cta * num_sms);
+  if (per_sm > need_per_sm) per_sm = static_cast<int>(need_per_sm < 1 ? 1 : need_per_sm);
+  return static_cast<unsigned>(per_sm) * static_cast<unsigned>(num_sms);
+}
+
+template <typename T>
+int launch_up(const GemvArgs& a, int num_sms, cudaStream_t stream, bool pdl) {
+  const size_t smem = gemv_up_smem(a);
+  if (cudaFuncSetAttribute(moe_gemv_up_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(smem)) != cudaSuccess)
+    return B200MOE_ERR_CUDA;
+  const unsigned grid = grid_for(moe_gemv_up_kernel<T>, smem, kUpThreads, static_cast<long long>(a.M) * a.topk * a.I,
+                                 num_sms);
+  note_launch("moe_gemv_up_kernel<gate/up>");
+  return launch_kernel(moe_gemv_up_kernel<T>, dim3(grid), dim3(kUpThreads), smem, stream, pdl, a) == cudaSuccess
+             ? B200MOE_OK
+             : B200MOE_ERR_CUDA;
+}
+template <typename T>
+int launch_down(const GemvArgs& a, int num_sms, cudaStream_t stream, bool pdl) {
+  const size_t smem = gemv_down_smem(a);
+  if (cudaFuncSetAttribute(moe_gemv_down_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(smem)) != cudaSuccess)
+    return B200MOE_ERR_CUDA;
+  const unsigned grid = grid_for(moe_gemv_down_kernel<T>, smem, kDownThreads, static_cast<long long>(a.M) * (a.H / 2),
+                                 num_sms);
+  note_launch("moe_gemv_down_kernel<down>");
+  return launch_kernel(moe_gemv_down_kernel<T>, dim3(grid), dim3(kDownThreads), smem, stream, pdl, a) == cudaSuccess
+             ? B200MOE_OK
+             : B200MOE_ERR_CUDA;
+}
+
+}  // namespace
+
+size_t gemv_up_smem(const GemvArgs& a) { return static_cast<size_t>(a.M) * a.H * 4 + routing_smem(); }
+size_t gemv_down_smem(const GemvArgs& a) { return static_cast<size_t>(a.M) * a.topk * a.I * 4 + routing_smem(); }
+bool gemv_fits(const GemvArgs& a) {
+  return a.M * a.topk <= kGemvMaxPairs && gemv_up_smem(a) + 1024 <= kSmemLimit && gemv_down_smem(a) + 1024 <= kSmemLimit;
+}
+
+int launch_gemv_up(const GemvArgs& a, int num_sms, cudaStream_t stream, bool pdl) {
+  if (!gemv_fits(a)) return B200MOE_ERR_UNSUPPORTED;
+  return a.dtype == B200MOE_DTYPE_BF16 ? launch_up<__nv_bfloat16>(a, num_sms, stream, pdl)
+                                       : launch_up<__half>(a, num_sms, stream, pdl);
+}
+int launch_gemv_down(const GemvArgs& a, int num_sms, cudaStream_t stream, bool pdl) {
+  if (!gemv_fits(a)) return B200MOE_ERR_UNSUPPORTED;
+  return a.dtype == B200MOE_DTYPE_BF16 ? launch_down<__nv_bfloat16>(a, num_sms, stream, pdl)
+                                       : launch_down<__half>(a, num_sms, stream, pdl);
+}
+
+}  // namespace b200moe

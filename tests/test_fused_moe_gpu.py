@@ -63,7 +63,7 @@ GOLD = np.load(GOLDEN / "fused_moe_ref_golden.npz")
 # of a large tensor shows up here long before it moves the tolerance check).
 BIT_EQUAL_FLOOR = {
     "M1_K1280_N3072_E64_topk8/gate_in": 0.93,      # measured 0.953
-    "M1_K1280_N3072_E64_topk8/out": 0.995,         # measured 0.9992
+    "M1_K1280_N3072_E64_topk8/out": 0.97,          # measured 0.981 (matrix-vector path: another summation order)
     "M4_K1280_N3072_E64_topk8/out": 0.99,          # measured 0.9986
     "M33_K256_N512_E16_topk4/gate_in": 0.995,      # measured 0.9998
     "M33_K256_N512_E16_topk4/out": 0.995,          # measured 0.9999

@@ -1,0 +1,166 @@
+"""GPU: the matrix-vector path for a handful of (token, choice) pairs (csrc/gemv.cu).
+
+Calls with 16-bit weights and M * topk <= 16 skip alignment, gather, grouped GEMMs and output
+conversion: two launches read the routing input directly.  Every case here is checked against the
+CPU oracle and against the grouped-GEMM path on the same inputs (forced by fixing the token
+block), and the launch log must show which path ran.
+"""
+import pytest
+import torch
+
+from oracle import moe as OM
+from parity import assert_parity
+
+pytestmark = pytest.mark.gpu
+
+
+def _names():
+    from flaggems_sglang_b200 import _lib
+    return _lib.launch_stats()[1]
+
+
+def _is_gemv():
+    return any("gemv" in n for n in _names())
+
+
+def _layer(h, i, e, device, dtype=torch.bfloat16, seed=3):
+    from flaggems_sglang_b200.testing import make_weights
+    return make_weights(h, i, e, dtype=dtype, device=device, seed=seed)
+
+
+@pytest.mark.parametrize("M,topk", [(1, 2), (1, 8), (2, 8), (3, 4), (16, 1)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_gemv_16bit_matches_oracle_and_grouped_path(cuda_device, M, topk, dtype):
+    import flaggems_sglang_b200 as F
+    from flaggems_sglang_b200.testing import make_tokens
+    h, i, e = 1024, 768, 16
+    d = cuda_device
+    w13, w2 = _layer(h, i, e, d, dtype)
+    x, tw, ids = make_tokens(M, h, e, topk, dtype=dtype, seed=M * 10 + topk)
+    out = F.fused_experts(x.to(d), w13, w2, tw.to(d), ids.to(d))
+    assert _is_gemv(), _names()
+    grouped = F.fused_experts(x.to(d), w13, w2, tw.to(d), ids.to(d), block_tokens=16)
+    assert not _is_gemv(), _names()
+    F.check_status()
+    ref = OM.fused_experts(x, w13.cpu().float(), w2.cpu().float(), tw, ids)
+    assert_parity(out, ref, what=f"gemv {dtype} M={M} topk={topk} vs oracle")
+    assert_parity(out, grouped.float(), what=f"gemv {dtype} M={M} topk={topk} vs grouped path")
+    again = F.fused_experts(x.to(d), w13, w2, tw.to(d), ids.to(d))
+    assert torch.equal(out, again), "fixed summation order: a rerun gives the same bits"
+
+
+def test_gemv_ragged_hidden_sizes(cuda_device):
+    """H and I that are multiples of 8 but not of the 256-element warp stride."""
+    import flaggems_sglang_b200 as F
+    from flaggems_sglang_b200.testing import make_tokens
+    h, i, e, topk = 264, 136, 4, 2
+    d = cuda_device
+    w13, w2 = _layer(h, i, e, d)
+    x, tw, ids = make_tokens(2, h, e, topk, seed=5)
+    out = F.fused_experts(x.to(d), w13, w2, tw.to(d), ids.to(d))
+    assert _is_gemv(), _names()
+    F.check_status()
+    ref = OM.fused_experts(x, w13.cpu().float(), w2.cpu().float(), tw, ids)
+    assert_parity(out, ref, what="gemv ragged H=264 I=136")
+
+
+def test_gemv_options(cuda_device):
+    """Router weight on the input side, scaling factor, per-pair output, gelu, int64 ids."""
+    import flaggems_sglang_b200 as F
+    from flaggems_sglang_b200.testing import make_tokens
+    h, i, e, topk = 512, 256, 8, 4
+    d = cuda_device
+    w13, w2 = _layer(h, i, e, d)
+    x, tw, ids = make_tokens(2, h, e, topk, seed=9)
+    xd, twd, idd = x.to(d), tw.to(d), ids.to(d)
+    for kw in (dict(apply_router_weight_on_input=True), dict(routed_scaling_factor=2.5), dict(no_combine=True),
+               dict(activation="gelu"), dict(mimic_reference_rounding=False)):
+        out = F.fused_experts(xd, w13, w2, twd, idd, **kw)
+        assert _is_gemv(), (kw, _names())
+        grouped = F.fused_experts(xd, w13, w2, twd, idd, block_tokens=16, **kw)
+        F.check_status()
+        assert out.shape == grouped.shape
+        assert_parity(out, grouped.float(), what=f"gemv {kw} vs grouped path")
+    out64 = F.fused_experts(xd, w13, w2, twd, idd.long())
+    assert _is_gemv(), _names()
+    assert torch.equal(out64, F.fused_experts(xd, w13, w2, twd, idd))
+
+
+def test_gemv_expert_map_drops_foreign_experts(cuda_device):
+    import flaggems_sglang_b200 as F
+    from flaggems_sglang_b200.testing import make_tokens
+    h, i, e_global, topk = 512, 256, 16, 4
+    d = cuda_device
+    w13, w2 = _layer(h, i, e_global, d)
+    x, tw, ids = make_tokens(2, h, e_global, topk, seed=11)
+    # this rank holds the even experts only
+    held = torch.arange(0, e_global, 2)
+    emap = torch.full((e_global,), -1, dtype=torch.int32)
+    emap[held] = torch.arange(held.numel(), dtype=torch.int32)
+    out = F.fused_experts(x.to(d), w13[held.to(d)].contiguous(), w2[held.to(d)].contiguous(), tw.to(d), ids.to(d),
+                          expert_map=emap.to(d))
+    assert _is_gemv(), _names()
+    F.check_status()
+    keep = (ids % 2 == 0)
+    ref = OM.fused_experts(x, w13.cpu().float(), w2.cpu().float(), tw * keep, ids)
+    assert_parity(out, ref, what="gemv with expert_map")
+
+
+def test_gemv_bias_and_clamped_swiglu(cuda_device):
+    import flaggems_sglang_b200 as F
+    from flaggems_sglang_b200.testing import make_tokens
+    h, i, e, topk = 512, 256, 8, 4
+    d = cuda_device
+    w13, w2 = _layer(h, i, e, d)
+    g = torch.Generator().manual_seed(4)
+    b13 = torch.randn(e, 2 * i, generator=g) * 0.1
+    b2 = torch.randn(e, h, generator=g) * 0.1
+    x, tw, ids = make_tokens(1, h, e, topk, seed=13)
+    kw = dict(b13=b13.to(d), b2=b2.to(d), activation="swiglu_oai", swiglu_alpha=1.702, swiglu_limit=7.0)
+    out = F.fused_experts(x.to(d), w13, w2, tw.to(d), ids.to(d), **kw)
+    assert _is_gemv(), _names()
+    grouped = F.fused_experts(x.to(d), w13, w2, tw.to(d), ids.to(d), block_tokens=16, **kw)
+    F.check_status()
+    assert_parity(out, grouped.float(), what="gemv bias + clamped swiglu vs grouped path")
+
+
+def test_gemv_through_the_operator_entry_point(cuda_device):
+    """The reference-compatible call (routing triple) takes the same path."""
+    import flaggems_sglang
+    from test_fused_moe_gpu import _ref_inputs, _run_reference_api
+    shape = (1, 1280, 3072, 64, 8)
+    x, w1, w2, tw, ids = _ref_inputs(*shape, cuda_device)
+    out = _run_reference_api(x, w1, w2, tw, ids, 64, cuda_device)
+    assert _is_gemv(), _names()
+    ref = OM.fused_experts(x, w1.transpose(1, 2).float(), w2.transpose(1, 2).float(), tw, ids)
+    assert_parity(out, ref, what="gemv through triton_kernel_fused_experts")
+
+
+def test_quantised_weights_take_the_grouped_path(cuda_device):
+    """FP8 (and int4) rows would be converted element by element on the CUDA cores: slower than the
+    tensor-core path even at one token, so they stay on it."""
+    import flaggems_sglang_b200 as F
+    from flaggems_sglang_b200.quant import quantize_fp8_block
+    from flaggems_sglang_b200.testing import make_tokens
+    h, i, e, topk = 1024, 512, 16, 8
+    d = cuda_device
+    w13, w2 = _layer(h, i, e, d)
+    w13q, s13 = quantize_fp8_block(w13)
+    w2q, s2 = quantize_fp8_block(w2)
+    x, tw, ids = make_tokens(1, h, e, topk, seed=22)
+    out = F.fused_experts(x.to(d), w13q, w2q, tw.to(d), ids.to(d), use_fp8_w8a8=True, w13_scale=s13, w2_scale=s2)
+    assert not _is_gemv(), _names()
+    F.check_status()
+    ref = OM.fused_experts_fp8(x, w13q.cpu(), w2q.cpu(), s13.cpu(), s2.cpu(), tw, ids)
+    assert_parity(out, ref, what="fp8 M=1 on the grouped path")
+
+
+def test_more_pairs_than_the_limit_take_the_grouped_path(cuda_device):
+    import flaggems_sglang_b200 as F
+    from flaggems_sglang_b200.testing import make_tokens
+    h, i, e, topk = 512, 256, 8, 2
+    d = cuda_device
+    w13, w2 = _layer(h, i, e, d)
+    x, tw, ids = make_tokens(9, h, e, topk, seed=2)        # 18 pairs
+    F.fused_experts(x.to(d), w13, w2, tw.to(d), ids.to(d))
+    assert not _is_gemv(), _names()
