@@ -574,6 +574,10 @@ int run_gemv(const b200moe_cfg* c, const Layout& L, const void* x, const void* w
   // on the grouped tensor-core path)
   if (L.P <= 0 || L.P > kGemvMaxPairs || c->block_tokens != 0) return B200MOE_ERR_UNSUPPORTED;
   if (c->wmode != B200MOE_W_16BIT || (c->flags & B200MOE_FLAG_SIMT)) return B200MOE_ERR_UNSUPPORTED;
+  // every pair streams its expert's weights by itself: two pairs of different tokens that meet in one
+  // expert read it twice, which the grouped path does not.  One token's experts are distinct; with more
+  // tokens the path is taken only while such meetings are rare (pairs <= experts / 4)
+  if (c->M > 1 && L.P * 4 > c->E) return B200MOE_ERR_UNSUPPORTED;
   const int sms = query_sms(c);
   GemvArgs g = {};
   g.x = x;

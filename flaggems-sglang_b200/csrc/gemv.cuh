@@ -32,6 +32,7 @@ struct GemvArgs {
   int M, H, I, E, topk;
   int dtype, activation, flags;
   int round_pair;           // round each pair's weighted row to the 16-bit type before the sum
+  int down_split;           // set by the launcher: warps that share one output task of the down kernel (1, 2, 4, 8)
   float alpha, limit, routed_scaling;
   const float* b1;          // [E, 2I] or nullptr
   const float* b2;          // [E, H] or nullptr

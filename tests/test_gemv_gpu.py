@@ -33,7 +33,7 @@ def _layer(h, i, e, device, dtype=torch.bfloat16, seed=3):
 def test_gemv_16bit_matches_oracle_and_grouped_path(cuda_device, M, topk, dtype):
     import flaggems_sglang_b200 as F
     from flaggems_sglang_b200.testing import make_tokens
-    h, i, e = 1024, 768, 16
+    h, i, e = 1024, 768, 64
     d = cuda_device
     w13, w2 = _layer(h, i, e, d, dtype)
     x, tw, ids = make_tokens(M, h, e, topk, dtype=dtype, seed=M * 10 + topk)
@@ -53,7 +53,7 @@ def test_gemv_ragged_hidden_sizes(cuda_device):
     """H and I that are multiples of 8 but not of the 256-element warp stride."""
     import flaggems_sglang_b200 as F
     from flaggems_sglang_b200.testing import make_tokens
-    h, i, e, topk = 264, 136, 4, 2
+    h, i, e, topk = 264, 136, 16, 2
     d = cuda_device
     w13, w2 = _layer(h, i, e, d)
     x, tw, ids = make_tokens(2, h, e, topk, seed=5)
@@ -68,7 +68,7 @@ def test_gemv_options(cuda_device):
     """Router weight on the input side, scaling factor, per-pair output, gelu, int64 ids."""
     import flaggems_sglang_b200 as F
     from flaggems_sglang_b200.testing import make_tokens
-    h, i, e, topk = 512, 256, 8, 4
+    h, i, e, topk = 512, 256, 32, 4
     d = cuda_device
     w13, w2 = _layer(h, i, e, d)
     x, tw, ids = make_tokens(2, h, e, topk, seed=9)
@@ -89,7 +89,7 @@ def test_gemv_options(cuda_device):
 def test_gemv_expert_map_drops_foreign_experts(cuda_device):
     import flaggems_sglang_b200 as F
     from flaggems_sglang_b200.testing import make_tokens
-    h, i, e_global, topk = 512, 256, 16, 4
+    h, i, e_global, topk = 512, 256, 64, 4
     d = cuda_device
     w13, w2 = _layer(h, i, e_global, d)
     x, tw, ids = make_tokens(2, h, e_global, topk, seed=11)
@@ -156,11 +156,18 @@ def test_quantised_weights_take_the_grouped_path(cuda_device):
 
 
 def test_more_pairs_than_the_limit_take_the_grouped_path(cuda_device):
+    """More than 16 pairs, or several tokens whose pairs would often meet in one expert (pairs >
+    experts / 4: each pair streams its expert's weights by itself)."""
     import flaggems_sglang_b200 as F
     from flaggems_sglang_b200.testing import make_tokens
-    h, i, e, topk = 512, 256, 8, 2
+    h, i, topk = 512, 256, 2
     d = cuda_device
-    w13, w2 = _layer(h, i, e, d)
-    x, tw, ids = make_tokens(9, h, e, topk, seed=2)        # 18 pairs
+    for m, e in ((9, 128), (4, 8)):                        # 18 pairs; 8 pairs over 8 experts
+        w13, w2 = _layer(h, i, e, d)
+        x, tw, ids = make_tokens(m, h, e, topk, seed=2)
+        F.fused_experts(x.to(d), w13, w2, tw.to(d), ids.to(d))
+        assert not _is_gemv(), (m, e, _names())
+    w13, w2 = _layer(h, i, 8, d)
+    x, tw, ids = make_tokens(1, h, 8, topk, seed=2)        # one token: its experts are distinct
     F.fused_experts(x.to(d), w13, w2, tw.to(d), ids.to(d))
-    assert not _is_gemv(), _names()
+    assert _is_gemv(), _names()
