@@ -569,11 +569,16 @@ int run_gemv(const b200moe_cfg* c, const Layout& L, const void* x, const void* w
              const b200moe_quant* quant, const float* topk_weights, const void* topk_ids,
              const int32_t* expert_map, const int32_t* hist, const int32_t* topk_indx, const float* gate_scal,
              uint8_t* ws, void* out, cudaStream_t st, int slot) {
-  // 16-bit weights only: FP8 and int4 rows need their conversions on the CUDA cores, which costs
-  // more than the launches saved (measured: a 32-expert FP8 layer at M = 1 took 152 us this way, 97 us
-  // on the grouped tensor-core path)
+  // 16-bit weights, and int4 weights on integer dot products; FP8 rows would be converted element by
+  // element on the CUDA cores, which costs more than the launches saved (measured: a 32-expert FP8
+  // layer at M = 1 took 152 us this way, 97 us on the grouped tensor-core path)
+  const bool w4 = c->wmode == B200MOE_W_INT4_AWQ;
   if (L.P <= 0 || L.P > kGemvMaxPairs || c->block_tokens != 0) return B200MOE_ERR_UNSUPPORTED;
-  if (c->wmode != B200MOE_W_16BIT || (c->flags & B200MOE_FLAG_SIMT)) return B200MOE_ERR_UNSUPPORTED;
+  if ((c->wmode != B200MOE_W_16BIT && !w4) || (c->flags & (B200MOE_FLAG_SIMT | B200MOE_FLAG_W4_SMEM_OPERANDS)))
+    return B200MOE_ERR_UNSUPPORTED;
+  if (w4 && (quant == nullptr || quant->w1_sz == nullptr || quant->w2_sz == nullptr)) return B200MOE_ERR_BAD_ARG;
+  // the pairs' 16-bit activations go where the grouped path keeps GEMM-1's output
+  if (static_cast<size_t>(L.cap) * c->I * L.act_bytes < static_cast<size_t>(L.P) * c->I * 2) return B200MOE_ERR_UNSUPPORTED;
   // every pair streams its expert's weights by itself: two pairs of different tokens that meet in one
   // expert read it twice, which the grouped path does not.  One token's experts are distinct; with more
   // tokens the path is taken only while such meetings are rare (pairs <= experts / 4)
@@ -597,6 +602,7 @@ int run_gemv(const b200moe_cfg* c, const Layout& L, const void* x, const void* w
   g.E = c->E;
   g.topk = c->topk;
   g.dtype = c->dtype;
+  g.w4 = w4 ? 1 : 0;
   g.activation = c->activation;
   g.flags = c->flags;
   g.round_pair =
@@ -608,6 +614,8 @@ int run_gemv(const b200moe_cfg* c, const Layout& L, const void* x, const void* w
     g.limit = quant->swiglu_limit;
     g.b1 = quant->b1;
     g.b2 = quant->b2;
+    g.w1_sz = quant->w1_sz;
+    g.w2_sz = quant->w2_sz;
   }
   g.act = ws + L.a2;   // the pairs' activations go where the grouped path keeps GEMM-1's output (cap >= P rows)
   g.out = out;

@@ -381,7 +381,395 @@ moe_gemv_down_kernel(const GemvArgs a) {
   }
 }
 
-size_t routing_smem() { return kGemvMaxPairs * 8 + 2 * 2 * (kDownThreads / 32) * 4 + 64; }   // tables + partial sums
+// ==========================================================================================
+// int4 (AWQ) weights: the same two launches on integer dot products.
+//
+// The activations take the form the integer tensor-core kernels use (gemm_w4.cu): per 128-k group
+// a power-of-two scale f = 2^(e-18) for a group maximum in [2^e, 2^(e+1)) and the exact integers
+// v = rint(x / f), |v| < 2^19, as three signed byte planes v = p0 + 256 p1 + 65536 p2.  A packed
+// word holds eight weights; `w & 0x0F0F0F0F` and `(w >> 4) & 0x0F0F0F0F` are their raw nibbles as
+// unsigned bytes in the order (0, 4, 1, 5) and (2, 6, 3, 7), the planes are staged in that order,
+// and one dp4a per plane and half word gives exact sums S = S0 + 256 S1 + 65536 S2.  Per 32-k
+// segment (one 16-byte load of a lane, inside one quantisation group):
+// acc += (s f) * float(S - z * sum(v)), s and z the group's scale and zero point of the row.
+// One instruction per weight instead of a conversion and a multiply-add for each.
+
+__device__ __forceinline__ int dp4a_u8_s8(uint32_t a, uint32_t b, int c) {
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
+// A row of K staged bytes per plane is kept in two halves: bytes 0..15 of every run of 32 in the
+// first, bytes 16..31 in the second, so that the two 16-byte reads of a lane (its 32 k) are
+// contiguous across the warp.
+__device__ __forceinline__ int half_index(int o, int K) { return ((o >> 4) & 1) * (K >> 1) + ((o >> 5) << 4) + (o & 15); }
+
+struct StagedW4 {
+  uint8_t* planes;   // [rows][3][K]
+  float* f;          // [rows][K / 128] group scale (routing weight folded in where asked)
+  int* vsum;         // [rows][K / 32] sum of the integers of every 32-k segment
+};
+
+// fp16 rows -> planes, scales and segment sums; one warp per (row, group), the arithmetic of
+// group_split_i8_kernel (prep.cu).  fold[row] multiplies the stored scale (nullptr: 1).
+__device__ __forceinline__ void stage_w4(const __half* src, int rows, int K, const StagedW4& st, const float* fold,
+                                         int nthreads) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int groups = K >> 7;
+  for (int w = warp; w < rows * groups; w += nthreads >> 5) {
+    const int r = w / groups, g = w - r * groups;
+    float v[4];
+    load4_f32<__half>(src + static_cast<size_t>(r) * K + g * 128 + lane * 4, v);
+    const float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    const unsigned int mb = __reduce_max_sync(0xffffffffu, __float_as_uint(amax));
+    const int ex = static_cast<int>(mb >> 23) - 127;
+    const float mult = (mb == 0u) ? 0.f : __uint_as_float(static_cast<unsigned int>(127 + 18 - ex) << 23);
+    const float f = (mb == 0u) ? 1.0f : __uint_as_float(static_cast<unsigned int>(127 + ex - 18) << 23);
+    uint32_t pk[3] = {0u, 0u, 0u};
+    int part = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int q = __float2int_rn(v[i] * mult);
+      const int b0 = (q << 24) >> 24;
+      const int q1 = (q - b0) >> 8;
+      const int b1 = (q1 << 24) >> 24;
+      const int b2 = (q1 - b1) >> 8;
+      pk[0] |= static_cast<uint32_t>(b0 & 0xFF) << (8 * i);
+      pk[1] |= static_cast<uint32_t>(b1 & 0xFF) << (8 * i);
+      pk[2] |= static_cast<uint32_t>(b2 & 0xFF) << (8 * i);
+      part += q;
+    }
+    // an even lane holds elements 0..3 of its run of eight, the odd neighbour 4..7; stored order
+    // is (0, 4, 1, 5 | 2, 6, 3, 7)
+    uint8_t* dst = st.planes + static_cast<size_t>(r) * 3 * K + half_index(g * 128 + lane * 4, K);
+#pragma unroll
+    for (int p = 0; p < 3; ++p) {
+      const uint32_t other = __shfl_xor_sync(0xffffffffu, pk[p], 1);
+      const uint32_t word = (lane & 1) ? __byte_perm(pk[p], other, 0x3726) : __byte_perm(pk[p], other, 0x5140);
+      *reinterpret_cast<uint32_t*>(dst + p * K) = word;
+    }
+    part += __shfl_xor_sync(0xffffffffu, part, 1);
+    part += __shfl_xor_sync(0xffffffffu, part, 2);
+    part += __shfl_xor_sync(0xffffffffu, part, 4);
+    if ((lane & 7) == 0) st.vsum[r * (K >> 5) + g * 4 + (lane >> 3)] = part;
+    if (lane == 0) st.f[r * groups + g] = f * (fold != nullptr ? fold[r] : 1.0f);
+  }
+}
+
+// exact integer dot of the 32 nibbles of one 16-byte load with the staged integers of its 32 k
+__device__ __forceinline__ int dot32_w4(const uint4& w, const uint8_t* row_planes, int k, int K) {
+  const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+  uint32_t lo[4], hi[4];
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    lo[r] = ww[r] & 0x0F0F0F0Fu;
+    hi[r] = (ww[r] >> 4) & 0x0F0F0F0Fu;
+  }
+  int s[3];
+#pragma unroll
+  for (int p = 0; p < 3; ++p) {
+    const uint4 xa = *reinterpret_cast<const uint4*>(row_planes + p * K + (k >> 1));
+    const uint4 xb = *reinterpret_cast<const uint4*>(row_planes + p * K + (K >> 1) + (k >> 1));
+    int acc = dp4a_u8_s8(lo[0], xa.x, 0);
+    acc = dp4a_u8_s8(hi[0], xa.y, acc);
+    acc = dp4a_u8_s8(lo[1], xa.z, acc);
+    acc = dp4a_u8_s8(hi[1], xa.w, acc);
+    acc = dp4a_u8_s8(lo[2], xb.x, acc);
+    acc = dp4a_u8_s8(hi[2], xb.y, acc);
+    acc = dp4a_u8_s8(lo[3], xb.z, acc);
+    acc = dp4a_u8_s8(hi[3], xb.w, acc);
+    s[p] = acc;
+  }
+  return s[0] + (s[1] << 8) + (s[2] << 16);
+}
+
+// acc + (s f) * float(S - z * sum(v)) for the segment at k; c is the scale word of the row and the
+// segment's group (fp16 scale | fp16(1024 + zero) << 16).  The words of a row lie one table row
+// apart ([E][K/128][rows]), so the callers load them together with the weights, not here.
+__device__ __forceinline__ float seg_w4(const uint4& w, const uint8_t* row_planes, const float* f, const int* vsum,
+                                        uint32_t c, int k, int K, float acc) {
+  const float s = __half2float(__ushort_as_half(static_cast<unsigned short>(c & 0xFFFFu)));
+  const int z = static_cast<int>((c >> 16) & 0x3FFu);
+  const int S = dot32_w4(w, row_planes, k, K) - z * vsum[k >> 5];
+  return fmaf(s * f[k >> 7], static_cast<float>(S), acc);
+}
+
+constexpr int kSeg = 32 * 32;   // k covered by one warp-wide 16-byte load of packed nibbles
+
+__device__ __forceinline__ StagedW4 carve_w4(uint8_t* base, int rows, int K) {
+  StagedW4 st;
+  st.planes = base;
+  st.f = reinterpret_cast<float*>(base + static_cast<size_t>(rows) * 3 * K);
+  st.vsum = reinterpret_cast<int*>(st.f + rows * (K >> 7));
+  return st;
+}
+size_t staged_w4_bytes(int rows, int K) {
+  return static_cast<size_t>(rows) * (3 * K + (K >> 7) * 4 + (K >> 5) * 4);
+}
+
+__global__ void __launch_bounds__(kUpThreads)
+moe_gemv_w4_up_kernel(const GemvArgs a) {
+  extern __shared__ __align__(16) uint8_t gemv_smem[];
+  const int P = a.M * a.topk;
+  const StagedW4 st = carve_w4(gemv_smem, a.M, a.H);
+  int* s_e = st.vsum + a.M * (a.H >> 5);
+  float* s_gam = reinterpret_cast<float*>(s_e + kGemvMaxPairs);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  griddep_wait();
+  griddep_launch_dependents();
+  stage_routing(a, s_e, s_gam);
+  stage_w4(reinterpret_cast<const __half*>(a.x), a.M, a.H, st, nullptr, kUpThreads);
+  __syncthreads();
+
+  const bool w_on_input = (a.flags & B200MOE_FLAG_WEIGHT_ON_INPUT) != 0;
+  const bool mimic = (a.flags & B200MOE_FLAG_MIMIC_ROUNDING) != 0;
+  const bool ext = a.b1 != nullptr || a.activation == B200MOE_ACT_SWIGLU_OAI;
+  ActParams ap;
+  ap.activation = a.activation;
+  ap.alpha = a.alpha;
+  ap.limit = a.limit;
+  __half* act = reinterpret_cast<__half*>(a.act);
+  const uint8_t* w1 = reinterpret_cast<const uint8_t*>(a.w1);
+  const uint32_t* sz1 = reinterpret_cast<const uint32_t*>(a.w1_sz);
+  const size_t rows = 2 * static_cast<size_t>(a.I);      // weight rows (and scale words per group) of an expert
+  const int G = a.H >> 7;
+
+  // (Two register buffers with the next item's loads in flight while the current one is multiplied
+  // were tried: 89 us against 69 us for the Mixtral-shaped layer at M = 1.)
+  const int total = P * a.I;
+  const int warps = gridDim.x * (kUpThreads / 32);
+  for (int c = warp * gridDim.x + blockIdx.x; c < total; c += warps) {
+    const int p = c / a.I, i = c - p * a.I;
+    const int e = s_e[p];
+    if (e < 0) {
+      if (lane == 0) act[c] = __float2half_rn(0.f);
+      continue;
+    }
+    const int t = p / a.topk;
+    const uint8_t* xp = st.planes + static_cast<size_t>(t) * 3 * a.H;
+    const float* xf = st.f + t * G;
+    const int* xv = st.vsum + t * (a.H >> 5);
+    const uint8_t* wg = w1 + (static_cast<size_t>(e) * rows + i) * (a.H >> 1);
+    const uint8_t* wu = wg + static_cast<size_t>(a.I) * (a.H >> 1);
+    const uint32_t* szg = sz1 + static_cast<size_t>(e) * G * rows + i;
+    const uint32_t* szu = szg + a.I;
+    float ag = 0.f, au = 0.f;
+    for (int k0 = lane * 32; k0 < a.H; k0 += 4 * kSeg) {
+      uint4 gq[4], uq[4];
+      uint32_t cg[4], cu[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int k = k0 + q * kSeg;
+        if (k < a.H) {
+          gq[q] = ldg_stream(wg + (k >> 1));
+          uq[q] = ldg_stream(wu + (k >> 1));
+          cg[q] = __ldg(szg + static_cast<size_t>(k >> 7) * rows);
+          cu[q] = __ldg(szu + static_cast<size_t>(k >> 7) * rows);
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int k = k0 + q * kSeg;
+        if (k < a.H) {
+          ag = seg_w4(gq[q], xp, xf, xv, cg[q], k, a.H, ag);
+          au = seg_w4(uq[q], xp, xf, xv, cu[q], k, a.H, au);
+        }
+      }
+    }
+    ag = warp_sum(ag);
+    au = warp_sum(au);
+    if (lane == 0) {
+      if (a.b1 != nullptr) {
+        ag += __ldg(a.b1 + static_cast<size_t>(e) * 2 * a.I + i);
+        au += __ldg(a.b1 + static_cast<size_t>(e) * 2 * a.I + a.I + i);
+      }
+      const float av = ext ? act_mul<__half, true>(ag, au, w_on_input, s_gam[p], mimic, ap)
+                           : act_mul<__half>(ag, au, w_on_input, s_gam[p], mimic, ap);
+      act[c] = __float2half_rn(av);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kDownThreads)
+moe_gemv_w4_down_kernel(const GemvArgs a) {
+  extern __shared__ __align__(16) uint8_t gemv_smem[];
+  const int P = a.M * a.topk;
+  const StagedW4 st = carve_w4(gemv_smem, P, a.I);
+  int* s_e = st.vsum + P * (a.I >> 5);
+  float* s_gam = reinterpret_cast<float*>(s_e + kGemvMaxPairs);
+  float* s_fold = s_gam + kGemvMaxPairs;
+  float* s_part = s_fold + kGemvMaxPairs;                           // [2 buffers][16 warps][2]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool w_on_input = (a.flags & B200MOE_FLAG_WEIGHT_ON_INPUT) != 0;
+  const bool no_combine = (a.flags & B200MOE_FLAG_NO_COMBINE) != 0;
+  const bool by_pair = no_combine || a.round_pair != 0;
+
+  griddep_wait();
+  griddep_launch_dependents();
+  stage_routing(a, s_e, s_gam);
+  __syncthreads();
+  if (threadIdx.x < P) s_fold[threadIdx.x] = (by_pair || w_on_input) ? 1.0f : s_gam[threadIdx.x];
+  __syncthreads();
+  stage_w4(reinterpret_cast<const __half*>(a.act), P, a.I, st, s_fold, kDownThreads);
+  __syncthreads();
+
+  const uint8_t* w2 = reinterpret_cast<const uint8_t*>(a.w2);
+  const uint32_t* sz2 = reinterpret_cast<const uint32_t*>(a.w2_sz);
+  const size_t rows = static_cast<size_t>(a.H);
+  const int G = a.I >> 7;
+  const int nch = (a.I + kSeg - 1) / kSeg;
+  __half* out = reinterpret_cast<__half*>(a.out);
+  const int half_h = a.H >> 1;
+  const int tasks = a.M * half_h;
+  const int S = by_pair ? 1 : a.down_split;
+  const int grp = warp / S, sub = warp - grp * S;
+  const int groups = gridDim.x * ((kDownThreads / 32) / S);
+  int iter = 0;
+  for (int task = grp * gridDim.x + blockIdx.x; task < tasks; task += groups, ++iter) {
+    const int t = task / half_h, h = (task - t * half_h) << 1;
+    if (!by_pair) {
+      // (pair, segment) flattened: four slots of two 16-byte loads (and their scale words) in flight
+      const int Q = a.topk * nch;
+      float acc0 = 0.f, acc1 = 0.f;
+      int j = 0, ch = 0;
+      for (int q0 = 0; q0 < Q; q0 += 4) {
+        if (S > 1 && ((q0 >> 2) % S) != sub) {
+          ch += 4;
+          while (ch >= nch) {
+            ch -= nch;
+            ++j;
+          }
+          continue;
+        }
+        uint4 wa[4], wb[4];
+        uint2 cc[4];
+        int kk[4], pp[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int p = t * a.topk + j;
+          const int k = ch * kSeg + lane * 32;
+          const int e = (q0 + u < Q) ? s_e[p] : -1;
+          const bool on = e >= 0 && k < a.I;
+          kk[u] = on ? k : -1;
+          pp[u] = p;
+          if (on) {
+            const uint8_t* wr = w2 + ((static_cast<size_t>(e) * rows + h) * a.I + k) / 2;
+            wa[u] = ldg_stream(wr);
+            wb[u] = ldg_stream(wr + (a.I >> 1));
+            // rows h and h + 1 (h even) are neighbours in the scale table: one 8-byte load
+            cc[u] = __ldg(reinterpret_cast<const uint2*>(sz2 + (static_cast<size_t>(e) * G + (k >> 7)) * rows + h));
+          }
+          if (++ch == nch) {
+            ch = 0;
+            ++j;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (kk[u] >= 0) {
+            const int p = pp[u];
+            const uint8_t* xp = st.planes + static_cast<size_t>(p) * 3 * a.I;
+            acc0 = seg_w4(wa[u], xp, st.f + p * G, st.vsum + p * (a.I >> 5), cc[u].x, kk[u], a.I, acc0);
+            acc1 = seg_w4(wb[u], xp, st.f + p * G, st.vsum + p * (a.I >> 5), cc[u].y, kk[u], a.I, acc1);
+          }
+        }
+      }
+      acc0 = warp_sum(acc0);
+      acc1 = warp_sum(acc1);
+      if (S > 1) {
+        float* part = s_part + (iter & 1) * 2 * (kDownThreads / 32);
+        if (lane == 0) {
+          part[2 * warp] = acc0;
+          part[2 * warp + 1] = acc1;
+        }
+        named_bar_sync(1 + grp, 32 * S);
+        if (sub == 0 && lane == 0) {
+          acc0 = 0.f;
+          acc1 = 0.f;
+          for (int w = 0; w < S; ++w) {
+            acc0 += part[2 * (warp + w)];
+            acc1 += part[2 * (warp + w) + 1];
+          }
+        }
+      }
+      if (sub == 0 && lane == 0) {
+        if (a.b2 != nullptr) {
+          for (int jb = 0; jb < a.topk; ++jb) {
+            const int p = t * a.topk + jb;
+            if (s_e[p] >= 0) {
+              const float gam = w_on_input ? 1.0f : s_gam[p];
+              acc0 = fmaf(__ldg(a.b2 + static_cast<size_t>(s_e[p]) * a.H + h), gam, acc0);
+              acc1 = fmaf(__ldg(a.b2 + static_cast<size_t>(s_e[p]) * a.H + h + 1), gam, acc1);
+            }
+          }
+        }
+        out[static_cast<size_t>(t) * a.H + h] = __float2half_rn(acc0 * a.routed_scaling);
+        out[static_cast<size_t>(t) * a.H + h + 1] = __float2half_rn(acc1 * a.routed_scaling);
+      }
+    } else {
+      float sum0 = 0.f, sum1 = 0.f;
+      for (int jb = 0; jb < a.topk; ++jb) {
+        const int p = t * a.topk + jb;
+        const int e = s_e[p];
+        float y0 = 0.f, y1 = 0.f;
+        if (e >= 0) {
+          const uint8_t* wr = w2 + ((static_cast<size_t>(e) * rows + h) * a.I) / 2;
+          const uint32_t* sz = sz2 + static_cast<size_t>(e) * G * rows + h;
+          const uint8_t* xp = st.planes + static_cast<size_t>(p) * 3 * a.I;
+          float acc0 = 0.f, acc1 = 0.f;
+          for (int k0 = lane * 32; k0 < a.I; k0 += 4 * kSeg) {
+            uint4 wa[4], wb[4];
+            uint2 cc[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              if (k0 + q * kSeg < a.I) {
+                wa[q] = ldg_stream(wr + ((k0 + q * kSeg) >> 1));
+                wb[q] = ldg_stream(wr + ((a.I + k0 + q * kSeg) >> 1));
+                cc[q] = __ldg(reinterpret_cast<const uint2*>(sz + static_cast<size_t>((k0 + q * kSeg) >> 7) * rows));
+              }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int k = k0 + q * kSeg;
+              if (k < a.I) {
+                acc0 = seg_w4(wa[q], xp, st.f + p * G, st.vsum + p * (a.I >> 5), cc[q].x, k, a.I, acc0);
+                acc1 = seg_w4(wb[q], xp, st.f + p * G, st.vsum + p * (a.I >> 5), cc[q].y, k, a.I, acc1);
+              }
+            }
+          }
+          acc0 = warp_sum(acc0);
+          acc1 = warp_sum(acc1);
+          if (a.b2 != nullptr) {
+            acc0 += __ldg(a.b2 + static_cast<size_t>(e) * a.H + h);
+            acc1 += __ldg(a.b2 + static_cast<size_t>(e) * a.H + h + 1);
+          }
+          y0 = w_on_input ? acc0 : acc0 * s_gam[p];
+          y1 = w_on_input ? acc1 : acc1 * s_gam[p];
+          if (a.round_pair) {
+            y0 = __half2float(__float2half_rn(y0));
+            y1 = __half2float(__float2half_rn(y1));
+          }
+        }
+        if (no_combine) {
+          if (lane == 0) {
+            out[static_cast<size_t>(p) * a.H + h] = __float2half_rn(y0);
+            out[static_cast<size_t>(p) * a.H + h + 1] = __float2half_rn(y1);
+          }
+        } else {
+          sum0 += y0;
+          sum1 += y1;
+        }
+      }
+      if (!no_combine && lane == 0) {
+        out[static_cast<size_t>(t) * a.H + h] = __float2half_rn(sum0 * a.routed_scaling);
+        out[static_cast<size_t>(t) * a.H + h + 1] = __float2half_rn(sum1 * a.routed_scaling);
+      }
+    }
+  }
+}
+
+size_t routing_smem() { return kGemvMaxPairs * 12 + 2 * 2 * (kDownThreads / 32) * 4 + 64; }   // tables + partial sums
 
 // resident CTAs per SM times SMs, but no more CTAs per SM than the work has warps for: the grid
 // stays a multiple of the SM count, so every SM streams the same share of the weights
@@ -396,24 +784,20 @@ unsigned grid_for(K kernel, size_t smem, int threads, long long items, int num_s
   return static_cast<unsigned>(per_sm) * static_cast<unsigned>(num_sms);
 }
 
-template <typename T>
-int launch_up(const GemvArgs& a, int num_sms, cudaStream_t stream, bool pdl) {
+template <typename K>
+int launch_up(K kernel, const GemvArgs& a, int num_sms, cudaStream_t stream, bool pdl) {
   const size_t smem = gemv_up_smem(a);
-  if (cudaFuncSetAttribute(moe_gemv_up_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           static_cast<int>(smem)) != cudaSuccess)
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return B200MOE_ERR_CUDA;
-  const unsigned grid = grid_for(moe_gemv_up_kernel<T>, smem, kUpThreads, static_cast<long long>(a.M) * a.topk * a.I,
-                                 num_sms);
-  note_launch("moe_gemv_up_kernel<gate/up>");
-  return launch_kernel(moe_gemv_up_kernel<T>, dim3(grid), dim3(kUpThreads), smem, stream, pdl, a) == cudaSuccess
-             ? B200MOE_OK
-             : B200MOE_ERR_CUDA;
+  const unsigned grid = grid_for(kernel, smem, kUpThreads, static_cast<long long>(a.M) * a.topk * a.I, num_sms);
+  note_launch(a.w4 ? "moe_gemv_w4_up_kernel<gate/up>" : "moe_gemv_up_kernel<gate/up>");
+  return launch_kernel(kernel, dim3(grid), dim3(kUpThreads), smem, stream, pdl, a) == cudaSuccess ? B200MOE_OK
+                                                                                                  : B200MOE_ERR_CUDA;
 }
-template <typename T>
-int launch_down(const GemvArgs& a, int num_sms, cudaStream_t stream, bool pdl) {
+template <typename K>
+int launch_down(K kernel, const GemvArgs& a, int num_sms, cudaStream_t stream, bool pdl) {
   const size_t smem = gemv_down_smem(a);
-  if (cudaFuncSetAttribute(moe_gemv_down_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           static_cast<int>(smem)) != cudaSuccess)
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return B200MOE_ERR_CUDA;
   // few output elements (short hidden size): several warps share one, so that every SM still has 16
   // warps' worth of loads in flight
@@ -422,30 +806,35 @@ int launch_down(const GemvArgs& a, int num_sms, cudaStream_t stream, bool pdl) {
   const long long all_warps = static_cast<long long>(num_sms) * (kDownThreads / 32);
   b.down_split = 1;
   while (b.down_split < 8 && tasks * b.down_split * 2 <= all_warps) b.down_split *= 2;
-  const unsigned grid = grid_for(moe_gemv_down_kernel<T>, smem, kDownThreads, tasks * b.down_split, num_sms);
-  note_launch("moe_gemv_down_kernel<down>");
-  return launch_kernel(moe_gemv_down_kernel<T>, dim3(grid), dim3(kDownThreads), smem, stream, pdl, b) == cudaSuccess
-             ? B200MOE_OK
-             : B200MOE_ERR_CUDA;
+  const unsigned grid = grid_for(kernel, smem, kDownThreads, tasks * b.down_split, num_sms);
+  note_launch(a.w4 ? "moe_gemv_w4_down_kernel<down>" : "moe_gemv_down_kernel<down>");
+  return launch_kernel(kernel, dim3(grid), dim3(kDownThreads), smem, stream, pdl, b) == cudaSuccess ? B200MOE_OK
+                                                                                                    : B200MOE_ERR_CUDA;
 }
 
 }  // namespace
 
-size_t gemv_up_smem(const GemvArgs& a) { return static_cast<size_t>(a.M) * a.H * 4 + routing_smem(); }
-size_t gemv_down_smem(const GemvArgs& a) { return static_cast<size_t>(a.M) * a.topk * a.I * 4 + routing_smem(); }
+size_t gemv_up_smem(const GemvArgs& a) {
+  return (a.w4 ? staged_w4_bytes(a.M, a.H) : static_cast<size_t>(a.M) * a.H * 4) + routing_smem();
+}
+size_t gemv_down_smem(const GemvArgs& a) {
+  return (a.w4 ? staged_w4_bytes(a.M * a.topk, a.I) : static_cast<size_t>(a.M) * a.topk * a.I * 4) + routing_smem();
+}
 bool gemv_fits(const GemvArgs& a) {
   return a.M * a.topk <= kGemvMaxPairs && gemv_up_smem(a) + 1024 <= kSmemLimit && gemv_down_smem(a) + 1024 <= kSmemLimit;
 }
 
 int launch_gemv_up(const GemvArgs& a, int num_sms, cudaStream_t stream, bool pdl) {
   if (!gemv_fits(a)) return B200MOE_ERR_UNSUPPORTED;
-  return a.dtype == B200MOE_DTYPE_BF16 ? launch_up<__nv_bfloat16>(a, num_sms, stream, pdl)
-                                       : launch_up<__half>(a, num_sms, stream, pdl);
+  if (a.w4) return launch_up(moe_gemv_w4_up_kernel, a, num_sms, stream, pdl);
+  return a.dtype == B200MOE_DTYPE_BF16 ? launch_up(moe_gemv_up_kernel<__nv_bfloat16>, a, num_sms, stream, pdl)
+                                       : launch_up(moe_gemv_up_kernel<__half>, a, num_sms, stream, pdl);
 }
 int launch_gemv_down(const GemvArgs& a, int num_sms, cudaStream_t stream, bool pdl) {
   if (!gemv_fits(a)) return B200MOE_ERR_UNSUPPORTED;
-  return a.dtype == B200MOE_DTYPE_BF16 ? launch_down<__nv_bfloat16>(a, num_sms, stream, pdl)
-                                       : launch_down<__half>(a, num_sms, stream, pdl);
+  if (a.w4) return launch_down(moe_gemv_w4_down_kernel, a, num_sms, stream, pdl);
+  return a.dtype == B200MOE_DTYPE_BF16 ? launch_down(moe_gemv_down_kernel<__nv_bfloat16>, a, num_sms, stream, pdl)
+                                       : launch_down(moe_gemv_down_kernel<__half>, a, num_sms, stream, pdl);
 }
 
 }  // namespace b200moe

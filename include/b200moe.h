@@ -84,7 +84,11 @@ typedef struct b200moe_cfg {
   int32_t w_layout;       /* B200MOE_LAYOUT_*                                   */
   int32_t activation;     /* B200MOE_ACT_*                                      */
   int32_t flags;          /* B200MOE_FLAG_*                                     */
-  int32_t block_tokens;   /* token block of the GEMMs: 0 = choose, else 16..256 */
+  int32_t block_tokens;   /* token block of the GEMMs: 0 = choose, else 16..256.
+                             With 0, 16-bit weights and at most 16 (token, expert)
+                             pairs the forward calls run two matrix-vector kernels
+                             instead of the grouped GEMMs; a non-zero value keeps
+                             every call on the grouped GEMMs                     */
   float routed_scaling;   /* output multiplier (1.0f for none)                  */
   int32_t num_sms;        /* 0 = query the current device                       */
   int32_t n_global_experts; /* entries of expert_map (required > 0 when a map is passed); ids at or

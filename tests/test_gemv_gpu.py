@@ -1,6 +1,6 @@
 """GPU: the matrix-vector path for a handful of (token, choice) pairs (csrc/gemv.cu).
 
-Calls with 16-bit weights and M * topk <= 16 skip alignment, gather, grouped GEMMs and output
+Calls with 16-bit or int4 weights and M * topk <= 16 skip alignment, gather, grouped GEMMs and output
 conversion: two launches read the routing input directly.  Every case here is checked against the
 CPU oracle and against the grouped-GEMM path on the same inputs (forced by fixing the token
 block), and the launch log must show which path ran.
@@ -136,8 +136,57 @@ def test_gemv_through_the_operator_entry_point(cuda_device):
     assert_parity(out, ref, what="gemv through triton_kernel_fused_experts")
 
 
-def test_quantised_weights_take_the_grouped_path(cuda_device):
-    """FP8 (and int4) rows would be converted element by element on the CUDA cores: slower than the
+def _awq_case(h, i, e, k, m, seed, device):
+    from flaggems_sglang_b200.quant import quantize_awq, repack_awq_for_kernel
+    from flaggems_sglang_b200.testing import make_tokens, make_weights
+    w13, w2 = make_weights(h, i, e, dtype=torch.float16, seed=seed)
+    x, tw, ids = make_tokens(m, h, e, k, dtype=torch.float16, seed=seed)
+    q1 = quantize_awq(w13.transpose(1, 2).contiguous())      # AWQ layout [E, K, N]
+    q2 = quantize_awq(w2.transpose(1, 2).contiguous())
+    p1, z1 = repack_awq_for_kernel(*[t.to(device) for t in q1])
+    p2, z2 = repack_awq_for_kernel(*[t.to(device) for t in q2])
+    return x, tw, ids, q1, q2, dict(use_int4_w4a16=True, w13_sz=z1, w2_sz=z2), p1, p2
+
+
+@pytest.mark.parametrize("h,i,e,k,m", [(1024, 512, 8, 2, 1), (4096, 1024, 8, 2, 1), (512, 384, 64, 8, 2),
+                                        (256, 128, 16, 4, 1), (2048, 1152, 64, 4, 3)])
+def test_gemv_int4_integer_dot_products(cuda_device, h, i, e, k, m):
+    """int4 (AWQ) weights: dp4a on raw nibbles and three int8 activation planes, the arithmetic of the
+    integer tensor-core kernels, so the two paths agree far inside the tolerance."""
+    import flaggems_sglang_b200 as F
+    d = cuda_device
+    x, tw, ids, q1, q2, kw, p1, p2 = _awq_case(h, i, e, k, m, seed=h + m, device=d)
+    out = F.fused_experts(x.to(d), p1, p2, tw.to(d), ids.to(d), **kw)
+    assert any("gemv_w4" in n for n in _names()), _names()
+    grouped = F.fused_experts(x.to(d), p1, p2, tw.to(d), ids.to(d), block_tokens=16, **kw)
+    assert not _is_gemv(), _names()
+    F.check_status()
+    ref = OM.fused_experts_awq(x, *q1, *q2, tw, ids)
+    assert out.dtype == torch.float16
+    assert_parity(out, ref, rtol=2e-2, atol=2e-2, what=f"gemv int4 {(h, i, e, k, m)} vs oracle")
+    assert_parity(out, grouped.float(), rtol=2e-3, atol=2e-3, what=f"gemv int4 {(h, i, e, k, m)} vs grouped path")
+    assert torch.equal(out, F.fused_experts(x.to(d), p1, p2, tw.to(d), ids.to(d), **kw)), "rerun differs"
+
+
+def test_gemv_int4_options(cuda_device):
+    import flaggems_sglang_b200 as F
+    d = cuda_device
+    h, i, e, k = 512, 256, 32, 4
+    x, tw, ids, q1, q2, kw, p1, p2 = _awq_case(h, i, e, k, 2, seed=31, device=d)
+    g = torch.Generator().manual_seed(6)
+    b13 = (torch.randn(e, 2 * i, generator=g) * 0.1).to(d)
+    b2 = (torch.randn(e, h, generator=g) * 0.1).to(d)
+    for extra in (dict(apply_router_weight_on_input=True), dict(no_combine=True), dict(routed_scaling_factor=0.5),
+                  dict(b13=b13, b2=b2, activation="swiglu_oai", swiglu_alpha=1.702, swiglu_limit=7.0)):
+        out = F.fused_experts(x.to(d), p1, p2, tw.to(d), ids.to(d), **kw, **extra)
+        assert any("gemv_w4" in n for n in _names()), (extra.keys(), _names())
+        grouped = F.fused_experts(x.to(d), p1, p2, tw.to(d), ids.to(d), block_tokens=16, **kw, **extra)
+        F.check_status()
+        assert_parity(out, grouped.float(), rtol=2e-3, atol=2e-3, what=f"gemv int4 {list(extra)} vs grouped path")
+
+
+def test_fp8_weights_take_the_grouped_path(cuda_device):
+    """FP8 rows would be converted element by element on the CUDA cores: slower than the
     tensor-core path even at one token, so they stay on it."""
     import flaggems_sglang_b200 as F
     from flaggems_sglang_b200.quant import quantize_fp8_block
