@@ -85,7 +85,7 @@ typedef struct b200moe_cfg {
   int32_t activation;     /* B200MOE_ACT_*                                      */
   int32_t flags;          /* B200MOE_FLAG_*                                     */
   int32_t block_tokens;   /* token block of the GEMMs: 0 = choose, else 16..256.
-                             With 0, 16-bit weights and at most 16 (token, expert)
+                             With 0, 16-bit or int4 weights and at most 16 (token, expert)
                              pairs the forward calls run two matrix-vector kernels
                              instead of the grouped GEMMs; a non-zero value keeps
                              every call on the grouped GEMMs                     */
