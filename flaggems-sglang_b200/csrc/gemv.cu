@@ -216,10 +216,67 @@ moe_gemv_down_kernel(const GemvArgs a) {
   // routing weight is folded into the staged activations and one running sum covers all pairs
   const bool by_pair = no_combine || a.round_pair != 0;
 
-  griddep_wait();
-  griddep_launch_dependents();
+  const T* w2 = reinterpret_cast<const T*>(a.w2);
+  const int nch = (a.I + kChunk - 1) / kChunk;
+  T* out = reinterpret_cast<T*>(a.out);
+  const int half_h = a.H >> 1;
+  const int tasks = a.M * half_h;
+  // With fewer tasks than warps, S = a.down_split warps share a task: each takes a contiguous share
+  // of the (pair, chunk) slots, the partial sums meet in shared memory and are added in a fixed order.
+  const int S = by_pair ? 1 : a.down_split;
+  const int grp = warp / S, sub = warp - grp * S;
+  const int groups = gridDim.x * ((kDownThreads / 32) / S);
+  const int Q = a.topk * nch;
+  const int share = (Q + S - 1) / S;
+  const int q_lo = sub * share, q_hi = min(Q, q_lo + share);
+  float* s_part = s_gam + kGemvMaxPairs;                            // [2 buffers][16 warps][2]
+
+  // a run: eight (pair, chunk) slots of two rows, 16 loads of 16 bytes in flight per lane
+  struct Run {
+    uint4 wa[8], wb[8];
+    int kk[8], pp[8];
+  };
+  auto load_run = [&](Run& r, int t, int h, int q0, int& j, int& ch) {
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int p = t * a.topk + j;
+      const int k = ch * kChunk + lane * 8;
+      const int e = (q0 + u < q_hi) ? s_e[p] : -1;
+      const bool on = e >= 0 && k < a.I;
+      r.kk[u] = on ? k : -1;
+      r.pp[u] = p;
+      if (on) {
+        const T* wr = w2 + (static_cast<size_t>(e) * a.H + h) * a.I + k;
+        r.wa[u] = ldg_stream(wr);
+        r.wb[u] = ldg_stream(wr + a.I);
+      }
+      if (++ch == nch) {
+        ch = 0;
+        ++j;
+      }
+    }
+  };
+
+  // The routing tables and the weights do not depend on the up kernel: they are read before waiting
+  // for it, and when the layer is small (several warps per task: the kernel is a few memory round
+  // trips long) the first run of this warp's first task is put in flight as well.  With one warp per
+  // task the early loads only take bandwidth from the up kernel's tail (Mixtral-shaped layer at M = 1:
+  // 127 us with, 123 us without).
   stage_routing(a, s_e, s_gam);
   __syncthreads();
+  Run r;                       // one register buffer: the prefetched run is consumed in place
+  const int task0 = grp * gridDim.x + blockIdx.x;
+  bool have_pre = false;
+  int pre_j = 0, pre_ch = 0;
+  if (!by_pair && S > 1 && task0 < tasks && q_lo < q_hi) {
+    const int t = task0 / half_h, h = (task0 - t * half_h) << 1;
+    pre_j = q_lo / nch;
+    pre_ch = q_lo - pre_j * nch;
+    load_run(r, t, h, q_lo, pre_j, pre_ch);
+    have_pre = true;
+  }
+  griddep_wait();
+  griddep_launch_dependents();
   const T* act = reinterpret_cast<const T*>(a.act);
   const int quads = a.I >> 2;
   for (int i = threadIdx.x; i < P * quads; i += kDownThreads) {
@@ -232,62 +289,26 @@ moe_gemv_down_kernel(const GemvArgs a) {
   }
   __syncthreads();
 
-  const T* w2 = reinterpret_cast<const T*>(a.w2);
-  const int nch = (a.I + kChunk - 1) / kChunk;
-  T* out = reinterpret_cast<T*>(a.out);
-  const int half_h = a.H >> 1;
-
-  const int tasks = a.M * half_h;
-  // With fewer tasks than warps, S = a.down_split warps share a task: each takes every S-th run of
-  // eight slots, the partial sums meet in shared memory and are added in a fixed order.
-  const int S = by_pair ? 1 : a.down_split;
-  const int grp = warp / S, sub = warp - grp * S;
-  const int groups = gridDim.x * ((kDownThreads / 32) / S);
-  float* s_part = s_gam + kGemvMaxPairs;                            // [2 buffers][16 warps][2]
   int iter = 0;
-  for (int task = grp * gridDim.x + blockIdx.x; task < tasks; task += groups, ++iter) {
+  for (int task = task0; task < tasks; task += groups, ++iter) {
     const int t = task / half_h, h = (task - t * half_h) << 1;
     if (!by_pair) {
-      // (pair, chunk) flattened: eight slots of two 16-byte loads in flight per lane
-      const int Q = a.topk * nch;
       float acc0 = 0.f, acc1 = 0.f;
-      int j = 0, ch = 0;
-      for (int q0 = 0; q0 < Q; q0 += 8) {
-        if (S > 1 && ((q0 >> 3) % S) != sub) {
-          // another warp's run: step the (pair, chunk) counters past it
-          ch += 8;
-          while (ch >= nch) {
-            ch -= nch;
-            ++j;
-          }
-          continue;
-        }
-        uint4 wa[8], wb[8];
-        int kk[8], pp[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const int p = t * a.topk + j;
-          const int k = ch * kChunk + lane * 8;
-          const int e = (q0 + u < Q) ? s_e[p] : -1;
-          const bool on = e >= 0 && k < a.I;
-          kk[u] = on ? k : -1;
-          pp[u] = p;
-          if (on) {
-            const T* wr = w2 + (static_cast<size_t>(e) * a.H + h) * a.I + k;
-            wa[u] = ldg_stream(wr);
-            wb[u] = ldg_stream(wr + a.I);
-          }
-          if (++ch == nch) {
-            ch = 0;
-            ++j;
-          }
+      int j = q_lo / nch, ch = q_lo - j * nch;
+      for (int q0 = q_lo; q0 < q_hi; q0 += 8) {
+        if (have_pre) {
+          j = pre_j;
+          ch = pre_ch;
+          have_pre = false;
+        } else {
+          load_run(r, t, h, q0, j, ch);
         }
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-          if (kk[u] >= 0) {
-            const float* av = s_act + static_cast<size_t>(pp[u]) * a.I;
-            acc0 = dot8<T>(wa[u], av, kk[u], a.I, acc0);
-            acc1 = dot8<T>(wb[u], av, kk[u], a.I, acc1);
+          if (r.kk[u] >= 0) {
+            const float* av = s_act + static_cast<size_t>(r.pp[u]) * a.I;
+            acc0 = dot8<T>(r.wa[u], av, r.kk[u], a.I, acc0);
+            acc1 = dot8<T>(r.wb[u], av, r.kk[u], a.I, acc1);
           }
         }
       }
