@@ -8,8 +8,6 @@ namespace {
 constexpr int kUpThreads = 256;     // 8 warps, one output column (gate row + up row) per warp at a time
 constexpr int kDownThreads = 512;   // 16 warps, two output elements per warp at a time
 constexpr int kChunk = 256;         // elements of one warp-wide 16-byte load
-constexpr int kUpChunks = 4;        // chunks of each row that a lane of the up kernel keeps in flight (8: fewer
-                                    // resident CTAs, measured 10 % slower)
 
 // streaming 16-byte load: the weights are read once, keep them out of L1
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
@@ -115,7 +113,10 @@ __device__ __forceinline__ void stage_routing(const GemvArgs& a, int* s_e, float
 
 // ------------------------------------------------------------------------------------------
 // act[p][i] = activation(w1[e_p][i] . x_t, w1[e_p][I + i] . x_t) in the 16-bit type
-template <typename T>
+// U: 256-element chunks of each row that a lane keeps in flight.  4 by default (8 halves the resident
+// CTAs and measured 10 % slower); 5 or 6 when that is the whole row, so that a row of 1280 or 1536
+// elements does not need a second, nearly empty pass.
+template <typename T, int U>
 __global__ void __launch_bounds__(kUpThreads)
 moe_gemv_up_kernel(const GemvArgs a) {
   extern __shared__ __align__(16) uint8_t gemv_smem[];
@@ -163,11 +164,10 @@ moe_gemv_up_kernel(const GemvArgs a) {
     const T* wg = w1 + (static_cast<size_t>(e) * 2 * a.I + i) * a.H;
     const T* wu = wg + static_cast<size_t>(a.I) * a.H;
     float ag = 0.f, au = 0.f;
-    // four 256-element chunks of both rows in flight per lane
-    for (int k0 = lane * 8; k0 < a.H; k0 += kUpChunks * kChunk) {
-      uint4 gq[kUpChunks], uq[kUpChunks];
+    for (int k0 = lane * 8; k0 < a.H; k0 += U * kChunk) {
+      uint4 gq[U], uq[U];
 #pragma unroll
-      for (int q = 0; q < kUpChunks; ++q) {
+      for (int q = 0; q < U; ++q) {
         const int k = k0 + q * kChunk;
         if (k < a.H) {
           gq[q] = ldg_stream(wg + k);
@@ -175,7 +175,7 @@ moe_gemv_up_kernel(const GemvArgs a) {
         }
       }
 #pragma unroll
-      for (int q = 0; q < kUpChunks; ++q) {
+      for (int q = 0; q < U; ++q) {
         const int k = k0 + q * kChunk;
         if (k < a.H) {
           ag = dot8<T>(gq[q], xs, k, a.H, ag);
@@ -849,8 +849,16 @@ bool gemv_fits(const GemvArgs& a) {
 int launch_gemv_up(const GemvArgs& a, int num_sms, cudaStream_t stream, bool pdl) {
   if (!gemv_fits(a)) return B200MOE_ERR_UNSUPPORTED;
   if (a.w4) return launch_up(moe_gemv_w4_up_kernel, a, num_sms, stream, pdl);
-  return a.dtype == B200MOE_DTYPE_BF16 ? launch_up(moe_gemv_up_kernel<__nv_bfloat16>, a, num_sms, stream, pdl)
-                                       : launch_up(moe_gemv_up_kernel<__half>, a, num_sms, stream, pdl);
+  const int chunks = (a.H + kChunk - 1) / kChunk;
+  const bool bf = a.dtype == B200MOE_DTYPE_BF16;
+  if (chunks == 5)
+    return bf ? launch_up(moe_gemv_up_kernel<__nv_bfloat16, 5>, a, num_sms, stream, pdl)
+              : launch_up(moe_gemv_up_kernel<__half, 5>, a, num_sms, stream, pdl);
+  if (chunks == 6)
+    return bf ? launch_up(moe_gemv_up_kernel<__nv_bfloat16, 6>, a, num_sms, stream, pdl)
+              : launch_up(moe_gemv_up_kernel<__half, 6>, a, num_sms, stream, pdl);
+  return bf ? launch_up(moe_gemv_up_kernel<__nv_bfloat16, 4>, a, num_sms, stream, pdl)
+            : launch_up(moe_gemv_up_kernel<__half, 4>, a, num_sms, stream, pdl);
 }
 int launch_gemv_down(const GemvArgs& a, int num_sms, cudaStream_t stream, bool pdl) {
   if (!gemv_fits(a)) return B200MOE_ERR_UNSUPPORTED;

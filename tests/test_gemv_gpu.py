@@ -49,11 +49,13 @@ def test_gemv_16bit_matches_oracle_and_grouped_path(cuda_device, M, topk, dtype)
     assert torch.equal(out, again), "fixed summation order: a rerun gives the same bits"
 
 
-def test_gemv_ragged_hidden_sizes(cuda_device):
-    """H and I that are multiples of 8 but not of the 256-element warp stride."""
+@pytest.mark.parametrize("h,i", [(264, 136), (1280, 384), (1536, 520)])
+def test_gemv_ragged_hidden_sizes(cuda_device, h, i):
+    """H and I that are multiples of 8 but not of the 256-element warp stride, and rows of five and
+    six chunks (kernel variants that keep the whole row in flight)."""
     import flaggems_sglang_b200 as F
     from flaggems_sglang_b200.testing import make_tokens
-    h, i, e, topk = 264, 136, 16, 2
+    e, topk = 16, 2
     d = cuda_device
     w13, w2 = _layer(h, i, e, d)
     x, tw, ids = make_tokens(2, h, e, topk, seed=5)
@@ -61,7 +63,7 @@ def test_gemv_ragged_hidden_sizes(cuda_device):
     assert _is_gemv(), _names()
     F.check_status()
     ref = OM.fused_experts(x, w13.cpu().float(), w2.cpu().float(), tw, ids)
-    assert_parity(out, ref, what="gemv ragged H=264 I=136")
+    assert_parity(out, ref, what=f"gemv ragged H={h} I={i}")
 
 
 def test_gemv_options(cuda_device):
