@@ -565,24 +565,37 @@ int run_experts(const b200moe_cfg* c, const Layout& L, const void* x, const void
 // instead of alignment, gather, grouped GEMMs and output conversion (gemv.cuh).  Returns
 // B200MOE_ERR_UNSUPPORTED when the call does not qualify; the caller then takes the usual path.
 // A caller that fixes the token block (cfg.block_tokens) asks for the grouped GEMMs.
-int run_gemv(const b200moe_cfg* c, const Layout& L, const void* x, const void* w1, const void* w2,
-             const b200moe_quant* quant, const float* topk_weights, const void* topk_ids,
-             const int32_t* expert_map, const int32_t* hist, const int32_t* topk_indx, const float* gate_scal,
-             uint8_t* ws, void* out, cudaStream_t st, int slot) {
+// Does this problem take the matrix-vector path?  Host arithmetic only.
+bool gemv_eligible(const b200moe_cfg* c, const Layout& L) {
   // 16-bit weights, and int4 weights on integer dot products; FP8 rows would be converted element by
   // element on the CUDA cores, which costs more than the launches saved (measured: a 32-expert FP8
   // layer at M = 1 took 152 us this way, 97 us on the grouped tensor-core path)
   const bool w4 = c->wmode == B200MOE_W_INT4_AWQ;
-  if (L.P <= 0 || L.P > kGemvMaxPairs || c->block_tokens != 0) return B200MOE_ERR_UNSUPPORTED;
+  if (L.P <= 0 || L.P > kGemvMaxPairs || c->block_tokens != 0) return false;
   if ((c->wmode != B200MOE_W_16BIT && !w4) || (c->flags & (B200MOE_FLAG_SIMT | B200MOE_FLAG_W4_SMEM_OPERANDS)))
-    return B200MOE_ERR_UNSUPPORTED;
-  if (w4 && (quant == nullptr || quant->w1_sz == nullptr || quant->w2_sz == nullptr)) return B200MOE_ERR_BAD_ARG;
+    return false;
   // the pairs' 16-bit activations go where the grouped path keeps GEMM-1's output
-  if (static_cast<size_t>(L.cap) * c->I * L.act_bytes < static_cast<size_t>(L.P) * c->I * 2) return B200MOE_ERR_UNSUPPORTED;
+  if (static_cast<size_t>(L.cap) * c->I * L.act_bytes < static_cast<size_t>(L.P) * c->I * 2) return false;
   // every pair streams its expert's weights by itself: two pairs of different tokens that meet in one
   // expert read it twice, which the grouped path does not.  One token's experts are distinct; with more
   // tokens the path is taken only while such meetings are rare (pairs <= experts / 4)
-  if (c->M > 1 && L.P * 4 > c->E) return B200MOE_ERR_UNSUPPORTED;
+  if (c->M > 1 && L.P * 4 > c->E) return false;
+  GemvArgs g = {};
+  g.M = c->M;
+  g.H = c->H;
+  g.I = c->I;
+  g.topk = c->topk;
+  g.w4 = w4 ? 1 : 0;
+  return gemv_fits(g);      // the staged rows must fit in shared memory
+}
+
+int run_gemv(const b200moe_cfg* c, const Layout& L, const void* x, const void* w1, const void* w2,
+             const b200moe_quant* quant, const float* topk_weights, const void* topk_ids,
+             const int32_t* expert_map, const int32_t* hist, const int32_t* topk_indx, const float* gate_scal,
+             uint8_t* ws, void* out, cudaStream_t st, int slot) {
+  if (!gemv_eligible(c, L)) return B200MOE_ERR_UNSUPPORTED;
+  const bool w4 = c->wmode == B200MOE_W_INT4_AWQ;
+  if (w4 && (quant == nullptr || quant->w1_sz == nullptr || quant->w2_sz == nullptr)) return B200MOE_ERR_BAD_ARG;
   const int sms = query_sms(c);
   GemvArgs g = {};
   g.x = x;
@@ -660,6 +673,14 @@ const char* b200moe_status_string(int code) {
     case B200MOE_ERR_TOO_LARGE: return "problem too large for this build";
     default: return "unknown status";
   }
+}
+
+int b200moe_uses_matrix_vector_path(const b200moe_cfg* cfg) {
+  int rc = check_cfg(cfg);
+  if (rc != B200MOE_OK) return rc;
+  Layout L;
+  if ((rc = make_layout(cfg, &L)) != B200MOE_OK) return rc;
+  return gemv_eligible(cfg, L) ? 1 : 0;
 }
 
 int b200moe_pick_block_tokens(const b200moe_cfg* cfg) {

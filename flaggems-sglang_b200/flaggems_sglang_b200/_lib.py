@@ -62,6 +62,7 @@ SYMBOLS = {
     "b200moe_version": (C.c_int, []),
     "b200moe_status_string": (C.c_char_p, [C.c_int]),
     "b200moe_pick_block_tokens": (C.c_int, [C.POINTER(Cfg)]),
+    "b200moe_uses_matrix_vector_path": (C.c_int, [C.POINTER(Cfg)]),
     "b200moe_workspace_bytes": (C.c_size_t, [C.POINTER(Cfg)]),
     "b200moe_align_capacity": (C.c_int, [C.c_int, C.c_int, C.c_int]),
     "b200moe_align_block_size": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int,

@@ -123,6 +123,12 @@ const char *b200moe_status_string(int code);
 /* Token block the library would pick for this problem (16, 32, 64, 128 or 256). */
 int b200moe_pick_block_tokens(const b200moe_cfg *cfg);
 
+/* 1 if the forward calls would run this problem on the two matrix-vector kernels (16-bit or int4
+ * weights, block_tokens = 0, at most 16 (token, expert) pairs: one token, or several while
+ * pairs <= experts / 4, and the staged rows fit in shared memory), 0 if on the grouped GEMMs,
+ * negative B200MOE_ERR_* for a bad cfg.  Host arithmetic only.  No reference counterpart. */
+int b200moe_uses_matrix_vector_path(const b200moe_cfg *cfg);
+
 /* Bytes of scratch b200moe_forward_* needs for this problem (256-byte aligned base). */
 size_t b200moe_workspace_bytes(const b200moe_cfg *cfg);
 

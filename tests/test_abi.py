@@ -53,6 +53,28 @@ def test_argument_errors(built_lib):
     assert built_lib.b200moe_status_string(_lib.ERR_WORKSPACE).decode().startswith("workspace")
 
 
+def test_matrix_vector_path_selection(built_lib):
+    """Which problems the forward calls run on the two matrix-vector kernels (host arithmetic only)."""
+    from flaggems_sglang_b200 import _lib
+
+    def uses(m, h, i, e, k, wmode=_lib.W_16BIT, dtype=0, block_tokens=0, flags=0):
+        cfg = _lib.Cfg(C.sizeof(_lib.Cfg), m, h, i, e, k, dtype, wmode, 0, 0, flags, block_tokens, 1.0, 148)
+        return built_lib.b200moe_uses_matrix_vector_path(C.byref(cfg))
+
+    assert uses(1, 4096, 14336, 8, 2) == 1                     # one token: always, its experts are distinct
+    assert uses(1, 2048, 768, 128, 8) == 1
+    assert uses(2, 2048, 768, 128, 8) == 1                     # 16 pairs over 128 experts
+    assert uses(2, 4096, 14336, 8, 2) == 0                     # 4 pairs over 8 experts: they would meet
+    assert uses(3, 2048, 768, 128, 8) == 0                     # 24 pairs
+    assert uses(1, 2048, 768, 128, 8, block_tokens=16) == 0    # the caller asked for the grouped GEMMs
+    assert uses(1, 7168, 2048, 256, 8, wmode=_lib.W_FP8_BLOCK) == 0
+    assert uses(1, 4096, 14336, 8, 2, wmode=_lib.W_INT4_AWQ, dtype=1) == 1
+    assert uses(1, 4096, 14336, 8, 2, flags=_lib.FLAG_SIMT) == 0
+    assert uses(1, 4096, 32768, 8, 4) == 0                     # 4 x 32768 fp32 activations do not fit in shared memory
+    bad = _lib.Cfg(4, 1, 128, 128, 8, 2, 0, 0, 0, 0, 0, 0, 1.0, 0)
+    assert built_lib.b200moe_uses_matrix_vector_path(C.byref(bad)) == _lib.ERR_BAD_ARG
+
+
 def test_product_fails_loudly_without_gpu():
     import torch
     import flaggems_sglang_b200 as F
